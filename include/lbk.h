@@ -1,0 +1,209 @@
+/* lbk.h - C ABI of the B200 tree-building kernels ("lbk").
+ *
+ * This is the drop-in boundary for the two tasks of legate-boost's tree model:
+ *   BUILD_TREE  (reference: src/models/tree/build_tree.cu:1274-1365, opcode 1 in src/legateboost.h:22)
+ *   PREDICT     (reference: src/models/tree/predict.cu:26-91,        opcode 2 in src/legateboost.h:23)
+ * A task body that receives a legate::TaskContext unpacks its stores into the argument
+ * structs below and calls lbk_build_tree / lbk_predict; nothing else of the reference changes.
+ *
+ * Conventions
+ *   - plain C, no C++/torch types; every pointer is a raw address and every size is explicit;
+ *   - data pointers are DEVICE pointers unless the struct's `host_buffers` field is non-zero,
+ *     in which case they are host pointers and the library stages the copies itself on `stream`;
+ *   - every call returns 0 on success or a negative lbk_status; lbk_last_error() gives the text;
+ *   - a context belongs to one device and one host thread at a time; different contexts may be
+ *     used concurrently from different threads (one per GPU, as the runtime calls task variants);
+ *   - there is no CPU fallback: every entry point fails with LBK_ERR_CUDA when no device is
+ *     usable.
+ */
+#ifndef LBK_H_
+#define LBK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum lbk_status {
+  LBK_OK            = 0,
+  LBK_ERR_ARGUMENT  = -1, /* bad shape / null pointer / unsupported value (reference: EXPECT, cpp_utils.h:85-96) */
+  LBK_ERR_CUDA      = -2, /* a CUDA runtime call failed (reference: CHECK_CUDA, cpp_utils.cuh:45-58) */
+  LBK_ERR_COMM      = -3, /* a collective failed (reference: CHECK_NCCL, cpp_utils.cuh:35-43) */
+  LBK_ERR_DEVICE    = -4, /* a kernel reported a fault through its status word (replaces EXPECT_DEVICE's trap) */
+  LBK_ERR_ALLOC     = -5  /* scratch allocation failed */
+} lbk_status;
+
+typedef enum lbk_dtype { LBK_F32 = 0, LBK_F64 = 1, LBK_I32 = 2, LBK_I64 = 3 } lbk_dtype;
+typedef enum lbk_redop { LBK_SUM = 0, LBK_MAX = 1 } lbk_redop;
+
+typedef struct lbk_context lbk_context;
+
+/* Version of this ABI (major*1000 + minor). */
+int lbk_version(void);
+
+/* Context: owns the scratch memory pool, the status word and (optionally) a communicator for
+ * one device.  Replaces the per-task state the reference gets from the runtime
+ * (legate::create_buffer scratch, context.get_task_stream(), context.communicator(0)). */
+int lbk_context_create(int device, lbk_context** out);
+void lbk_context_destroy(lbk_context* ctx);
+/* Text of the last error on this context (or of the last context-less call on this thread). */
+const char* lbk_last_error(const lbk_context* ctx);
+/* Release cached scratch memory back to the driver. */
+int lbk_context_trim(lbk_context* ctx);
+
+/* Communicator (reference: the ncclComm_t* the runtime hands to the task, cpp_utils.cuh:100-134).
+ * Either create one from an id that rank 0 made and every rank received out of band ... */
+#define LBK_UNIQUE_ID_BYTES 128
+int lbk_comm_unique_id(void* id_out /* LBK_UNIQUE_ID_BYTES */);
+int lbk_comm_init(lbk_context* ctx, const void* id, int rank, int n_ranks);
+/* ... or attach an existing ncclComm_t (what a legate adapter passes; not destroyed by lbk) ... */
+int lbk_comm_attach_nccl(lbk_context* ctx, void* nccl_comm, int rank, int n_ranks);
+/* ... or supply the all-reduce as a callback (in place on a device buffer, ordered on `stream`). */
+typedef int (*lbk_allreduce_fn)(void* user, void* buf, size_t count, int dtype /* lbk_dtype */,
+                                int op /* lbk_redop */, void* stream);
+int lbk_comm_set_callback(lbk_context* ctx, lbk_allreduce_fn fn, void* user, int rank, int n_ranks);
+int lbk_comm_size(const lbk_context* ctx);
+
+/* ------------------------------------------------------------------------------------------
+ * BUILD_TREE.  Field order follows the task's argument order (legateboost/models/tree.py:117-183,
+ * build_tree.cu:1278-1307): inputs X, g, h, optional feature set; scalars max_depth, max_nodes,
+ * split_samples, seed, dataset_rows, l1, l2, min_split_gain; outputs leaf_value, feature,
+ * split_value, gain, hessian.  Rows [row_offset, row_offset+n_local_rows) of the global data set
+ * live on this rank (the store's shape.lo[0] and extent).
+ */
+typedef struct lbk_build_tree_args {
+  const void* X;      /* [n_local_rows, n_features], element stride 1, row stride ldx elements */
+  int32_t x_dtype;    /* LBK_F32 or LBK_F64 */
+  int64_t ldx;
+  const double* g;    /* [n_local_rows, n_outputs], row stride ldg elements */
+  const double* h;
+  int64_t ldg;
+  const uint8_t* feature_set; /* optional bool[n_features]; NULL = all features */
+  int64_t row_offset;
+  int64_t n_local_rows;
+  int32_t n_features;
+  int32_t n_outputs;
+  /* scalars 0-7 */
+  int32_t max_depth;
+  int32_t max_nodes;     /* must equal 2^(max_depth+1)-1 */
+  int32_t split_samples; /* <= 2048 */
+  int32_t seed;
+  int64_t dataset_rows;
+  double l1_regularization;
+  double l2_regularization;
+  double min_split_gain;
+  /* outputs 0-4, identical on every rank */
+  double* leaf_value;  /* [max_nodes, n_outputs] */
+  int32_t* feature;    /* [max_nodes], -1 = leaf */
+  double* split_value; /* [max_nodes] */
+  double* gain;        /* [max_nodes] */
+  double* hessian;     /* [max_nodes, n_outputs] */
+  void* stream;        /* cudaStream_t; the call returns after the stream has drained, as the
+                          reference does (build_tree.cu:1356) */
+  int32_t host_buffers;
+  /* Optional device-side traces for tests (NULL to skip): */
+  int64_t* trace_node_sums; /* [max_nodes, n_outputs, 2] quantised node sums */
+  int64_t* trace_hist;      /* [trace_nodes, n_outputs, B, 2]: each node's histogram as it was when
+                               its split was evaluated */
+  int32_t trace_nodes;
+  int32_t* out_total_bins;  /* host pointer: B */
+} lbk_build_tree_args;
+
+int lbk_build_tree(lbk_context* ctx, const lbk_build_tree_args* args);
+
+/* ------------------------------------------------------------------------------------------
+ * PREDICT.  Inputs X then (leaf_value, feature, split_value) per tree, output pred
+ * (legateboost/models/tree.py:252-277, predict.cu:26-84).  pred is overwritten (zero + sum of
+ * leaves in tree order, float64); the caller adds the model's initial prediction.
+ */
+typedef struct lbk_predict_args {
+  const void* X;
+  int32_t x_dtype;
+  int64_t ldx;
+  int64_t n_rows;
+  int32_t n_features;
+  int32_t n_outputs;
+  int32_t n_trees;
+  const double* const* leaf_value;  /* host array of n_trees pointers, each [max_nodes[t], n_outputs] */
+  const int32_t* const* feature;    /* each [max_nodes[t]] */
+  const double* const* split_value; /* each [max_nodes[t]] */
+  const int32_t* max_nodes;         /* host array [n_trees] */
+  double* pred;                     /* [n_rows, n_outputs], row stride ldp elements */
+  int64_t ldp;
+  void* stream;
+  int32_t host_buffers;
+} lbk_predict_args;
+
+int lbk_predict(lbk_context* ctx, const lbk_predict_args* args);
+
+/* ------------------------------------------------------------------------------------------
+ * Stage-level entry points.  They expose the steps of BUILD_TREE separately so each can be
+ * checked and timed on its own; lbk_build_tree runs the same kernels.
+ */
+
+/* Split proposals (reference: SelectSplitSamples, build_tree.cu:867-964).  Writes the CSR of
+ * sorted unique sampled values per feature, last value of every feature = +inf.
+ * proposals: [n_features*split_samples] of x_dtype (first B valid), row_ptr: [n_features+1].
+ * total_bins is a host pointer. */
+int lbk_split_proposals(lbk_context* ctx, const void* X, int x_dtype, int64_t ldx, int64_t row_offset,
+                        int64_t n_local_rows, int n_features, int split_samples, int seed,
+                        int64_t dataset_rows, void* proposals, int32_t* row_ptr, int32_t* total_bins,
+                        void* stream);
+
+/* Bin ids (reference: SparseSplitProposals::FindBin, build_tree.h:178-185, evaluated once per
+ * tree instead of once per level).  bins layout: feature groups of 32, group-major:
+ *   bins[(f/32)*n_rows*32 + row*32 + f%32] = index of the first proposal >= x inside feature f.
+ * bin_bytes = 1 (every feature has <= 256 proposals) or 2. */
+int lbk_bin_matrix(lbk_context* ctx, const void* X, int x_dtype, int64_t ldx, int64_t n_rows,
+                   int n_features, const void* proposals, const int32_t* row_ptr, void* bins,
+                   int bin_bytes, void* stream);
+/* Size in bytes of the bins buffer for the layout above. */
+size_t lbk_bin_matrix_bytes(int64_t n_rows, int n_features, int bin_bytes);
+
+/* Quantised gradient pairs (reference: GradientQuantiser, build_tree.cu:51-140, and
+ * reduce_base_sums, :168-204).  gpair: int32 [n_local_rows, n_outputs, 2]; root_sums: int64
+ * [n_outputs, 2] (summed over ranks); scale: double[4] = scale.g, scale.h, 1/scale.g, 1/scale.h. */
+int lbk_quantise(lbk_context* ctx, const double* g, const double* h, int64_t ldg, int64_t row_offset,
+                 int64_t n_local_rows, int n_outputs, int seed, int32_t* gpair, int64_t* root_sums,
+                 double* scale, void* stream);
+
+/* Histogram build over node-grouped rows (reference: fill_histogram_shared, build_tree.cu:213-577).
+ * Rows are given as an index array grouped by node: rows of node (node_begin + j) are
+ * row_index[seg[j] .. seg[j+1]).  For every listed node, output and feature:
+ *   hist[j][k][row_ptr[f] + bin(row,f)] += value(row,k)
+ * mode 0: value = int32 pair from gpair, hist = int64 pairs  [n_nodes, n_outputs, B, 2]
+ * mode 1: value = float32 pair from gpair_f32, hist = float64 pairs of the same shape.
+ * hist is zeroed by the call. */
+typedef struct lbk_histogram_args {
+  const void* bins;   /* layout of lbk_bin_matrix */
+  int32_t bin_bytes;
+  int64_t n_rows;     /* rows of the bin matrix */
+  int32_t n_features;
+  const int32_t* row_ptr;   /* [n_features+1] device (host if host_buffers) */
+  int32_t total_bins;       /* B = row_ptr[n_features] */
+  const int32_t* gpair;     /* mode 0: [n_rows, n_outputs, 2] int32 */
+  const float* gpair_f32;   /* mode 1: [n_rows, n_outputs, 2] float32 */
+  int32_t n_outputs;
+  const int32_t* row_index; /* [seg[n_nodes]] */
+  const int32_t* seg;       /* [n_nodes+1] */
+  int32_t n_nodes;
+  int32_t mode;
+  void* hist;
+  void* stream;
+  int32_t host_buffers;
+} lbk_histogram_args;
+
+int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* args);
+
+/* Group rows by node id (stable): row_index/seg as lbk_histogram expects.  node_of_row values
+ * outside [node_begin, node_begin+n_nodes) are dropped.  (Reference: the radix sort of
+ * (node,row) pairs in UpdatePositions, build_tree.cu:1050-1079.) */
+int lbk_group_rows(lbk_context* ctx, const int32_t* node_of_row, int64_t n_rows, int node_begin,
+                   int n_nodes, int32_t* row_index, int32_t* seg, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LBK_H_ */

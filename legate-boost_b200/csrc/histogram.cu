@@ -1,0 +1,482 @@
+// Histogram construction: hist[node][output][bin] += (grad, hess) for the rows of the nodes that
+// have to be built on this level.
+//
+// Reference behaviour restated here: fill_histogram_shared / HistogramAgent,
+// src/models/tree/build_tree.cu:213-577 (shared-memory int32 pairs per block flushed with 64-bit
+// global atomics, impure tiles straight to global atomics).
+//
+// Design for B200:
+//   * rows arrive grouped by node (an index array plus per-node offsets), so a thread block only
+//     ever accumulates one node at a time and its private histogram lives in shared memory;
+//   * bins are one byte per element in groups of 32 features (see proposals.cu); a warp handles
+//     one row at a time with ONE LANE PER FEATURE, and the private histogram is laid out
+//     [bin][lane]: lane l always hits shared-memory bank l, so the two atomics a warp issues per
+//     row are conflict free whatever the bins are, and no two lanes of a warp share an address;
+//   * the row index and the quantised pair of a row are staged once per 512 rows into shared
+//     memory (coalesced index load, one gather per row) and re-read by broadcast;
+//   * accumulation is in int32 like the reference, but guarded: the sum of |q| over everything
+//     accumulated since the last flush is tracked per block and the private histogram is flushed
+//     before it could reach 2^31, so no partial sum can wrap;
+//   * work is cut into (node, row chunk, feature group, output) tickets sized on the device so
+//     that every level gives each resident block about two tickets; blocks draw tickets from an
+//     atomic counter (persistent grid = 3 blocks per SM, limited by 72 KB of shared memory);
+//   * a node whose rows fit one chunk owns its output region and flushes with plain stores;
+//     otherwise the flush uses 64-bit global atomics; chunks of <= 128 rows skip shared memory.
+#include "device_utils.cuh"
+#include "internal.h"
+
+namespace lbk {
+namespace {
+
+constexpr int kHistThreads = 256;
+constexpr int kHistWarps   = kHistThreads / 32;
+constexpr int kStageRows   = 512;   // rows staged per sub-tile
+constexpr int kDirectRows  = 128;   // chunks up to this size go straight to global atomics
+constexpr int kMinChunk    = 2048;
+constexpr int kSmemBins    = 256;   // bins per feature held by the private histogram
+
+struct HistParams {
+  const void* bins;
+  int64_t n_rows;
+  int F, K, B, G, mb;
+  const int32_t* row_ptr;
+  const void* gpair;
+  const int32_t* row_index;
+  const int32_t* seg;
+  const int32_t* slot_of_node;  // may be null = identity
+  int n_nodes;
+  const int32_t* chunk_off;  // [n_nodes+1]
+  const int32_t* plan;       // [0] rows per chunk, [1] total chunks
+  unsigned int* ticket;
+  void* out;
+};
+
+// Single block: rows per chunk for this level and the chunk offsets of every built node.
+__global__ void __launch_bounds__(1024)
+  k_hist_plan(const int32_t* __restrict__ seg, const int32_t* __restrict__ slot_of_node, int n_nodes, int GK,
+              int target_tickets, int32_t* __restrict__ chunk_off, int32_t* __restrict__ plan,
+              unsigned int* __restrict__ ticket)
+{
+  __shared__ long long red[32];
+  __shared__ int wsum[32];
+  __shared__ int carry;
+  __shared__ int ch_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  long long rows = 0;
+  for (int j = tid; j < n_nodes; j += blockDim.x) {
+    const bool built = slot_of_node == nullptr || slot_of_node[j] >= 0;
+    if (built) rows += seg[j + 1] - seg[j];
+  }
+  for (int off = 16; off >= 1; off >>= 1) rows += __shfl_down_sync(0xffffffffu, rows, off);
+  if (lane == 0) red[warp] = rows;
+  __syncthreads();
+  if (tid == 0) {
+    long long total = 0;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) total += red[w];
+    long long ch = (total * GK + target_tickets - 1) / target_tickets;
+    if (ch < kMinChunk) ch = kMinChunk;
+    ch = (ch + kStageRows - 1) / kStageRows * kStageRows;
+    if (ch > (1ll << 30)) ch = 1ll << 30;
+    ch_s  = static_cast<int>(ch);
+    carry = 0;
+    chunk_off[0] = 0;
+  }
+  __syncthreads();
+  const int ch = ch_s;
+  for (int base = 0; base < n_nodes; base += blockDim.x) {
+    const int j = base + tid;
+    int c       = 0;
+    if (j < n_nodes) {
+      const bool built = slot_of_node == nullptr || slot_of_node[j] >= 0;
+      const int r      = seg[j + 1] - seg[j];
+      c                = (built && r > 0) ? (r + ch - 1) / ch : 0;
+    }
+    int incl = c;
+    for (int off = 1; off < 32; off <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += n;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w  = lane < (blockDim.x >> 5) ? wsum[lane] : 0;
+      int wi = w;
+      for (int off = 1; off < 32; off <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, wi, off);
+        if (lane >= off) wi += n;
+      }
+      wsum[lane] = wi - w;
+    }
+    __syncthreads();
+    const int before = carry + wsum[warp];
+    if (j < n_nodes) chunk_off[j + 1] = before + incl;
+    __syncthreads();
+    if (tid == blockDim.x - 1) carry = before + incl;
+    __syncthreads();
+  }
+  if (tid == 0) {
+    plan[0] = ch;
+    plan[1] = carry;
+    *ticket = 0;
+  }
+}
+
+template <bool kFloat>
+struct Acc;
+template <>
+struct Acc<false> {
+  using smem_t = int;
+  using in_t   = int2;
+  using out_t  = GPairI64;
+  __device__ static void add_global(out_t* dst, int g, int h)
+  {
+    atomicAdd(reinterpret_cast<unsigned long long*>(&dst->grad), static_cast<unsigned long long>(static_cast<long long>(g)));
+    atomicAdd(reinterpret_cast<unsigned long long*>(&dst->hess), static_cast<unsigned long long>(static_cast<long long>(h)));
+  }
+  __device__ static void store_global(out_t* dst, int g, int h)
+  {
+    *reinterpret_cast<longlong2*>(dst) = make_longlong2(g, h);
+  }
+  __device__ static bool nonzero(int g, int h) { return (g | h) != 0; }
+};
+template <>
+struct Acc<true> {
+  using smem_t = float;
+  using in_t   = float2;
+  using out_t  = GPairF64;
+  __device__ static void add_global(out_t* dst, float g, float h)
+  {
+    atomicAdd(&dst->grad, static_cast<double>(g));
+    atomicAdd(&dst->hess, static_cast<double>(h));
+  }
+  __device__ static void store_global(out_t* dst, float g, float h)
+  {
+    *reinterpret_cast<double2*>(dst) = make_double2(g, h);
+  }
+  __device__ static bool nonzero(float g, float h) { return g != 0.f || h != 0.f; }
+};
+
+template <typename BinT, bool kFloat, bool kSmem>
+__global__ void __launch_bounds__(kHistThreads)
+  k_hist(const HistParams p)
+{
+  using A      = Acc<kFloat>;
+  using smem_t = typename A::smem_t;
+  using in_t   = typename A::in_t;
+  using out_t  = typename A::out_t;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  smem_t* hg   = reinterpret_cast<smem_t*>(smem_raw);
+  smem_t* hh   = hg + (kSmem ? p.mb * kGroup : 0);
+  int4* stage  = reinterpret_cast<int4*>(hh + (kSmem ? p.mb * kGroup : 0));
+  __shared__ unsigned int s_ticket;
+  __shared__ long long s_red[2][kHistWarps];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int CH           = p.plan[0];
+  const int total_chunks = p.plan[1];
+  const long long total  = static_cast<long long>(total_chunks) * p.G * p.K;
+  const BinT* bins       = static_cast<const BinT*>(p.bins);
+  const in_t* gpair      = static_cast<const in_t*>(p.gpair);
+  out_t* out             = static_cast<out_t*>(p.out);
+  const int hist_words   = p.mb * kGroup;
+
+  while (true) {
+    __syncthreads();
+    if (tid == 0) s_ticket = atomicAdd(p.ticket, 1u);
+    __syncthreads();
+    const long long t = s_ticket;
+    if (t >= total) break;
+    const int k = static_cast<int>(t % p.K);
+    const int g = static_cast<int>((t / p.K) % p.G);
+    const int c = static_cast<int>(t / (static_cast<long long>(p.K) * p.G));
+    // node that owns chunk c: last j with chunk_off[j] <= c
+    int lo = 0, hi = p.n_nodes;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.chunk_off[mid] <= c) lo = mid; else hi = mid;
+    }
+    const int j       = lo;
+    const int nchunks = p.chunk_off[j + 1] - p.chunk_off[j];
+    const int slot    = p.slot_of_node ? p.slot_of_node[j] : j;
+    const int rb      = p.seg[j] + (c - p.chunk_off[j]) * CH;
+    const int re      = min(p.seg[j + 1], rb + CH);
+    const int feat    = g * kGroup + lane;
+    const bool active = feat < p.F;
+    const int fbeg    = active ? p.row_ptr[feat] : 0;
+    const int fbins   = active ? p.row_ptr[feat + 1] - fbeg : 0;
+    out_t* obase      = out + (static_cast<int64_t>(slot) * p.K + k) * p.B + fbeg;
+    const BinT* gbins = bins + static_cast<int64_t>(g) * p.n_rows * kGroup + lane;
+
+    auto direct_rows = [&](int b, int e) {
+      for (int r = b + warp; r < e; r += kHistWarps) {
+        const int ridx = p.row_index[r];
+        const in_t v   = gpair[static_cast<int64_t>(ridx) * p.K + k];
+        if (active) {
+          const int bin = gbins[static_cast<int64_t>(ridx) * kGroup];
+          A::add_global(obase + bin, v.x, v.y);
+        }
+      }
+    };
+
+    if (!kSmem || re - rb <= kDirectRows) {
+      direct_rows(rb, re);
+      continue;
+    }
+
+    bool use_atomics = nchunks > 1;
+    auto flush = [&](bool atomics) {
+      for (int e = tid; e < hist_words; e += kHistThreads) {  // e & 31 == lane for every e of a thread
+        const int bin = e >> 5;
+        if (bin < fbins) {
+          const smem_t vg = hg[e], vh = hh[e];
+          if (A::nonzero(vg, vh)) {
+            if (atomics) A::add_global(obase + bin, vg, vh); else A::store_global(obase + bin, vg, vh);
+          }
+        }
+      }
+    };
+    for (int e = tid; e < hist_words; e += kHistThreads) {
+      hg[e] = smem_t(0);
+      hh[e] = smem_t(0);
+    }
+    long long run_g = 0, run_h = 0;
+    for (int st = rb; st < re; st += kStageRows) {
+      const int n = min(kStageRows, re - st);
+      __syncthreads();  // previous sub-tile fully consumed (and zeroing done) before restaging
+      long long ag = 0, ah = 0;
+      for (int i = tid; i < n; i += kHistThreads) {
+        const int ridx = p.row_index[st + i];
+        const in_t v   = gpair[static_cast<int64_t>(ridx) * p.K + k];
+        int4 rec;
+        rec.x = ridx;
+        if (kFloat) {
+          rec.y = __float_as_int(v.x);
+          rec.z = __float_as_int(v.y);
+        } else {
+          rec.y = v.x;
+          rec.z = v.y;
+          ag += llabs(static_cast<long long>(v.x));
+          ah += llabs(static_cast<long long>(v.y));
+        }
+        rec.w    = 0;
+        stage[i] = rec;
+      }
+      bool direct_tile = false;
+      if (!kFloat) {
+        for (int off = 16; off >= 1; off >>= 1) {
+          ag += __shfl_down_sync(0xffffffffu, ag, off);
+          ah += __shfl_down_sync(0xffffffffu, ah, off);
+        }
+        if (lane == 0) {
+          s_red[0][warp] = ag;
+          s_red[1][warp] = ah;
+        }
+        __syncthreads();
+        long long tg = 0, th = 0;
+#pragma unroll
+        for (int w = 0; w < kHistWarps; ++w) {
+          tg += s_red[0][w];
+          th += s_red[1][w];
+        }
+        const long long lim = 2147483647ll;
+        if (tg > lim || th > lim) {
+          direct_tile = true;  // this sub-tile alone could wrap an int32: add it with 64-bit atomics
+        } else if (run_g + tg > lim || run_h + th > lim) {
+          flush(true);
+          use_atomics = true;
+          __syncthreads();
+          for (int e = tid; e < hist_words; e += kHistThreads) {
+            hg[e] = smem_t(0);
+            hh[e] = smem_t(0);
+          }
+          run_g = tg;
+          run_h = th;
+        } else {
+          run_g += tg;
+          run_h += th;
+        }
+        if (direct_tile) use_atomics = true;
+      }
+      __syncthreads();
+      if (direct_tile) {
+        direct_rows(st, st + n);
+        continue;
+      }
+#pragma unroll 4
+      for (int r = warp; r < n; r += kHistWarps) {
+        const int4 rec = stage[r];
+        if (active) {
+          const int bin = gbins[static_cast<int64_t>(rec.x) * kGroup];
+          const int idx = bin * kGroup + lane;
+          if (kFloat) {
+            atomicAdd(reinterpret_cast<float*>(hg) + idx, __int_as_float(rec.y));
+            atomicAdd(reinterpret_cast<float*>(hh) + idx, __int_as_float(rec.z));
+          } else {
+            atomicAdd(reinterpret_cast<int*>(hg) + idx, rec.y);
+            atomicAdd(reinterpret_cast<int*>(hh) + idx, rec.z);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    flush(use_atomics);
+  }
+}
+
+// ---- row grouping (utility for the stage-level API) -------------------------------------------
+constexpr int kGroupTile = 4096;
+
+__global__ void k_group_count(const int32_t* __restrict__ node_of_row, int64_t n_rows, int node_begin, int n_nodes,
+                              int32_t* __restrict__ counts /* [blocks][n_nodes] */)
+{
+  extern __shared__ int cnt[];
+  for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kGroupTile;
+  for (int i = threadIdx.x; i < kGroupTile; i += blockDim.x) {
+    const int64_t r = base + i;
+    if (r < n_rows) {
+      const int nd = node_of_row[r] - node_begin;
+      if (nd >= 0 && nd < n_nodes) atomicAdd(&cnt[nd], 1);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_nodes; i += blockDim.x)
+    counts[static_cast<int64_t>(blockIdx.x) * n_nodes + i] = cnt[i];
+}
+
+// counts[b][nd] -> exclusive offset of (nd, b) in node-major order; seg[nd] = start of node nd
+__global__ void k_group_scan(int32_t* __restrict__ counts, int n_blocks, int n_nodes, int32_t* __restrict__ seg)
+{
+  // one thread per node sums its column, then a serial scan over nodes by thread 0
+  extern __shared__ int tot[];
+  for (int nd = threadIdx.x; nd < n_nodes; nd += blockDim.x) {
+    int s = 0;
+    for (int b = 0; b < n_blocks; ++b) s += counts[static_cast<int64_t>(b) * n_nodes + nd];
+    tot[nd] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int nd = 0; nd < n_nodes; ++nd) {
+      seg[nd] = run;
+      run += tot[nd];
+    }
+    seg[n_nodes] = run;
+  }
+  __syncthreads();
+  for (int nd = threadIdx.x; nd < n_nodes; nd += blockDim.x) {
+    int run = seg[nd];
+    for (int b = 0; b < n_blocks; ++b) {
+      const int c = counts[static_cast<int64_t>(b) * n_nodes + nd];
+      counts[static_cast<int64_t>(b) * n_nodes + nd] = run;
+      run += c;
+    }
+  }
+}
+
+// one warp per tile walks its rows in order so that rows keep their relative order inside a node
+__global__ void k_group_scatter(const int32_t* __restrict__ node_of_row, int64_t n_rows, int node_begin, int n_nodes,
+                                const int32_t* __restrict__ offsets, int32_t* __restrict__ row_index)
+{
+  extern __shared__ int cur[];
+  const int lane = threadIdx.x;
+  for (int i = lane; i < n_nodes; i += 32) cur[i] = offsets[static_cast<int64_t>(blockIdx.x) * n_nodes + i];
+  __syncwarp();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kGroupTile;
+  for (int i = 0; i < kGroupTile; i += 32) {
+    const int64_t r = base + i + lane;
+    int nd          = -1;
+    if (r < n_rows) {
+      nd = node_of_row[r] - node_begin;
+      if (nd < 0 || nd >= n_nodes) nd = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, nd);
+    const int rank       = __popc(peers & ((1u << lane) - 1u));
+    int start            = 0;
+    if (nd >= 0) start = cur[nd];
+    __syncwarp();
+    if (nd >= 0) {
+      row_index[start + rank] = static_cast<int32_t>(r);
+      if (rank == __popc(peers) - 1) cur[nd] = start + rank + 1;
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace
+
+void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStream_t stream)
+{
+  if (lv.n_nodes <= 0) return;
+  HistParams p;
+  p.bins         = lv.bins;
+  p.n_rows       = lv.n_rows;
+  p.F            = lv.F;
+  p.K            = lv.K;
+  p.B            = lv.B;
+  p.G            = (lv.F + kGroup - 1) / kGroup;
+  p.row_ptr      = lv.row_ptr;
+  p.gpair        = lv.float_mode ? static_cast<const void*>(lv.gpair_f) : static_cast<const void*>(lv.gpair);
+  p.row_index    = lv.row_index;
+  p.seg          = lv.seg + lv.seg_node_offset;
+  p.slot_of_node = lv.slot_of_node;
+  p.n_nodes      = lv.n_nodes;
+  int32_t* chunk_off = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes) + 1);
+  int32_t* plan      = s.alloc<int32_t>(4);
+  p.chunk_off        = chunk_off;
+  p.plan             = plan;
+  p.ticket           = reinterpret_cast<unsigned int*>(plan + 2);
+  p.out              = lv.out;
+
+  const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
+  p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
+  const size_t smem    = smem_path ? static_cast<size_t>(p.mb) * kGroup * 8 + kStageRows * sizeof(int4) : 0;
+  int blocks_per_sm    = smem_path ? static_cast<int>((ctx->max_smem_optin) / (smem + 1024)) : 8;
+  if (blocks_per_sm > 8) blocks_per_sm = 8;
+  if (blocks_per_sm < 1) blocks_per_sm = 1;
+  const int grid = ctx->sm_count * blocks_per_sm;
+
+  k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, p.G * p.K, grid * 2, chunk_off, plan, p.ticket);
+  LBK_LAUNCH_CHECK();
+
+#define LBK_HIST_LAUNCH(BinT, FL, SM)                                                                              \
+  do {                                                                                                             \
+    if (smem > 48 * 1024)                                                                                          \
+      LBK_CUDA(cudaFuncSetAttribute(k_hist<BinT, FL, SM>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                                    static_cast<int>(smem)));                                                      \
+    k_hist<BinT, FL, SM><<<grid, kHistThreads, smem, stream>>>(p);                                                 \
+  } while (0)
+  if (smem_path) {
+    if (lv.float_mode) LBK_HIST_LAUNCH(uint8_t, true, true); else LBK_HIST_LAUNCH(uint8_t, false, true);
+  } else if (lv.bin_bytes == 1) {
+    if (lv.float_mode) LBK_HIST_LAUNCH(uint8_t, true, false); else LBK_HIST_LAUNCH(uint8_t, false, false);
+  } else {
+    if (lv.float_mode) LBK_HIST_LAUNCH(uint16_t, true, false); else LBK_HIST_LAUNCH(uint16_t, false, false);
+  }
+#undef LBK_HIST_LAUNCH
+  LBK_LAUNCH_CHECK();
+}
+
+void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t n_rows, int node_begin,
+               int n_nodes, int32_t* row_index, int32_t* seg, cudaStream_t stream)
+{
+  LBK_EXPECT(n_nodes >= 1 && n_nodes <= 8192, "group_rows supports 1..8192 nodes");
+  const int64_t n_blocks = (n_rows + kGroupTile - 1) / kGroupTile;
+  if (n_blocks == 0) {
+    LBK_CUDA(cudaMemsetAsync(seg, 0, sizeof(int32_t) * (n_nodes + 1), stream));
+    return;
+  }
+  int32_t* counts   = s.alloc<int32_t>(static_cast<size_t>(n_blocks) * n_nodes);
+  const size_t smem = sizeof(int) * n_nodes;
+  k_group_count<<<static_cast<unsigned>(n_blocks), 256, smem, stream>>>(node_of_row, n_rows, node_begin, n_nodes, counts);
+  LBK_LAUNCH_CHECK();
+  k_group_scan<<<1, 1024, smem, stream>>>(counts, static_cast<int>(n_blocks), n_nodes, seg);
+  LBK_LAUNCH_CHECK();
+  k_group_scatter<<<static_cast<unsigned>(n_blocks), 32, smem, stream>>>(node_of_row, n_rows, node_begin, n_nodes, counts,
+                                                                         row_index);
+  LBK_LAUNCH_CHECK();
+  (void)ctx;
+}
+
+}  // namespace lbk

@@ -1,0 +1,195 @@
+// Internal declarations shared by the translation units of liblbk.so.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <functional>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "lbk.h"
+
+namespace lbk {
+
+struct Error : public std::runtime_error {
+  int code;
+  Error(int c, const std::string& m) : std::runtime_error(m), code(c) {}
+};
+
+#define LBK_CUDA(call)                                                                        \
+  do {                                                                                        \
+    cudaError_t e_ = (call);                                                                  \
+    if (e_ != cudaSuccess) {                                                                  \
+      throw ::lbk::Error(LBK_ERR_CUDA, std::string(__FILE__) + ":" + std::to_string(__LINE__) + \
+                                         ": " #call ": " + cudaGetErrorString(e_));           \
+    }                                                                                         \
+  } while (0)
+
+#define LBK_EXPECT(cond, msg)                                                                 \
+  do {                                                                                        \
+    if (!(cond)) {                                                                            \
+      throw ::lbk::Error(LBK_ERR_ARGUMENT, std::string(__FILE__) + ":" + std::to_string(__LINE__) + \
+                                             ": " + (msg));                                   \
+    }                                                                                         \
+  } while (0)
+
+#define LBK_LAUNCH_CHECK() LBK_CUDA(cudaGetLastError())
+
+// 16-byte (grad, hess) pairs
+struct GPairI64 {
+  long long grad, hess;
+};
+struct GPairF64 {
+  double grad, hess;
+};
+
+// Quantiser parameters, device resident (reference: GradientQuantiser, build_tree.cu:51-104)
+struct QuantParams {
+  double scale_g, scale_h, inv_g, inv_h;
+};
+
+inline int LevelBegin(int level) { return (1 << level) - 1; }
+inline int LevelEnd(int level) { return (1 << (level + 1)) - 1; }
+
+constexpr int kGroup = 32;  // features per feature group (one lane per feature)
+
+}  // namespace lbk
+
+// The context is an opaque C struct for callers.
+struct lbk_context {
+  int device        = 0;
+  int sm_count      = 0;
+  int max_smem_optin = 0;
+  cudaMemPool_t pool = nullptr;
+  std::string err;
+  // device status word: 0 = ok, otherwise a kernel wrote a fault code
+  int* d_status = nullptr;
+  // communicator
+  int rank = 0, n_ranks = 1;
+  void* nccl_comm     = nullptr;
+  bool owns_nccl      = false;
+  lbk_allreduce_fn cb = nullptr;
+  void* cb_user       = nullptr;
+};
+
+namespace lbk {
+
+// Stream-ordered scratch allocation from the context's pool (replaces legate::create_buffer).
+class Scratch {
+ public:
+  Scratch(lbk_context* ctx, cudaStream_t stream) : ctx_(ctx), stream_(stream) {}
+  ~Scratch();
+  Scratch(const Scratch&)            = delete;
+  Scratch& operator=(const Scratch&) = delete;
+  void* alloc_bytes(size_t bytes);
+  template <typename T>
+  T* alloc(size_t n)
+  {
+    return static_cast<T*>(alloc_bytes(sizeof(T) * (n > 0 ? n : 1)));
+  }
+  void free_one(void* p);
+
+ private:
+  lbk_context* ctx_;
+  cudaStream_t stream_;
+  std::vector<void*> ptrs_;
+};
+
+// In-place all-reduce over the context's communicator; no-op for a single rank.
+void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream);
+// Reads the device status word (synchronises the stream) and throws LBK_ERR_DEVICE if set.
+void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream);
+
+// Runs f, turning exceptions into a status code and an error text (the ABI boundary).
+int Guard(lbk_context* ctx, const std::function<void()>& f);
+
+// ---- stage launchers (defined in the .cu files named in the comments) ------------------------
+// proposals.cu
+struct ProposalInfo {
+  int total_bins;            // B
+  int max_bins_per_feature;  // largest feature
+};
+template <typename T>
+ProposalInfo SplitProposals(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_t row_offset,
+                            int64_t n_local, int F, int S, int seed, int64_t dataset_rows, T* proposals,
+                            int32_t* row_ptr, cudaStream_t stream);  // synchronises the stream
+template <typename T>
+void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposals, const int32_t* row_ptr,
+               void* bins, int bin_bytes, int max_bins_per_feature, cudaStream_t stream);
+// quantise.cu
+void Quantise(lbk_context* ctx, Scratch& s, const double* g, const double* h, int64_t ldg, int64_t row_offset,
+              int64_t n_local, int K, int seed, int2* gpair, GPairI64* root_sums, QuantParams* params,
+              cudaStream_t stream);
+// histogram.cu
+struct HistLevel {
+  const void* bins;
+  int bin_bytes;
+  int64_t n_rows;      // rows of the bin matrix (local rows)
+  int F, K, B;
+  int max_bins_per_feature;
+  const int32_t* row_ptr;
+  const int2* gpair;       // int path
+  const float2* gpair_f;   // float path
+  const int32_t* row_index;
+  const int32_t* seg;      // [n_level_nodes+1] offsets for nodes node_begin.. of the level range
+  int n_nodes;             // nodes in this batch
+  int seg_node_offset;     // index into seg of the batch's first node
+  // built-node selection: slot_of_node[j] = slot in `out` for node j of the batch, or -1
+  const int32_t* slot_of_node;
+  void* out;               // [n_slots, K, B] pairs (int64 or double), already zeroed
+  bool float_mode;
+};
+void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStream_t stream);
+void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t n_rows, int node_begin,
+               int n_nodes, int32_t* row_index, int32_t* seg, cudaStream_t stream);
+// split.cu
+struct TreeArrays {
+  double* leaf_value;
+  int32_t* feature;
+  double* split_value;
+  double* gain;
+  GPairI64* node_sums;
+  int32_t* split_bin;  // feature-relative bin of the chosen split, per node
+  int max_nodes;
+};
+struct SplitParams {
+  double l1, l2, min_split_gain;
+  const uint8_t* feature_set;
+};
+// Decide which nodes of the batch are built: slot_of_node[j] (>=0 built, -1 derived/none).
+void PlanBuilt(const GPairI64* node_sums, int K, int node_begin, int n_nodes, bool parent_available,
+               int32_t* slot_of_node, cudaStream_t stream);
+// Scan built histograms into the level histogram, derive siblings from the parent.
+void ScanLevel(const GPairI64* built, const int32_t* slot_of_node, GPairI64* level_hist /* node_begin based */,
+               const GPairI64* parent_hist /* level above, may be null */, int parent_begin,
+               const GPairI64* node_sums, int node_begin, int n_nodes, int K, int F, int B,
+               const int32_t* row_ptr, bool parent_available, cudaStream_t stream);
+template <typename T>
+void BestSplit(const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B,
+               const int32_t* row_ptr, const T* proposals, const QuantParams* qp, const SplitParams& sp,
+               TreeArrays tree, cudaStream_t stream);
+void RootLeaf(TreeArrays tree, int K, const QuantParams* qp, double l1, double l2, cudaStream_t stream);
+void WriteHessian(const GPairI64* node_sums, const QuantParams* qp, double* hessian, int64_t n, cudaStream_t stream);
+// partition.cu
+struct PartitionLevel {
+  const void* bins;
+  int bin_bytes;
+  int64_t n_rows;
+  const int32_t* row_index_in;
+  const int32_t* seg_in;  // [n_nodes+1] for the level
+  int32_t* row_index_out;
+  int32_t* seg_out;       // [2*n_nodes+1] for the next level
+  int node_begin, n_nodes;
+  const int32_t* feature;
+  const int32_t* split_bin;
+};
+void PartitionRows(lbk_context* ctx, Scratch& s, const PartitionLevel& pl, cudaStream_t stream);
+void InitRows(int32_t* row_index, int32_t* seg, int64_t n_rows, cudaStream_t stream);
+// predict.cu
+template <typename T>
+void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
+                   const double* const* leaf, const int32_t* const* feat, const double* const* split,
+                   const int32_t* max_nodes, double* pred, int64_t ldp, cudaStream_t stream);
+
+}  // namespace lbk

@@ -1,0 +1,296 @@
+// Split proposals and the binned matrix.
+//
+// Reference behaviour restated here:
+//   SelectSplitSamples  src/models/tree/build_tree.cu:867-964 - draw split_samples row ids from
+//     the seed, gather those rows (zeros where another rank owns the row), sum over ranks, keep
+//     the sorted unique values per feature as a CSR, overwrite each feature's largest value
+//     with +inf.
+//   FindBin             src/models/tree/build_tree.h:178-185 - bin = first proposal >= x.
+// The reference re-runs the search for every element on every tree level; here it runs once per
+// tree and the result is kept as one byte (or two) per element, grouped 32 features at a time
+// so that a warp reads one 32-byte sector per row with one lane per feature.
+#include <cfloat>
+#include <cmath>
+#include <limits>
+
+#include "device_utils.cuh"
+#include "internal.h"
+
+namespace lbk {
+namespace {
+
+constexpr int kSortThreads = 256;
+
+template <typename T>
+__global__ void k_gather_samples(const T* __restrict__ X, int64_t ldx, int64_t row_offset, int64_t n_local,
+                                 int F, int S, int seed, int64_t dataset_rows, T* __restrict__ draft)
+{
+  // draft is feature-major [F][S]
+  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (idx >= static_cast<int64_t>(F) * S) return;
+  const int i = static_cast<int>(idx / F);
+  const int f = static_cast<int>(idx % F);
+  MinStd eng(static_cast<uint32_t>(seed));
+  eng.discard(static_cast<unsigned long long>(i));
+  const long long row = eng.uniform_int(0, dataset_rows - 1);
+  const bool has      = row >= row_offset && row < row_offset + n_local;
+  draft[static_cast<int64_t>(f) * S + i] = has ? X[(row - row_offset) * ldx + f] : T(0);
+}
+
+// One block per feature: bitonic sort of the S samples in shared memory, then unique.
+template <typename T>
+__global__ void __launch_bounds__(kSortThreads)
+  k_sort_unique(const T* __restrict__ draft, int S, int S_pad, T* __restrict__ uniq, int32_t* __restrict__ counts)
+{
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* vals        = reinterpret_cast<T*>(smem_raw);
+  int* scan_tmp  = reinterpret_cast<int*>(vals + S_pad);
+  const int f    = blockIdx.x;
+  const int tid  = threadIdx.x;
+  for (int i = tid; i < S_pad; i += kSortThreads)
+    vals[i] = i < S ? draft[static_cast<int64_t>(f) * S + i] : static_cast<T>(INFINITY);
+  __syncthreads();
+  for (int k = 2; k <= S_pad; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = tid; i < S_pad; i += kSortThreads) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const T a = vals[i], b = vals[ixj];
+          const bool up = (i & k) == 0;
+          if (up ? (b < a) : (a < b)) {
+            vals[i]   = b;
+            vals[ixj] = a;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  // unique over the first S sorted entries; each thread owns a contiguous run
+  const int per   = (S + kSortThreads - 1) / kSortThreads;
+  const int begin = min(tid * per, S), end = min(begin + per, S);
+  int local = 0;
+  for (int i = begin; i < end; ++i) local += (i == 0 || vals[i] != vals[i - 1]) ? 1 : 0;
+  scan_tmp[tid] = local;
+  __syncthreads();
+  // exclusive scan of 256 counts by a single warp (8 per lane)
+  if (tid < 32) {
+    int v[kSortThreads / 32];
+    int sum = 0;
+#pragma unroll
+    for (int j = 0; j < kSortThreads / 32; ++j) {
+      v[j] = scan_tmp[tid * (kSortThreads / 32) + j];
+      sum += v[j];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, incl, off);
+      if (tid >= off) incl += n;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int j = 0; j < kSortThreads / 32; ++j) {
+      scan_tmp[tid * (kSortThreads / 32) + j] = run;
+      run += v[j];
+    }
+    if (tid == 31) counts[f] = incl;
+  }
+  __syncthreads();
+  int pos = scan_tmp[tid];
+  for (int i = begin; i < end; ++i) {
+    if (i == 0 || vals[i] != vals[i - 1]) uniq[static_cast<int64_t>(f) * S + pos++] = vals[i];
+  }
+}
+
+// row_ptr = exclusive scan of counts (single block)
+__global__ void k_scan_counts(const int32_t* __restrict__ counts, int F, int32_t* __restrict__ row_ptr,
+                              int32_t* __restrict__ max_bins)
+{
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  __shared__ int max_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    carry_s = 0;
+    max_s   = 0;
+    row_ptr[0] = 0;
+  }
+  __syncthreads();
+  for (int base = 0; base < F; base += blockDim.x) {
+    const int i = base + tid;
+    const int c = i < F ? counts[i] : 0;
+    int incl    = c;
+    for (int off = 1; off < 32; off <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += n;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    atomicMax(&max_s, c);
+    __syncthreads();
+    if (warp == 0) {
+      int w = lane < (blockDim.x >> 5) ? warp_sums[lane] : 0;
+      int wi = w;
+      for (int off = 1; off < 32; off <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, wi, off);
+        if (lane >= off) wi += n;
+      }
+      warp_sums[lane] = wi - w;  // exclusive
+    }
+    __syncthreads();
+    const int total_before = carry_s + warp_sums[warp];
+    if (i < F) row_ptr[i + 1] = total_before + incl;
+    __syncthreads();
+    if (tid == blockDim.x - 1) carry_s = total_before + incl;
+    __syncthreads();
+  }
+  if (tid == 0) *max_bins = max_s;
+}
+
+template <typename T>
+__global__ void k_write_proposals(const T* __restrict__ uniq, int S, const int32_t* __restrict__ row_ptr,
+                                  T* __restrict__ proposals)
+{
+  const int f     = blockIdx.x;
+  const int begin = row_ptr[f], end = row_ptr[f + 1];
+  for (int j = threadIdx.x; j < end - begin; j += blockDim.x) {
+    T v = uniq[static_cast<int64_t>(f) * S + j];
+    if (j == end - begin - 1) v = static_cast<T>(INFINITY);
+    proposals[begin + j] = v;
+  }
+}
+
+// One warp per row, one lane per feature of the group.  The group's slice of the proposal
+// CSR sits in shared memory when it fits.
+template <typename T, typename BinT, bool kUseSmem>
+__global__ void __launch_bounds__(256)
+  k_bin(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, const T* __restrict__ proposals,
+        const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins)
+{
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* sp           = reinterpret_cast<T*>(smem_raw);
+  const int g     = blockIdx.y;
+  const int f0    = g * kGroup;
+  const int lane  = threadIdx.x & 31;
+  const int f     = f0 + lane;
+  const int fend  = min(F, f0 + kGroup);
+  const int gbase = row_ptr[f0];
+  if (kUseSmem) {
+    const int gcount = row_ptr[fend] - gbase;
+    for (int i = threadIdx.x; i < gcount; i += blockDim.x) sp[i] = proposals[gbase + i];
+    __syncthreads();
+  }
+  const bool active = f < F;
+  int begin = 0, n = 0;
+  if (active) {
+    begin = row_ptr[f];
+    n     = row_ptr[f + 1] - begin;
+  }
+  const T* p = kUseSmem ? sp + (begin - gbase) : proposals + begin;
+  BinT* out  = bins + static_cast<int64_t>(g) * n_rows * kGroup;
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5); row < n_rows;
+       row += warps_total) {
+    int bin = 0;
+    if (active) {
+      const T x = X[row * ldx + f];
+      int len = n, base = 0;
+      while (len > 1) {
+        const int half = len >> 1;
+        base           = (p[base + half] < x) ? base + half : base;
+        len -= half;
+      }
+      bin = base + ((p[base] < x) ? 1 : 0);
+    }
+    out[row * kGroup + lane] = static_cast<BinT>(bin);
+  }
+}
+
+int NextPow2(int v)
+{
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+}  // namespace
+
+template <typename T>
+ProposalInfo SplitProposals(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_t row_offset, int64_t n_local,
+                   int F, int S, int seed, int64_t dataset_rows, T* proposals, int32_t* row_ptr,
+                   cudaStream_t stream)
+{
+  const int64_t FS = static_cast<int64_t>(F) * S;
+  T* draft         = s.alloc<T>(FS);
+  T* uniq          = s.alloc<T>(FS);
+  int32_t* counts  = s.alloc<int32_t>(F + 1);
+  {
+    const int threads = 256;
+    const int64_t blocks = (FS + threads - 1) / threads;
+    k_gather_samples<T><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(X, ldx, row_offset, n_local, F, S, seed,
+                                                                               dataset_rows, draft);
+    LBK_LAUNCH_CHECK();
+  }
+  AllReduce(ctx, draft, static_cast<size_t>(FS), sizeof(T) == 4 ? LBK_F32 : LBK_F64, LBK_SUM, stream);
+  const int S_pad   = NextPow2(S);
+  const size_t smem = sizeof(T) * S_pad + sizeof(int) * kSortThreads;
+  k_sort_unique<T><<<F, kSortThreads, smem, stream>>>(draft, S, S_pad, uniq, counts);
+  LBK_LAUNCH_CHECK();
+  k_scan_counts<<<1, 1024, 0, stream>>>(counts, F, row_ptr, counts + F);
+  LBK_LAUNCH_CHECK();
+  k_write_proposals<T><<<F, 128, 0, stream>>>(uniq, S, row_ptr, proposals);
+  LBK_LAUNCH_CHECK();
+  int32_t h[2] = {0, 0};
+  LBK_CUDA(cudaMemcpyAsync(&h[0], row_ptr + F, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  LBK_CUDA(cudaMemcpyAsync(&h[1], counts + F, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  LBK_CUDA(cudaStreamSynchronize(stream));
+  s.free_one(draft);
+  s.free_one(uniq);
+  return ProposalInfo{h[0], h[1]};
+}
+
+template <typename T>
+void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposals, const int32_t* row_ptr,
+               void* bins, int bin_bytes, int max_bins_per_feature, cudaStream_t stream)
+{
+  if (n_rows <= 0) return;
+  const int G           = (F + kGroup - 1) / kGroup;
+  const size_t smem     = sizeof(T) * static_cast<size_t>(kGroup) * max_bins_per_feature;
+  const bool use_smem   = smem <= 96 * 1024;
+  const int warps_per_b = 8;
+  int64_t blocks_x      = (n_rows + warps_per_b * 8 - 1) / (warps_per_b * 8);  // ~8 rows per warp
+  if (blocks_x > 65535 * 16) blocks_x = 65535 * 16;
+  if (blocks_x < 1) blocks_x = 1;
+  dim3 grid(static_cast<unsigned>(blocks_x), G);
+#define LBK_BIN_LAUNCH(BinT)                                                                              \
+  do {                                                                                                    \
+    if (use_smem) {                                                                                       \
+      if (smem > 48 * 1024)                                                                               \
+        LBK_CUDA(cudaFuncSetAttribute(k_bin<T, BinT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                      static_cast<int>(smem)));                                           \
+      k_bin<T, BinT, true><<<grid, 256, smem, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,           \
+                                                         static_cast<BinT*>(bins));                       \
+    } else {                                                                                              \
+      k_bin<T, BinT, false><<<grid, 256, 0, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,             \
+                                                       static_cast<BinT*>(bins));                         \
+    }                                                                                                     \
+  } while (0)
+  if (bin_bytes == 1) {
+    LBK_BIN_LAUNCH(uint8_t);
+  } else {
+    LBK_BIN_LAUNCH(uint16_t);
+  }
+#undef LBK_BIN_LAUNCH
+  LBK_LAUNCH_CHECK();
+}
+
+template ProposalInfo SplitProposals<float>(lbk_context*, Scratch&, const float*, int64_t, int64_t, int64_t, int, int, int,
+                                   int64_t, float*, int32_t*, cudaStream_t);
+template ProposalInfo SplitProposals<double>(lbk_context*, Scratch&, const double*, int64_t, int64_t, int64_t, int, int, int,
+                                    int64_t, double*, int32_t*, cudaStream_t);
+template void BinMatrix<float>(const float*, int64_t, int64_t, int, const float*, const int32_t*, void*, int, int,
+                               cudaStream_t);
+template void BinMatrix<double>(const double*, int64_t, int64_t, int, const double*, const int32_t*, void*, int, int,
+                                cudaStream_t);
+
+}  // namespace lbk

@@ -1,0 +1,186 @@
+// Gradient quantiser: scale from the local |g|,|h| sums, one stochastic-rounded int32 pair per
+// (row, output), and the root node sums.
+//
+// Reference behaviour restated here:
+//   GradientQuantiser ctor   src/models/tree/build_tree.cu:69-104  - scale = INT32_MAX / max over
+//     ranks of the local sum of |g| (resp. |h|), 1 if that sum is 0.
+//   QuantiseStochasticRounding  :112-129, hash_combine :143-165.
+//   reduce_base_sums            :168-204 - node_sums[0,k] = sum of the quantised pairs.
+// The reference recomputes the quantised pair of a row for every feature group on every level;
+// its value depends only on (seed, global row, output), so it is computed once here.
+//
+// Order of the floating-point |g| sum (the reference leaves it to thrust::reduce): blocks of
+// 4096 elements; thread t of 256 adds elements t, t+256, ... in order; groups of 32 threads fold
+// with offsets 16,8,4,2,1; the 8 group sums are added left to right; block sums are reduced the
+// same way until one value is left.  The CPU oracle uses the same order.
+#include "device_utils.cuh"
+#include "internal.h"
+
+namespace lbk {
+namespace {
+
+constexpr int kSumThreads = 256;
+constexpr int kSumItems   = 16;
+constexpr int kSumBlock   = kSumThreads * kSumItems;  // 4096
+
+// level 0 reads |g|,|h| from the strided [n_rows, K] inputs; higher levels read partial sums
+template <bool kFirst>
+__global__ void __launch_bounds__(kSumThreads)
+  k_abs_sum(const double* __restrict__ g, const double* __restrict__ h, int64_t ldg, int K, int64_t n,
+            double* __restrict__ out_g, double* __restrict__ out_h)
+{
+  __shared__ double wg[kSumThreads / 32], wh[kSumThreads / 32];
+  const int tid      = threadIdx.x;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kSumBlock;
+  double sg = 0.0, sh = 0.0;
+#pragma unroll
+  for (int j = 0; j < kSumItems; ++j) {
+    const int64_t idx = base + static_cast<int64_t>(j) * kSumThreads + tid;
+    double vg = 0.0, vh = 0.0;
+    if (idx < n) {
+      if (kFirst) {
+        const int64_t row = idx / K;
+        const int k       = static_cast<int>(idx - row * K);
+        vg                = fabs(g[row * ldg + k]);
+        vh                = fabs(h[row * ldg + k]);
+      } else {
+        vg = g[idx];
+        vh = h[idx];
+      }
+    }
+    sg += vg;
+    sh += vh;
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    sg += __shfl_down_sync(0xffffffffu, sg, off);
+    sh += __shfl_down_sync(0xffffffffu, sh, off);
+  }
+  if ((tid & 31) == 0) {
+    wg[tid >> 5] = sg;
+    wh[tid >> 5] = sh;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    double tg = wg[0], th = wh[0];
+#pragma unroll
+    for (int w = 1; w < kSumThreads / 32; ++w) {
+      tg += wg[w];
+      th += wh[w];
+    }
+    out_g[blockIdx.x] = tg;
+    out_h[blockIdx.x] = th;
+  }
+}
+
+__global__ void k_make_scale(const double* __restrict__ sums /* g,h */, QuantParams* __restrict__ qp)
+{
+  const double max_int = 2147483647.0;
+  const double sg = sums[0], sh = sums[1];
+  QuantParams p;
+  p.scale_g = sg == 0 ? 1.0 : max_int / sg;
+  p.scale_h = sh == 0 ? 1.0 : max_int / sh;
+  p.inv_g   = 1.0 / p.scale_g;
+  p.inv_h   = 1.0 / p.scale_h;
+  *qp       = p;
+}
+
+// One thread per row, looping over outputs; per-output block sums go to node_sums[0,k] with one
+// 64-bit atomic pair per block and output.  Blocks walk the rows with a grid stride so that
+// the number of atomics stays small.
+__global__ void __launch_bounds__(256)
+  k_quantise(const double* __restrict__ g, const double* __restrict__ h, int64_t ldg, int64_t row_offset,
+             int64_t n_local, int K, long long seed, const QuantParams* __restrict__ qp_ptr,
+             int2* __restrict__ gpair, GPairI64* __restrict__ root_sums)
+{
+  __shared__ long long red[2][8];
+  const QuantParams qp = *qp_ptr;
+  const int tid        = threadIdx.x;
+  for (int k = 0; k < K; ++k) {
+    long long sg = 0, sh = 0;
+    for (int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x) + tid; row < n_local;
+         row += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const double gv = g[row * ldg + k];
+      const double hv = h[row * ldg + k];
+      const int2 q    = QuantisePair(gv, hv, qp, HashCombine(seed, row_offset + row, k));
+      gpair[row * K + k] = q;
+      sg += q.x;
+      sh += q.y;
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      sg += __shfl_down_sync(0xffffffffu, sg, off);
+      sh += __shfl_down_sync(0xffffffffu, sh, off);
+    }
+    if ((tid & 31) == 0) {
+      red[0][tid >> 5] = sg;
+      red[1][tid >> 5] = sh;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      long long tg = 0, th = 0;
+      for (int w = 0; w < 8; ++w) {
+        tg += red[0][w];
+        th += red[1][w];
+      }
+      atomicAdd(reinterpret_cast<unsigned long long*>(&root_sums[k].grad), static_cast<unsigned long long>(tg));
+      atomicAdd(reinterpret_cast<unsigned long long*>(&root_sums[k].hess), static_cast<unsigned long long>(th));
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+void Quantise(lbk_context* ctx, Scratch& s, const double* g, const double* h, int64_t ldg, int64_t row_offset,
+              int64_t n_local, int K, int seed, int2* gpair, GPairI64* root_sums, QuantParams* params,
+              cudaStream_t stream)
+{
+  // canonical |g|,|h| sums
+  int64_t n        = n_local * K;
+  double* sums     = s.alloc<double>(2);
+  if (n == 0) {
+    LBK_CUDA(cudaMemsetAsync(sums, 0, 2 * sizeof(double), stream));
+  } else {
+    const double* in_g = g;
+    const double* in_h = h;
+    bool first         = true;
+    while (true) {
+      const int64_t nblocks = (n + kSumBlock - 1) / kSumBlock;
+      double* out_g;
+      double* out_h;
+      if (nblocks == 1) {
+        out_g = sums;
+        out_h = sums + 1;
+      } else {
+        out_g = s.alloc<double>(nblocks);
+        out_h = s.alloc<double>(nblocks);
+      }
+      if (first)
+        k_abs_sum<true><<<static_cast<unsigned>(nblocks), kSumThreads, 0, stream>>>(in_g, in_h, ldg, K, n, out_g, out_h);
+      else
+        k_abs_sum<false><<<static_cast<unsigned>(nblocks), kSumThreads, 0, stream>>>(in_g, in_h, 0, 1, n, out_g, out_h);
+      LBK_LAUNCH_CHECK();
+      if (nblocks == 1) break;
+      in_g  = out_g;
+      in_h  = out_h;
+      n     = nblocks;
+      first = false;
+    }
+  }
+  AllReduce(ctx, sums, 2, LBK_F64, LBK_MAX, stream);
+  k_make_scale<<<1, 1, 0, stream>>>(sums, params);
+  LBK_LAUNCH_CHECK();
+  LBK_CUDA(cudaMemsetAsync(root_sums, 0, sizeof(GPairI64) * K, stream));
+  if (n_local > 0) {
+    int64_t blocks = (n_local + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(ctx->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    k_quantise<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(g, h, ldg, row_offset, n_local, K,
+                                                                  static_cast<long long>(seed), params, gpair, root_sums);
+    LBK_LAUNCH_CHECK();
+  }
+  AllReduce(ctx, root_sums, static_cast<size_t>(2) * K, LBK_I64, LBK_SUM, stream);
+}
+
+}  // namespace lbk

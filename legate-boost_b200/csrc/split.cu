@@ -1,0 +1,272 @@
+// Node selection, prefix scan with sibling subtraction, and split evaluation.
+//
+// Reference behaviour restated here (src/models/tree/):
+//   SelectHistogramNode / ComputeHistogramBin  build_tree.h:80-104 - only the child with the
+//     smaller quantised hessian of output 0 is built (ties: the right child) when the parent's
+//     histogram is available;
+//   scan_kernel        build_tree.cu:597-668 - inclusive prefix over the bins of each feature; the
+//     prefix replaces the bin value only if prefix.grad > 0 or prefix.hess > 0; then
+//     sibling = parent - node;
+//   perform_best_split build_tree.cu:682-782 - gain of every bin summed over outputs in float64 on
+//     dequantised sums, zero if any output has a non-positive hessian on either side, accept if
+//     the best gain exceeds 1e-5.  Ties: the reference keeps, per thread t = bin mod 512, the
+//     first strict maximum and reduces with op(a,b) = a.gain > b.gain ? a : b where a always
+//     comes from lower thread ids, so equal gains resolve to the largest (bin mod 512) and then
+//     the smallest bin.  That total order is applied here, independent of the reduction shape.
+// Compiled with -fmad=false.
+#include "device_utils.cuh"
+#include "internal.h"
+
+namespace lbk {
+namespace {
+
+__global__ void k_plan_built(const GPairI64* __restrict__ node_sums, int K, int node_begin, int n_nodes,
+                             bool parent_available, int32_t* __restrict__ slot_of_node)
+{
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= n_nodes) return;
+  const int node = node_begin + j;
+  int slot;
+  if (node == 0) {
+    slot = 0;
+  } else if (!parent_available) {
+    slot = j;
+  } else {
+    const int parent = (node - 1) / 2;
+    const int l = 2 * parent + 1, r = 2 * parent + 2;
+    const int hist_node =
+      (node_sums[static_cast<int64_t>(l) * K].hess < node_sums[static_cast<int64_t>(r) * K].hess) ? l : r;
+    slot = hist_node == node ? j / 2 : -1;
+  }
+  slot_of_node[j] = slot;
+}
+
+// One warp per (node, feature); blockIdx.y = output.
+__global__ void __launch_bounds__(256)
+  k_scan(const GPairI64* __restrict__ built, const int32_t* __restrict__ slot_of_node,
+         GPairI64* __restrict__ level_hist, const GPairI64* __restrict__ parent_hist, int parent_begin,
+         const GPairI64* __restrict__ node_sums, int node_begin, int n_nodes, int K, int F, int B,
+         const int32_t* __restrict__ row_ptr, bool parent_available)
+{
+  const int lane    = threadIdx.x & 31;
+  const int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (wid >= static_cast<int64_t>(n_nodes) * F) return;
+  const int j    = static_cast<int>(wid / F);
+  const int f    = static_cast<int>(wid % F);
+  const int k    = blockIdx.y;
+  const int node = node_begin + j;
+  const int slot = slot_of_node[j];
+  if (slot < 0) return;
+  const GPairI64* src = built + (static_cast<int64_t>(slot) * K + k) * B;
+  GPairI64* dst       = level_hist + (static_cast<int64_t>(j) * K + k) * B;
+  const int fb = row_ptr[f], fe = row_ptr[f + 1];
+  if (node_sums[static_cast<int64_t>(node) * K + k].hess <= 0) {
+    // not scanned: the raw values stay, no sibling is derived
+    if (src != dst)
+      for (int b = fb + lane; b < fe; b += 32) StorePair(dst + b, LoadPair(src + b));
+    return;
+  }
+  const bool derive = node != 0 && parent_available;
+  GPairI64* sib     = nullptr;
+  const GPairI64* par = nullptr;
+  if (derive) {
+    const int js = j ^ 1;  // a level starts at an odd heap index: j even = left child
+    sib          = level_hist + (static_cast<int64_t>(js) * K + k) * B;
+    par          = parent_hist + (static_cast<int64_t>((node - 1) / 2 - parent_begin) * K + k) * B;
+  }
+  long long agg_g = 0, agg_h = 0;
+  for (int base = fb; base < fe; base += 32) {
+    const int b     = base + lane;
+    const bool part = b < fe;
+    GPairI64 raw{0, 0};
+    if (part) raw = LoadPair(src + b);
+    long long sg = raw.grad, sh = raw.hess;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const long long ng = __shfl_up_sync(0xffffffffu, sg, off);
+      const long long nh = __shfl_up_sync(0xffffffffu, sh, off);
+      if (lane >= off) {
+        sg += ng;
+        sh += nh;
+      }
+    }
+    const long long tile_g = __shfl_sync(0xffffffffu, sg, 31);
+    const long long tile_h = __shfl_sync(0xffffffffu, sh, 31);
+    sg += agg_g;
+    sh += agg_h;
+    if (part) {
+      const GPairI64 v = (sg > 0 || sh > 0) ? GPairI64{sg, sh} : raw;
+      StorePair(dst + b, v);
+      if (derive) {
+        const GPairI64 pv = LoadPair(par + b);
+        StorePair(sib + b, GPairI64{pv.grad - v.grad, pv.hess - v.hess});
+      }
+    }
+    agg_g += tile_g;
+    agg_h += tile_h;
+  }
+}
+
+struct Cand {
+  double gain;
+  int bin;
+};
+__device__ inline bool Better(const Cand& a, const Cand& b)
+{
+  if (a.gain > b.gain) return true;
+  if (a.gain < b.gain) return false;
+  if (a.bin < 0 || b.bin < 0) return b.bin < 0 && a.bin >= 0;
+  const int ta = a.bin & 511, tb = b.bin & 511;
+  if (ta != tb) return ta > tb;
+  return a.bin < b.bin;
+}
+
+constexpr int kSplitThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kSplitThreads)
+  k_best_split(const GPairI64* __restrict__ level_hist, int node_begin, int K, int F, int B,
+               const int32_t* __restrict__ row_ptr, const T* __restrict__ proposals,
+               const QuantParams* __restrict__ qp_ptr, double l1, double l2, double msg,
+               const uint8_t* __restrict__ feature_set, TreeArrays tree)
+{
+  const int j    = blockIdx.x;
+  const int node = node_begin + j;
+  GPairI64* node_sums = tree.node_sums;
+  if (LoadPair(node_sums + static_cast<int64_t>(node) * K).hess <= 0) return;
+  const QuantParams qp = *qp_ptr;
+  const GPairI64* hist = level_hist + static_cast<int64_t>(j) * K * B;
+  __shared__ Cand s_c[kSplitThreads / 32];
+  __shared__ Cand s_best;
+  const int tid = threadIdx.x;
+  Cand best{0.0, -1};
+  for (int b = tid; b < B; b += kSplitThreads) {
+    if (feature_set) {
+      int lo = 0, hi = F;  // last f with row_ptr[f] <= b
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (row_ptr[mid] <= b) lo = mid; else hi = mid;
+      }
+      if (!feature_set[lo]) continue;
+    }
+    double gain = 0;
+    for (int k = 0; k < K; ++k) {
+      const GPairI64 ns = LoadPair(node_sums + static_cast<int64_t>(node) * K + k);
+      const GPairI64 ls = LoadPair(hist + static_cast<int64_t>(k) * B + b);
+      const GPairI64 rs{ns.grad - ls.grad, ns.hess - ls.hess};
+      if (ls.hess <= 0 || rs.hess <= 0) {
+        gain = 0;
+        break;
+      }
+      gain += CalculateGain(Dequantise(ls, qp), Dequantise(rs, qp), Dequantise(ns, qp), l1, l2, msg);
+    }
+    const Cand c{gain, b};
+    if (gain > 0 && Better(c, best)) best = c;
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    Cand o;
+    o.gain = __shfl_down_sync(0xffffffffu, best.gain, off);
+    o.bin  = __shfl_down_sync(0xffffffffu, best.bin, off);
+    if (Better(o, best)) best = o;
+  }
+  if ((tid & 31) == 0) s_c[tid >> 5] = best;
+  __syncthreads();
+  if (tid == 0) {
+    Cand b0 = s_c[0];
+    for (int w = 1; w < kSplitThreads / 32; ++w)
+      if (Better(s_c[w], b0)) b0 = s_c[w];
+    s_best = b0;
+  }
+  __syncthreads();
+  const Cand nb = s_best;
+  if (!(nb.gain > 1e-5)) return;
+  int lo = 0, hi = F;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (row_ptr[mid] <= nb.bin) lo = mid; else hi = mid;
+  }
+  const int bf = lo;
+  const int l = 2 * node + 1, r = 2 * node + 2;
+  for (int k = tid; k < K; k += kSplitThreads) {
+    const GPairI64 ns = LoadPair(node_sums + static_cast<int64_t>(node) * K + k);
+    const GPairI64 ls = LoadPair(hist + static_cast<int64_t>(k) * B + nb.bin);
+    const GPairI64 rs{ns.grad - ls.grad, ns.hess - ls.hess};
+    StorePair(node_sums + static_cast<int64_t>(l) * K + k, ls);
+    StorePair(node_sums + static_cast<int64_t>(r) * K + k, rs);
+    const GPairF64 dl = Dequantise(ls, qp), dr = Dequantise(rs, qp);
+    tree.leaf_value[static_cast<int64_t>(l) * K + k] = CalculateLeafValue(dl.grad, dl.hess, l1, l2);
+    tree.leaf_value[static_cast<int64_t>(r) * K + k] = CalculateLeafValue(dr.grad, dr.hess, l1, l2);
+    if (k == 0) {
+      tree.feature[node]     = bf;
+      tree.split_value[node] = static_cast<double>(proposals[nb.bin]);
+      tree.gain[node]        = nb.gain;
+      tree.split_bin[node]   = nb.bin - row_ptr[bf];
+    }
+  }
+}
+
+__global__ void k_root_leaf(TreeArrays tree, int K, const QuantParams* __restrict__ qp_ptr, double l1, double l2)
+{
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  const GPairF64 s   = Dequantise(tree.node_sums[k], *qp_ptr);
+  tree.leaf_value[k] = CalculateLeafValue(s.grad, s.hess, l1, l2);
+}
+
+__global__ void k_write_hessian(const GPairI64* __restrict__ node_sums, const QuantParams* __restrict__ qp_ptr,
+                                double* __restrict__ hessian, int64_t n)
+{
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i < n) hessian[i] = static_cast<double>(node_sums[i].hess) * qp_ptr->inv_h;
+}
+
+}  // namespace
+
+void PlanBuilt(const GPairI64* node_sums, int K, int node_begin, int n_nodes, bool parent_available,
+               int32_t* slot_of_node, cudaStream_t stream)
+{
+  k_plan_built<<<(n_nodes + 255) / 256, 256, 0, stream>>>(node_sums, K, node_begin, n_nodes, parent_available,
+                                                          slot_of_node);
+  LBK_LAUNCH_CHECK();
+}
+
+void ScanLevel(const GPairI64* built, const int32_t* slot_of_node, GPairI64* level_hist, const GPairI64* parent_hist,
+               int parent_begin, const GPairI64* node_sums, int node_begin, int n_nodes, int K, int F, int B,
+               const int32_t* row_ptr, bool parent_available, cudaStream_t stream)
+{
+  const int64_t warps  = static_cast<int64_t>(n_nodes) * F;
+  const int64_t blocks = (warps + 7) / 8;
+  dim3 grid(static_cast<unsigned>(blocks), K);
+  k_scan<<<grid, 256, 0, stream>>>(built, slot_of_node, level_hist, parent_hist, parent_begin, node_sums, node_begin,
+                                   n_nodes, K, F, B, row_ptr, parent_available);
+  LBK_LAUNCH_CHECK();
+}
+
+template <typename T>
+void BestSplit(const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B, const int32_t* row_ptr,
+               const T* proposals, const QuantParams* qp, const SplitParams& sp, TreeArrays tree, cudaStream_t stream)
+{
+  k_best_split<T><<<n_nodes, kSplitThreads, 0, stream>>>(level_hist, node_begin, K, F, B, row_ptr, proposals, qp, sp.l1,
+                                                         sp.l2, sp.min_split_gain, sp.feature_set, tree);
+  LBK_LAUNCH_CHECK();
+}
+
+void RootLeaf(TreeArrays tree, int K, const QuantParams* qp, double l1, double l2, cudaStream_t stream)
+{
+  k_root_leaf<<<(K + 127) / 128, 128, 0, stream>>>(tree, K, qp, l1, l2);
+  LBK_LAUNCH_CHECK();
+}
+
+void WriteHessian(const GPairI64* node_sums, const QuantParams* qp, double* hessian, int64_t n, cudaStream_t stream)
+{
+  k_write_hessian<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(node_sums, qp, hessian, n);
+  LBK_LAUNCH_CHECK();
+}
+
+template void BestSplit<float>(const GPairI64*, int, int, int, int, int, const int32_t*, const float*, const QuantParams*,
+                               const SplitParams&, TreeArrays, cudaStream_t);
+template void BestSplit<double>(const GPairI64*, int, int, int, int, int, const int32_t*, const double*,
+                                const QuantParams*, const SplitParams&, TreeArrays, cudaStream_t);
+
+}  // namespace lbk

@@ -1,0 +1,186 @@
+"""CPU tests of the oracle: the reference's known answers and invariants
+(legateboost/test/models/test_tree.py, legateboost/testing/utils.py), the RNG restatement against
+the toolkit's thrust headers, the restatement against the stub-compiled reference sources when
+that build is present, and against the committed golden vectors."""
+import glob
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def tree_tuple(t):
+    return (t.leaf_value, t.feature, t.split_value)
+
+
+@pytest.mark.parametrize("mode", ["Q", "D"])
+def test_basic_known_answer(oracle, mode):
+    # reference: test_tree.py:11-21
+    X = np.array([[0.0], [1.0]])
+    g = np.array([[0.0], [-1.0]])
+    h = np.array([[1.0], [1.0]])
+    t = oracle.build_tree(X, g, h, max_depth=1, l2=0.0, seed=1872583848, mode=mode)
+    assert np.allclose(oracle.predict(X, [tree_tuple(t)]), np.array([[0.0], [1.0]]))
+
+
+@pytest.mark.parametrize("mode", ["Q", "D"])
+def test_l2_known_answer(oracle, mode):
+    # reference: test_tree.py:64-78 (init=None, lr=1: g = pred - y = -y, h = 1)
+    X = np.array([[0.0], [0.0]])
+    y = np.array([500.0, 500.0])
+    l2 = 10.0
+    t = oracle.build_tree(X, -y[:, None], np.ones((2, 1)), max_depth=0, l2=l2, seed=5, mode=mode)
+    assert np.isclose(oracle.predict(X, [tree_tuple(t)])[0, 0], y.sum() / (y.size + l2))
+
+
+@pytest.mark.parametrize("mode", ["Q", "D"])
+def test_l1_known_answer(oracle, mode):
+    # reference: test_tree.py:160-184
+    X = np.array([[0.0], [0.0]])
+    y = np.array([500.0, 500.0])
+    l1 = 1.5
+    t = oracle.build_tree(X, -y[:, None], np.ones((2, 1)), max_depth=0, l1=l1, l2=0.0, seed=5, mode=mode)
+    assert np.isclose(oracle.predict(X, [tree_tuple(t)])[0, 0], (y.sum() - l1) / y.size)
+    y = np.array([0.5, 0.5])
+    t = oracle.build_tree(X, -y[:, None], np.ones((2, 1)), max_depth=0, l1=l1, l2=0.0, seed=5, mode=mode)
+    assert np.isclose(oracle.predict(X, [tree_tuple(t)])[0, 0], 0.0)
+
+
+@pytest.mark.parametrize("mode", ["Q", "D"])
+def test_min_split_gain(oracle, mode):
+    # reference: test_tree.py:187-215
+    rng = np.random.RandomState(0)
+    X = rng.random((100, 1))
+    y = rng.random(100)
+    a = oracle.build_tree(X, -y[:, None], np.ones((100, 1)), max_depth=12, min_split_gain=0.0, seed=3, mode=mode)
+    b = oracle.build_tree(X, -y[:, None], np.ones((100, 1)), max_depth=12, min_split_gain=0.03, seed=3, mode=mode)
+    assert (b.hessian > 0).sum() < (a.hessian > 0).sum()
+    assert np.isclose(a.gain[0], b.gain[0] + 0.03)
+
+
+def sanity_check(t):
+    # reference: legateboost/testing/utils.py:22-50
+    split = t.feature != -1
+    assert np.all(t.hessian[split] > 0.0)
+    assert np.all(t.gain[split] > 0.0)
+    leaves = (t.feature == -1) & (t.hessian[:, 0] > 0.0)
+    assert np.isclose(t.hessian[leaves].sum(axis=0), t.hessian[0]).all()
+
+
+@pytest.mark.parametrize("mode", ["Q", "D"])
+@pytest.mark.parametrize("K", [1, 5])
+def test_improving_with_depth(oracle, mode, K):
+    # reference: test_tree.py:24-45 (smaller)
+    rs = np.random.RandomState(0)
+    X = rs.random((2000, 20))
+    g = rs.normal(size=(2000, K))
+    h = rs.random(g.shape) + 0.1
+    y = -g / h
+    metrics = []
+    for depth in range(0, 8):
+        t = oracle.build_tree(X, g, h, max_depth=depth, seed=1872583848, mode=mode)
+        sanity_check(t)
+        p = oracle.predict(X, [tree_tuple(t)])
+        metrics.append((((p - y) ** 2 * h).sum(axis=0) / h.sum(axis=0)).mean())
+    assert all(a - b > -1e-3 for a, b in zip(metrics, metrics[1:]))
+    assert metrics[-1] < metrics[0]
+
+
+def test_batch_predict_is_sum(oracle):
+    # reference: test_model.py:8-21
+    rs = np.random.RandomState(0)
+    X = rs.random((1000, 10))
+    g = rs.normal(size=(1000, 5))
+    h = rs.random(g.shape) + 0.1
+    a = oracle.build_tree(X, g, h, max_depth=8, seed=1, mode="Q")
+    b = oracle.build_tree(X, rs.normal(size=(1000, 5)), h, max_depth=8, seed=1, mode="Q")
+    both = oracle.predict(X, [tree_tuple(a), tree_tuple(b)])
+    assert np.allclose(both, oracle.predict(X, [tree_tuple(a)]) + oracle.predict(X, [tree_tuple(b)]))
+
+
+def test_deep_tree_two_rows(oracle):
+    # reference: test_tree.py:48-61
+    X = np.random.RandomState(0).random((2, 1))
+    t = oracle.build_tree(X, -np.array([[500.0], [500.0]]), np.ones((2, 1)), max_depth=16, seed=9, mode="Q")
+    assert t.feature.shape[0] == 2 ** 17 - 1
+
+
+def test_feature_set(oracle):
+    rs = np.random.RandomState(0)
+    X = rs.random((500, 10))
+    g = rs.normal(size=(500, 1))
+    h = np.ones((500, 1))
+    mask = np.zeros(10, dtype=bool)
+    mask[1] = True
+    for mode in "QD":
+        t = oracle.build_tree(X, g, h, max_depth=5, seed=4, feature_set=mask, mode=mode)
+        used = t.feature[t.feature >= 0]
+        assert used.size > 0 and np.all(used == 1)
+
+
+def test_rank_simulation_changes_only_scale(oracle):
+    # integer histograms do not depend on how rows are split; the scale does (max of local sums)
+    rs = np.random.RandomState(1)
+    X = rs.random((3000, 8)).astype(np.float32)
+    g = rs.normal(size=(3000, 1))
+    h = np.ones((3000, 1))
+    a = oracle.build_tree(X, g, h, max_depth=4, seed=11, mode="Q", n_ranks=1)
+    b = oracle.build_tree(X, g, h, max_depth=4, seed=11, mode="Q", n_ranks=4)
+    assert a.B == b.B and np.array_equal(a.proposals, b.proposals)
+    assert b.scale[0] > a.scale[0]
+    sanity_check(b)
+
+
+def test_rng_matches_thrust(oracle):
+    exe = os.path.join(ROOT, "oracle", "check_rng")
+    if not os.path.exists(exe):
+        pytest.skip("check_rng not built (needs the CUDA toolkit headers)")
+    assert subprocess.run([exe], capture_output=True).returncode == 0
+
+
+def test_abs_sum_order(oracle):
+    rs = np.random.RandomState(3)
+    for n in [1, 31, 4096, 4097, 100000]:
+        v = rs.normal(size=n) * 10.0 ** rs.randint(-3, 3, size=n)
+        s = oracle.abs_sum(v)
+        assert np.isclose(s, np.abs(v).sum(), rtol=1e-12)
+    # order sensitivity: the canonical sum is a fixed function of the sequence
+    v = rs.normal(size=10000)
+    assert oracle.abs_sum(v) == oracle.abs_sum(v.copy())
+
+
+@pytest.mark.parametrize("case", range(4))
+def test_mode_d_matches_reference_build(oracle, case):
+    """Bit-for-bit against the reference's own build_tree.cc / predict.cc (stub-compiled)."""
+    if oracle.ref_lib() is None:
+        pytest.skip("oracle/_ref/libref_cpu.so not built here")
+    rs = np.random.RandomState(case)
+    N, F, K, D, S, dt = [(1000, 10, 1, 4, 64, np.float32), (3000, 20, 3, 6, 256, np.float64),
+                         (300, 5, 2, 8, 16, np.float32), (4000, 40, 5, 5, 128, np.float64)][case]
+    X = rs.random((N, F)).astype(dt)
+    g = rs.normal(size=(N, K))
+    h = rs.random((N, K)) + 0.1
+    a = oracle.build_tree(X, g, h, max_depth=D, split_samples=S, seed=77 + case, mode="D")
+    b = oracle.build_tree(X, g, h, max_depth=D, split_samples=S, seed=77 + case, mode="D", use_reference=True)
+    for f in ["leaf_value", "feature", "split_value", "gain", "hessian"]:
+        assert np.array_equal(getattr(a, f), getattr(b, f)), f
+
+
+def test_golden_vectors(oracle):
+    """Committed outputs of the reference CPU build (tests/golden/make_golden.py)."""
+    files = sorted(glob.glob(os.path.join(HERE, "golden", "tree_*.npz")))
+    assert files, "golden fixtures missing"
+    for path in files:
+        z = np.load(path)
+        t = oracle.build_tree(z["X"], z["g"], z["h"], max_depth=int(z["max_depth"]),
+                              split_samples=int(z["split_samples"]), seed=int(z["seed"]),
+                              l1=float(z["l1"]), l2=float(z["l2"]), min_split_gain=float(z["min_split_gain"]),
+                              mode="D")
+        for f in ["leaf_value", "feature", "split_value", "gain", "hessian"]:
+            assert np.array_equal(getattr(t, f), z[f]), (path, f)
+        p = oracle.predict(z["X"], [tree_tuple(t)])
+        assert np.array_equal(p, z["pred"]), path
