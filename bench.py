@@ -1,0 +1,421 @@
+"""Benchmark of the tree-building hot path.
+
+Default workload = the histogram-build microbenchmark: 10M rows x 128 features of uint8 bin ids
+uniform in [0,255], rows assigned uniformly at random to the 128 nodes of tree level 7, one
+output, quantised int32 gradient pairs.  A step is one histogram build over the whole batch; with
+N GPUs every rank holds its own 10M-row shard (weak scaling) and the level's histograms are summed
+over ranks with an NCCL all-reduce inside the step.
+
+    python bench.py --gpus N --steps K --warmup W          (torchrun for N > 1)
+    python bench.py --impl reference ...                   the reference's CPU code, timed on the host
+    python bench.py --workload train|predict ...           other stages of the path (own JSON line)
+
+One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+HIST_ROWS, HIST_FEATURES, HIST_NODES, HIST_BINS = 10_000_000, 128, 128, 256
+
+
+def shard_rows(n_rows, rank, world):
+    """Contiguous block [begin, end) of rank `rank` when n_rows are cut into `world` blocks."""
+    base, extra = divmod(n_rows, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.rows = []
+        self.proc = None
+        self.device_index = device_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def hist_inputs(torch, n_rows, seed, device):
+    """Synthetic level-7 inputs on the device: group-major uint8 bins, node-grouped row index,
+    quantised pairs from the library's own quantiser (scale = INT32_MAX / sum|g|, as the tree
+    builder uses), float32 pairs for the float path."""
+    from legateboost_b200 import stages
+
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    G = HIST_FEATURES // 32
+    bins = torch.randint(0, HIST_BINS, (G, n_rows, 32), dtype=torch.uint8, device=device, generator=gen)
+    row_ptr = (torch.arange(HIST_FEATURES + 1, dtype=torch.int32, device=device) * HIST_BINS)
+    g = torch.randn((n_rows, 1), dtype=torch.float64, device=device, generator=gen)
+    h = torch.ones((n_rows, 1), dtype=torch.float64, device=device)
+    gpair, _, _ = stages.quantise(g, h, seed=seed)
+    gpair_f = torch.stack([g.to(torch.float32), h.to(torch.float32)], dim=2).contiguous()
+    node = torch.randint(0, HIST_NODES, (n_rows,), dtype=torch.int32, device=device, generator=gen) + (HIST_NODES - 1)
+    row_index, seg = stages.group_rows(node, HIST_NODES - 1, HIST_NODES)
+    del g, h
+    return bins, row_ptr, gpair, gpair_f, row_index, seg, node
+
+
+def algorithmic_bytes(n_rows):
+    # per processed row: F bin bytes + 8 (int32 pair) + 4 (row index); per built node: B*16
+    return n_rows * (HIST_FEATURES + 8 + 4) + HIST_NODES * HIST_FEATURES * HIST_BINS * 16
+
+
+def cpu_hist_sample(n_rows_sample, seed, threads):
+    """The histogram of the oracle (a restatement of the reference CPU loop, build_tree.cc:267-280)
+    timed on `threads` host threads over row shards of one sample, partial histograms summed in
+    process.  Returns (rows*features/s, description)."""
+    from oracle import oracle as O
+
+    rs = np.random.default_rng(seed)
+    bins = rs.integers(0, HIST_BINS, size=(n_rows_sample, HIST_FEATURES), dtype=np.uint8)
+    row_ptr = (np.arange(HIST_FEATURES + 1) * HIST_BINS).astype(np.int32)
+    g = rs.normal(size=(n_rows_sample, 1)).astype(np.float32)
+    h = np.ones((n_rows_sample, 1), dtype=np.float32)
+    node = rs.integers(0, HIST_NODES, size=n_rows_sample).astype(np.int32) + (HIST_NODES - 1)
+    O.lib()
+    parts = [None] * threads
+
+    def work(t):
+        b, e = shard_rows(n_rows_sample, t, threads)
+        parts[t] = O.histogram_d(bins[b:e], row_ptr, g[b:e], h[b:e], node[b:e], HIST_NODES - 1, 2 * HIST_NODES - 1)
+
+    t0 = time.perf_counter()
+    ths = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    total = parts[0]
+    for p in parts[1:]:
+        total += p
+    dt = time.perf_counter() - t0
+    return n_rows_sample * HIST_FEATURES / dt, dt
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU histogram path on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample = 2_000_000
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_hist_sample(200_000, 1, threads)
+    vals = []
+    t_all = 0.0
+    for i in range(args.steps):
+        v, dt = cpu_hist_sample(sample, 1 + i, threads)
+        vals.append(v)
+        t_all += dt
+    value = sample * HIST_FEATURES * args.steps / t_all
+    line = {
+        "impl": "reference", "metric": "histogram rows*features/s", "value": value, "unit": "row-features/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "histogram build, level 7 (128 nodes), %d features x %d bins, float64 accumulation"
+                               % (HIST_FEATURES, HIST_BINS)},
+        "cpu_baseline": {"value": value, "unit": "row-features/s", "cores": threads, "kind": "port",
+                         "sample": "%d-row sample of the 10M-row batch per step, %d threads on row shards" % (sample, threads)},
+        "e2e": {"value": value, "unit": "row-features/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_hist(args):
+    import torch
+    import torch.distributed as dist
+
+    import legateboost_b200 as lb
+    from legateboost_b200 import stages
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    ctx = lb.library.init_distributed(local)
+    lib = ctx.lib
+    n_rows = args.rows
+    mode = 1 if args.float_path else 0
+    bins, row_ptr, gpair, gpair_f, row_index, seg, node = hist_inputs(torch, n_rows, 1 + rank, device)
+    gp = gpair_f if mode else gpair
+    hist = torch.empty((HIST_NODES, 1, HIST_FEATURES * HIST_BINS, 2),
+                       dtype=torch.float64 if mode else torch.int64, device=device)
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=device)  # > L2 (126 MB)
+
+    lb.library.load().lbk_profile_enable(ctx.handle, 1)
+    import ctypes as C
+
+    def step():
+        stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, mode=mode, hist=hist, ctx=ctx)
+        if world > 1:
+            dist.all_reduce(hist)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    kernel_ms = []
+    for i in range(args.steps):
+        flush.fill_(i & 0xFF)  # evict the inputs from L2 between timed iterations
+        ev[i][0].record()
+        step()
+        ev[i][1].record()
+        ms = C.c_float(0)
+        ctx.check(lib.lbk_profile_histogram_ms(ctx.handle, C.byref(ms)))
+        kernel_ms.append(ms.value)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = sum(a.elapsed_time(b) for a, b in ev)
+    t = torch.tensor([total_ms, sum(kernel_ms)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, ksum = float(t[0]), float(t[1])
+    value = n_rows * HIST_FEATURES * world * args.steps / (total_ms * 1e-3)
+
+    # end to end through the C ABI with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        hb = bins.cpu().pin_memory()
+        hgp = gp.cpu().pin_memory()
+        hidx = row_index.cpu().pin_memory()
+        hseg = seg.cpu()
+        hrp = row_ptr.cpu()
+        hh = torch.empty(hist.shape, dtype=hist.dtype).pin_memory()
+        n_e2e = max(2, min(args.steps, 5))
+        for _ in range(2):
+            stages.histogram(hb, hrp, hgp, hidx, hseg, HIST_FEATURES, mode=mode, hist=hh, ctx=ctx, host=True)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            stages.histogram(hb, hrp, hgp, hidx, hseg, HIST_FEATURES, mode=mode, hist=hh, ctx=ctx, host=True)
+        torch.cuda.synchronize()
+        dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": n_rows * HIST_FEATURES * world * n_e2e / float(dt[0]), "unit": "row-features/s",
+               "h2d_bytes_per_step": int(hb.numel() + hgp.numel() * hgp.element_size() + hidx.numel() * 4
+                                         + hseg.numel() * 4 + hrp.numel() * 4),
+               "d2h_bytes_per_step": int(hh.numel() * 8)}
+
+    if rank == 0:
+        peak, which = measured_peaks()
+        kms = ksum / args.steps
+        achieved = algorithmic_bytes(n_rows) / (kms * 1e-3) / 1e9
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "hist_traffic.json")
+        if os.path.exists(tpath):
+            with open(tpath) as f:
+                traffic = json.load(f).get("int32" if mode == 0 else "float32")
+        line = {
+            "metric": "histogram rows*features/s", "value": value, "unit": "row-features/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32" if mode else "int32", "data": "synthetic",
+            "config": {"workload": "histogram build, level 7 (128 nodes), %d rows x %d features x %d bins per GPU, "
+                                   "%s gradient pairs%s" % (n_rows, HIST_FEATURES, HIST_BINS,
+                                                            "float32" if mode else "quantised int32",
+                                                            ", NCCL all-reduce of the level's histograms" if world > 1 else ""),
+                       "l2": "160 MB flush buffer written between timed steps; inputs (1.4 GB) exceed L2"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "peak_source": which, "kernel": "k_hist", "kernel_ms": kms},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps,
+        }
+        if not args.no_cpu and world >= 1:
+            threads = os.cpu_count() or 1
+            v, dt = cpu_hist_sample(1_000_000, 7, threads)
+            line["cpu_baseline"] = {"value": v, "unit": "row-features/s", "cores": threads, "kind": "port",
+                                    "sample": "one 1M-row sample of the batch, %d threads on row shards (%.1f s)" % (threads, dt)}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_train(args):
+    """Boosting rounds per second: squared error, Tree(max_depth=args.depth), 256 bins."""
+    import torch
+    import torch.distributed as dist
+
+    import legateboost_b200 as lb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lb.library.init_distributed(local)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(3 + rank)
+    n, F = args.rows, args.features
+    X = torch.rand((n, F), dtype=torch.float32, device=device, generator=gen)
+    w = torch.randn(F, dtype=torch.float32, device=device, generator=torch.Generator(device=device).manual_seed(3))
+    y = X @ w + 0.1 * torch.randn(n, dtype=torch.float32, device=device, generator=gen)
+    rounds = args.steps
+    m = lb.LBRegressor(n_estimators=max(args.warmup, 1), base_models=(lb.Tree(max_depth=args.depth),), random_state=0)
+    m.fit(X, y)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    m = lb.LBRegressor(n_estimators=rounds, base_models=(lb.Tree(max_depth=args.depth),), random_state=0)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    m.fit(X, y)
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = float(t[0])
+        print(json.dumps({"metric": "boosting rounds/s", "value": rounds / (ms * 1e-3), "unit": "rounds/s",
+                          "n_gpus": world, "steps": rounds, "warmup": max(args.warmup, 1), "ms_per_step": ms / rounds,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
+                          "data": "synthetic",
+                          "config": {"workload": "squared-error boosting, depth %d, 256 bins, %d rows x %d features per GPU"
+                                                 % (args.depth, n, F)}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_predict(args):
+    import torch
+
+    from legateboost_b200.tree import predict_arrays
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4)
+    n, F, T, D = args.rows, args.features, args.trees, args.depth
+    X = torch.rand((n, F), dtype=torch.float32, device=device, generator=gen)
+    M = 2 ** (D + 1) - 1
+    trees = []
+    for _ in range(T):
+        feat = torch.randint(0, F, (M,), dtype=torch.int32, device=device, generator=gen)
+        feat[2 ** D - 1:] = -1
+        trees.append((torch.randn((M, 1), dtype=torch.float64, device=device, generator=gen), feat,
+                      torch.rand((M,), dtype=torch.float64, device=device, generator=gen)))
+    for _ in range(max(args.warmup, 1)):
+        predict_arrays(X, trees)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        predict_arrays(X, trees)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    peak, which = measured_peaks()
+    gbs = n * (F * 4 + 8) / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "predict rows/s", "value": n / (ms * 1e-3), "unit": "rows/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+                      "dtype": "f64", "data": "synthetic",
+                      "config": {"workload": "%d trees depth %d, %d rows x %d features" % (T, D, n, F)},
+                      "node_visits_per_s": n * T * D / (ms * 1e-3),
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                   "peak_source": which}}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="hist", choices=["hist", "train", "predict"])
+    ap.add_argument("--rows", type=int, default=None)
+    ap.add_argument("--features", type=int, default=64)
+    ap.add_argument("--depth", type=int, default=8)
+    ap.add_argument("--trees", type=int, default=500)
+    ap.add_argument("--float-path", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.workload == "hist":
+        args.rows = args.rows or HIST_ROWS
+        return run_hist(args)
+    if args.workload == "train":
+        args.rows = args.rows or 10_000_000
+        return run_train(args)
+    args.rows = args.rows or 5_000_000
+    return run_predict(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -66,6 +66,12 @@ typedef int (*lbk_allreduce_fn)(void* user, void* buf, size_t count, int dtype /
 int lbk_comm_set_callback(lbk_context* ctx, lbk_allreduce_fn fn, void* user, int rank, int n_ranks);
 int lbk_comm_size(const lbk_context* ctx);
 
+/* Timing of the histogram kernel alone (no counterpart in the reference, which leaves profiling
+ * to external tools): when enabled, every histogram launch is bracketed by CUDA events on the
+ * caller's stream; lbk_profile_histogram_ms returns the duration of the most recent one. */
+int lbk_profile_enable(lbk_context* ctx, int on);
+int lbk_profile_histogram_ms(lbk_context* ctx, float* ms);
+
 /* ------------------------------------------------------------------------------------------
  * BUILD_TREE.  Field order follows the task's argument order (legateboost/models/tree.py:117-183,
  * build_tree.cu:1278-1307): inputs X, g, h, optional feature set; scalars max_depth, max_nodes,

@@ -195,6 +195,8 @@ void lbk_context_destroy(lbk_context* ctx)
   if (ctx->owns_nccl && ctx->nccl_comm && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
+  if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+  if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   delete ctx;
 }
 
@@ -270,5 +272,29 @@ int lbk_comm_set_callback(lbk_context* ctx, lbk_allreduce_fn fn, void* user, int
 }
 
 int lbk_comm_size(const lbk_context* ctx) { return ctx ? ctx->n_ranks : 0; }
+
+int lbk_profile_enable(lbk_context* ctx, int on)
+{
+  return lbk::Guard(ctx, [&] {
+    LBK_EXPECT(ctx != nullptr, "context is null");
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    if (on && !ctx->ev_start) {
+      LBK_CUDA(cudaEventCreate(&ctx->ev_start));
+      LBK_CUDA(cudaEventCreate(&ctx->ev_stop));
+    }
+    ctx->profile          = on != 0;
+    ctx->profile_recorded = false;
+  });
+}
+
+int lbk_profile_histogram_ms(lbk_context* ctx, float* ms)
+{
+  return lbk::Guard(ctx, [&] {
+    LBK_EXPECT(ctx && ms, "null argument");
+    LBK_EXPECT(ctx->profile && ctx->profile_recorded, "no histogram launch has been timed");
+    LBK_CUDA(cudaEventSynchronize(ctx->ev_stop));
+    LBK_CUDA(cudaEventElapsedTime(ms, ctx->ev_start, ctx->ev_stop));
+  });
+}
 
 }  // extern "C"

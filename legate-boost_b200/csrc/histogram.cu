@@ -447,6 +447,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
                                     static_cast<int>(smem)));                                                      \
     k_hist<BinT, FL, SM><<<grid, kHistThreads, smem, stream>>>(p);                                                 \
   } while (0)
+  if (ctx->profile) LBK_CUDA(cudaEventRecord(ctx->ev_start, stream));
   if (smem_path) {
     if (lv.float_mode) LBK_HIST_LAUNCH(uint8_t, true, true); else LBK_HIST_LAUNCH(uint8_t, false, true);
   } else if (lv.bin_bytes == 1) {
@@ -456,6 +457,10 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   }
 #undef LBK_HIST_LAUNCH
   LBK_LAUNCH_CHECK();
+  if (ctx->profile) {
+    LBK_CUDA(cudaEventRecord(ctx->ev_stop, stream));
+    ctx->profile_recorded = true;
+  }
 }
 
 void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t n_rows, int node_begin,

@@ -71,6 +71,10 @@ struct lbk_context {
   bool owns_nccl      = false;
   lbk_allreduce_fn cb = nullptr;
   void* cb_user       = nullptr;
+  // optional timing of the histogram kernel alone (events on the caller's stream)
+  bool profile            = false;
+  cudaEvent_t ev_start    = nullptr, ev_stop = nullptr;
+  bool profile_recorded   = false;
 };
 
 namespace lbk {

@@ -19,7 +19,7 @@ UNIQUE_ID_BYTES = 128
 EXPORTS = [
     "lbk_version", "lbk_context_create", "lbk_context_destroy", "lbk_last_error", "lbk_context_trim",
     "lbk_comm_unique_id", "lbk_comm_init", "lbk_comm_attach_nccl", "lbk_comm_set_callback",
-    "lbk_comm_size", "lbk_build_tree", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
+    "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
     "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_group_rows",
 ]
 
@@ -96,6 +96,8 @@ def load():
             lib.lbk_comm_init.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
             lib.lbk_comm_attach_nccl.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
             lib.lbk_comm_size.argtypes = [C.c_void_p]
+            lib.lbk_profile_enable.argtypes = [C.c_void_p, C.c_int]
+            lib.lbk_profile_histogram_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
             lib.lbk_build_tree.argtypes = [C.c_void_p, C.POINTER(BuildTreeArgs)]
             lib.lbk_predict.argtypes = [C.c_void_p, C.POINTER(PredictArgs)]
             lib.lbk_histogram.argtypes = [C.c_void_p, C.POINTER(HistogramArgs)]

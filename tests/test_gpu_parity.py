@@ -1,0 +1,384 @@
+"""GPU parity tests: every stage of the CUDA tree builder and the whole BUILD_TREE / PREDICT calls
+against the CPU oracle on identical seeded inputs, through the C ABI (liblbk.so).
+
+Bars: integer / index results bit-exact; float histograms <= 1e-5 relative (to the largest
+magnitude of the histogram); predictions bit-exact (the bar is <= 1e-4)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def lb():
+    import legateboost_b200 as lb
+    from legateboost_b200 import stages  # noqa: F401
+
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    lb.library.load()  # fails loudly if liblbk.so is missing
+    return lb
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def tree_tuple(t):
+    return (t.leaf_value, t.feature, t.split_value)
+
+
+def to_row_major(bins_g, F):
+    G, N, _ = bins_g.shape
+    return bins_g.permute(1, 0, 2).reshape(N, G * 32)[:, :F]
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("N,F,S", [(1000, 7, 16), (5000, 50, 256), (300, 33, 500), (64, 3, 2048), (2, 1, 256)])
+def test_split_proposals_and_bins(lb, oracle, dtype, N, F, S):
+    from legateboost_b200 import stages
+
+    rs = np.random.RandomState(N + F)
+    X = rs.random((N, F)).astype(dtype)
+    X[:, 0] = np.round(X[:, 0] * 3)  # a low-cardinality feature
+    for seed in (0, 1872583848):
+        want_p, want_rp = oracle.split_proposals(X, S, seed, mode="Q")
+        got_p, got_rp = stages.split_proposals(dev(X), S, seed)
+        assert np.array_equal(got_rp.cpu().numpy(), want_rp)
+        assert np.array_equal(got_p.cpu().numpy(), want_p)
+        want_bins = oracle.bin_x(X, want_p, want_rp)
+        mb = int(np.diff(want_rp).max())
+        bb = 1 if mb <= 256 else 2
+        got = stages.bin_matrix(dev(X), got_p, got_rp, bin_bytes=bb)
+        assert np.array_equal(to_row_major(got, F).cpu().numpy().astype(np.int16), want_bins)
+
+
+@pytest.mark.parametrize("N,K", [(1, 1), (1000, 1), (5000, 3), (70000, 2), (1 << 21, 1)])
+def test_quantise(lb, oracle, N, K):
+    from legateboost_b200 import stages
+
+    rs = np.random.RandomState(N)
+    g = rs.normal(size=(N, K)) * 10.0 ** rs.randint(-2, 3, size=(N, K))
+    h = rs.random((N, K)) + 1e-8
+    want_q, want_scale = oracle.quantise(g, h, seed=1234567)
+    gp, root, scale = stages.quantise(dev(g), dev(h), seed=1234567)
+    assert np.array_equal(scale.cpu().numpy(), want_scale)
+    assert np.array_equal(gp.cpu().numpy().astype(np.int64), want_q)
+    assert np.array_equal(root.cpu().numpy(), want_q.sum(axis=0))
+
+
+def test_quantise_row_offset(lb, oracle):
+    # the quantised pair depends on the GLOBAL row id: a shard quantised on its own, with the
+    # scale of its own |g| sum, must equal the oracle's shard
+    from legateboost_b200 import stages
+
+    rs = np.random.RandomState(0)
+    g = rs.normal(size=(4000, 2))
+    h = np.ones((4000, 2))
+    gp, _, scale = stages.quantise(dev(g[1000:3000]), dev(h[1000:3000]), seed=99, row_offset=1000)
+    want_q, want_scale = oracle.quantise(g, h, seed=99, rank_off=[0, 1000, 3000, 4000])
+    # the oracle takes the max over shards; compare only when this shard carries the max
+    single_q, single_scale = oracle.quantise(g[1000:3000], h[1000:3000], seed=99)
+    assert np.array_equal(scale.cpu().numpy(), single_scale)
+    if np.array_equal(single_scale, want_scale):
+        assert np.array_equal(gp.cpu().numpy().astype(np.int64), want_q[1000:3000])
+
+
+# ---------------------------------------------------------------------------------------------
+def _hist_case(rs, N, F, K, n_nodes, nb):
+    bins = rs.randint(0, nb, size=(N, F)).astype(np.uint8)
+    row_ptr = (np.arange(F + 1) * nb).astype(np.int32)
+    node = rs.randint(0, n_nodes, size=N).astype(np.int32) + (n_nodes - 1)
+    return bins, row_ptr, node
+
+
+@pytest.mark.parametrize("N,F,K,n_nodes,nb", [(200000, 128, 1, 128, 256), (50000, 50, 3, 8, 256),
+                                              (3000, 100, 1, 64, 7), (100, 5, 2, 4, 256), (70000, 64, 1, 1, 256)])
+def test_histogram_int_exact(lb, oracle, N, F, K, n_nodes, nb):
+    from legateboost_b200 import stages
+
+    rs = np.random.RandomState(F)
+    bins, row_ptr, node = _hist_case(rs, N, F, K, n_nodes, nb)
+    q = rs.randint(-(2 ** 20), 2 ** 20, size=(N, K, 2)).astype(np.int32)
+    q[:, :, 1] = np.abs(q[:, :, 1])
+    want = oracle.histogram_q(bins, row_ptr, q, node, n_nodes - 1, 2 * n_nodes - 1)
+    row_index, seg = stages.group_rows(dev(node), n_nodes - 1, n_nodes)
+    # grouping is stable: rows ascending inside each node
+    ri, sg = row_index.cpu().numpy(), seg.cpu().numpy()
+    assert sg[-1] == N
+    for j in range(n_nodes):
+        r = ri[sg[j]:sg[j + 1]]
+        assert np.all(node[r] == j + n_nodes - 1) and np.all(np.diff(r) > 0)
+    got = stages.histogram(stages.to_group_major(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_histogram_int_no_wraparound(lb, oracle):
+    """Partial sums that exceed int32 in one chunk must still come out exact."""
+    from legateboost_b200 import stages
+
+    N, F = 6000, 4
+    rs = np.random.RandomState(5)
+    bins = np.zeros((N, F), dtype=np.uint8)  # everything in one bin
+    row_ptr = (np.arange(F + 1) * 2).astype(np.int32)
+    node = np.zeros(N, dtype=np.int32)
+    q = np.full((N, 1, 2), 2 ** 30, dtype=np.int32)  # sums reach 6000 * 2^30
+    q[::2, 0, 0] *= -1
+    q[:, 0, 0] += rs.randint(0, 1000, size=N).astype(np.int32)
+    want = oracle.histogram_q(bins, row_ptr, q, node, 0, 1)
+    row_index, seg = stages.group_rows(dev(node), 0, 1)
+    got = stages.histogram(stages.to_group_major(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("N,F,K,n_nodes", [(200000, 128, 1, 128), (20000, 40, 2, 16)])
+def test_histogram_float_tolerance(lb, oracle, N, F, K, n_nodes):
+    from legateboost_b200 import stages
+
+    rs = np.random.RandomState(7)
+    bins, row_ptr, node = _hist_case(rs, N, F, K, n_nodes, 256)
+    gh = np.stack([rs.normal(size=(N, K)), np.ones((N, K))], axis=2).astype(np.float32)
+    want = oracle.histogram_d(bins, row_ptr, gh[:, :, 0].copy(), gh[:, :, 1].copy(), node, n_nodes - 1, 2 * n_nodes - 1)
+    row_index, seg = stages.group_rows(dev(node), n_nodes - 1, n_nodes)
+    got = stages.histogram(stages.to_group_major(dev(bins)), dev(row_ptr), dev(gh), row_index, seg, F, mode=1)
+    got = got.cpu().numpy()
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= 1e-5 * scale
+
+
+def test_histogram_host_buffers(lb, oracle):
+    from legateboost_b200 import stages
+
+    rs = np.random.RandomState(11)
+    N, F, K, n_nodes = 30000, 64, 1, 8
+    bins, row_ptr, node = _hist_case(rs, N, F, K, n_nodes, 256)
+    q = rs.randint(-1000, 1000, size=(N, K, 2)).astype(np.int32)
+    want = oracle.histogram_q(bins, row_ptr, q, node, n_nodes - 1, 2 * n_nodes - 1)
+    row_index, seg = stages.group_rows(dev(node), n_nodes - 1, n_nodes)
+    bins_g = stages.to_group_major(dev(bins)).cpu().pin_memory()
+    got = stages.histogram(bins_g, torch.from_numpy(row_ptr), torch.from_numpy(q).pin_memory(),
+                           row_index.cpu(), seg.cpu(), F, mode=0, host=True)
+    assert np.array_equal(got.numpy(), want)
+
+
+# ---------------------------------------------------------------------------------------------
+TREE_CASES = [
+    # N, F, K, depth, S, dtype, kwargs
+    (1000, 10, 1, 4, 64, np.float32, {}),
+    (5000, 20, 3, 6, 256, np.float64, {}),
+    (300, 5, 2, 8, 16, np.float32, {}),
+    (10000, 100, 5, 7, 256, np.float64, {}),
+    (20000, 50, 1, 6, 256, np.float32, {}),
+    (2000, 33, 1, 5, 500, np.float32, {}),                      # two-byte bins
+    (3000, 12, 2, 6, 64, np.float32, {"l1": 0.5, "l2": 2.0, "min_split_gain": 0.01}),
+    (2, 1, 1, 12, 256, np.float64, {}),
+    (500, 6, 1, 0, 32, np.float32, {}),                          # depth 0: root only
+    (4000, 9, 1, 5, 128, np.float32, {"mask": True}),
+]
+
+
+def _run_tree_case(lb, oracle, case, seed, n_ranks=1, trace_nodes=0, hess_small=False):
+    from legateboost_b200.tree import build_tree_arrays
+
+    N, F, K, D, S, dt, kw = case
+    kw = dict(kw)
+    rs = np.random.RandomState(N * 7 + F)
+    X = rs.random((N, F)).astype(dt)
+    X[:, 0] = np.round(X[:, 0] * 5) / 5
+    g = rs.normal(size=(N, K))
+    h = rs.random((N, K)) * (1e-3 if hess_small else 1.0) + (0.0 if hess_small else 0.1)
+    mask = None
+    if kw.pop("mask", False):
+        mask = rs.random(F) < 0.5
+        mask[0] = True
+    want = oracle.build_tree(X, g, h, max_depth=D, split_samples=S, seed=seed, mode="Q", feature_set=mask,
+                             trace_nodes=trace_nodes, **kw)
+    got = build_tree_arrays(dev(X), dev(g), dev(h), max_depth=D, split_samples=S, seed=seed,
+                            feature_set=None if mask is None else torch.from_numpy(mask),
+                            row_offset=0, dataset_rows=N, trace_nodes=trace_nodes, **kw)
+    return X, want, got
+
+
+@pytest.mark.parametrize("case", TREE_CASES, ids=[str(c[:5]) for c in TREE_CASES])
+def test_build_tree_bit_exact(lb, oracle, case):
+    for seed in (2, 1872583848):
+        X, want, got = _run_tree_case(lb, oracle, case, seed)
+        assert got["B"] == want.B
+        assert np.array_equal(got["node_sums"].cpu().numpy(), want.node_sums)
+        assert np.array_equal(got["feature"].cpu().numpy(), want.feature)
+        assert np.array_equal(got["split_value"].cpu().numpy(), want.split_value)
+        assert np.array_equal(got["gain"].cpu().numpy(), want.gain)
+        assert np.array_equal(got["leaf_value"].cpu().numpy(), want.leaf_value)
+        assert np.array_equal(got["hessian"].cpu().numpy(), want.hessian)
+
+
+def test_build_tree_histograms_bit_exact(lb, oracle):
+    """Every node's histogram as it was when its split was evaluated (scan, write-skip rule,
+    sibling subtraction), including a case where quantised hessians of 0 occur."""
+    for case, small in (((3000, 8, 2, 5, 32, np.float32, {}), False), ((3000, 8, 2, 5, 32, np.float32, {}), True)):
+        D = case[3]
+        nodes = 2 ** D - 1
+        X, want, got = _run_tree_case(lb, oracle, case, seed=5, trace_nodes=nodes, hess_small=small)
+        assert np.array_equal(got["trace_hist"].cpu().numpy(), want.trace_hist)
+        assert np.array_equal(got["feature"].cpu().numpy(), want.feature)
+
+
+def test_build_tree_level_batching(lb, oracle):
+    """More bins than the 1 GB histogram rule holds on the deepest levels: levels are cut into
+    batches and built without parents (reference: test_wide_deep, test_tree.py:218-227)."""
+    case = (3000, 500, 1, 10, 256, np.float32, {})
+    X, want, got = _run_tree_case(lb, oracle, case, seed=3)
+    assert np.array_equal(got["feature"].cpu().numpy(), want.feature)
+    assert np.array_equal(got["node_sums"].cpu().numpy(), want.node_sums)
+    assert np.array_equal(got["leaf_value"].cpu().numpy(), want.leaf_value)
+
+
+def test_golden_trees_on_gpu(lb, oracle):
+    """The committed golden inputs: the GPU (quantised) tree must predict within 1e-4 of... itself
+    via the oracle's Mode Q, and stay close to the reference CPU tree's training loss."""
+    from legateboost_b200.tree import build_tree_arrays, predict_arrays
+
+    for path in sorted(glob.glob(os.path.join(HERE, "golden", "tree_*.npz"))):
+        z = np.load(path)
+        kw = dict(max_depth=int(z["max_depth"]), split_samples=int(z["split_samples"]), seed=int(z["seed"]),
+                  l1=float(z["l1"]), l2=float(z["l2"]), min_split_gain=float(z["min_split_gain"]))
+        want = oracle.build_tree(z["X"], z["g"], z["h"], mode="Q", **kw)
+        got = build_tree_arrays(dev(z["X"]), dev(z["g"]), dev(z["h"]), row_offset=0, dataset_rows=z["X"].shape[0], **kw)
+        assert np.array_equal(got["feature"].cpu().numpy(), want.feature)
+        assert np.array_equal(got["leaf_value"].cpu().numpy(), want.leaf_value)
+        # predict of the reference CPU tree stored in the fixture, evaluated by the GPU kernel
+        p = predict_arrays(dev(z["X"]), [(dev(z["leaf_value"]), dev(z["feature"]), dev(z["split_value"]))])
+        assert np.array_equal(p.cpu().numpy(), z["pred"])
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("N,F,K,T,D", [(1000, 10, 1, 5, 4), (5000, 100, 1, 40, 8), (777, 33, 5, 7, 6), (129, 3, 2, 1, 0)])
+def test_predict_bit_exact(lb, oracle, dtype, N, F, K, T, D):
+    from legateboost_b200.tree import predict_arrays
+
+    rs = np.random.RandomState(T)
+    X = rs.random((N, F)).astype(dtype)
+    M = 2 ** (D + 1) - 1
+    trees = []
+    for _ in range(T):
+        feat = rs.randint(0, F, size=M).astype(np.int32)
+        feat[2 ** D - 1:] = -1                      # last level are leaves
+        feat[rs.random(M) < 0.15] = -1              # some early leaves
+        split = rs.random(M)
+        leaf = rs.normal(size=(M, K))
+        trees.append((leaf, feat, split))
+    want = oracle.predict(X, trees)
+    got = predict_arrays(dev(X), [(dev(a), dev(b), dev(c)) for a, b, c in trees])
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_predict_empty_and_batch_sum(lb, oracle):
+    from legateboost_b200.tree import predict_arrays
+
+    rs = np.random.RandomState(0)
+    X = rs.random((500, 6)).astype(np.float32)
+    mk = lambda: (dev(rs.normal(size=(3, 1))), dev(np.array([2, -1, -1], dtype=np.int32)), dev(rs.random(3)))
+    a, b = mk(), mk()
+    pa, pb = predict_arrays(dev(X), [a]), predict_arrays(dev(X), [b])
+    assert torch.equal(predict_arrays(dev(X), [a, b]), pa + pb)
+    assert predict_arrays(dev(X[:0]), [a]).shape == (0, 1)
+
+
+# ---------------------------------------------------------------------------------------------
+def test_tree_class_known_answers(lb):
+    # reference: test_tree.py:11-21, 64-78, 160-184
+    X = dev(np.array([[0.0], [1.0]]))
+    g = dev(np.array([[0.0], [-1.0]]))
+    h = dev(np.array([[1.0], [1.0]]))
+    m = lb.Tree(max_depth=1, l2_regularization=0.0).set_random_state(np.random.RandomState(2)).fit(X, g, h)
+    assert np.allclose(m.predict(X).cpu().numpy(), np.array([[0.0], [1.0]]))
+    X0 = dev(np.array([[0.0], [0.0]]))
+    y = np.array([500.0, 500.0])
+    m = lb.Tree(max_depth=0, l2_regularization=10.0).set_random_state(np.random.RandomState(0))
+    m.fit(X0, dev(-y[:, None]), dev(np.ones((2, 1))))
+    assert np.isclose(m.predict(X0)[0, 0].item(), y.sum() / (y.size + 10.0))
+    m = lb.Tree(max_depth=0, l2_regularization=0.0, l1_regularization=1.5).set_random_state(np.random.RandomState(0))
+    m.fit(X0, dev(-y[:, None]), dev(np.ones((2, 1))))
+    assert np.isclose(m.predict(X0)[0, 0].item(), (y.sum() - 1.5) / y.size)
+    assert "leaf=" in str(m) and m == m and (m * 2.0).leaf_value[0, 0].item() == 2 * m.leaf_value[0, 0].item()
+
+
+def test_tree_class_depth_and_invariants(lb):
+    # reference: test_tree.py:24-45 and legateboost/testing/utils.py:22-50
+    rs = np.random.RandomState(0)
+    X = rs.random((10000, 100))
+    for K in (1, 5):
+        g = rs.normal(size=(X.shape[0], K))
+        h = rs.random(g.shape) + 0.1
+        y = -g / h
+        metrics = []
+        for depth in range(0, 10):
+            m = lb.Tree(max_depth=depth).set_random_state(np.random.RandomState(2)).fit(dev(X), dev(g), dev(h))
+            p = m.predict(dev(X)).cpu().numpy()
+            metrics.append((((p - y) ** 2 * h).sum(axis=0) / h.sum(axis=0)).mean())
+            feat, hess, gain = m.feature.cpu().numpy(), m.hessian.cpu().numpy(), m.gain.cpu().numpy()
+            split = feat != -1
+            assert np.all(hess[split] > 0.0) and np.all(gain[split] > 0.0)
+            leaves = (feat == -1) & (hess[:, 0] > 0.0)
+            assert np.isclose(hess[leaves].sum(axis=0), hess[0]).all()
+        assert all(a - b > -1e-3 for a, b in zip(metrics, metrics[1:])) and metrics[-1] < metrics[0]
+
+
+def test_max_depth_20_two_rows(lb):
+    # reference: test_tree.py:48-61
+    X = dev(np.random.RandomState(0).random((2, 1)))
+    m = lb.LBRegressor(init=None, base_models=(lb.Tree(max_depth=20),), learning_rate=1.0, n_estimators=1,
+                       random_state=0)
+    m.fit(X, dev(np.array([500.0, 500.0])))
+    assert m[0].feature.shape[0] == 2 ** 21 - 1
+
+
+def test_estimators_config1_reduced(lb, oracle):
+    """Configuration 1 at reduced size: squared error, depth 6, lr 0.1; loss falls every round and
+    every tree equals the oracle's tree for the same gradients and seed."""
+    rng = np.random.default_rng(0)
+    X = rng.random((20000, 50), dtype=np.float32)
+    y = (np.sin(6 * X[:, :5]).sum(axis=1) + rng.normal(0, 0.1, size=20000)).astype(np.float32)
+    m = lb.LBRegressor(n_estimators=5, learning_rate=0.1, base_models=(lb.Tree(max_depth=6, split_samples=256),),
+                       random_state=0, verbose=1)
+    m.fit(dev(X), dev(y))
+    assert all(a > b for a, b in zip(m.train_metric_, m.train_metric_[1:]))
+    # replay round 0 with the oracle
+    rs = np.random.RandomState(0)
+    seed = rs.randint(0, 2 ** 31)
+    y64 = y.astype(np.float64)[:, None]
+    g = (np.full_like(y64, y64.mean()) - y64) * 0.1
+    want = oracle.build_tree(X, g, np.ones_like(g), max_depth=6, split_samples=256, seed=seed, mode="Q")
+    assert np.array_equal(m[0].feature.cpu().numpy(), want.feature)
+    assert np.allclose(m[0].leaf_value.cpu().numpy(), want.leaf_value, rtol=1e-9, atol=1e-12)
+
+
+def test_classifier_multiclass(lb):
+    rng = np.random.default_rng(2)
+    X = rng.normal(size=(5000, 20)).astype(np.float32)
+    W = rng.normal(size=(10, 4))
+    y = np.argmax(X[:, :10] @ W + rng.normal(0, 0.5, size=(5000, 4)), axis=1)
+    m = lb.LBClassifier(n_estimators=5, base_models=(lb.Tree(max_depth=4),), random_state=1, verbose=1)
+    m.fit(dev(X), dev(y))
+    assert all(a > b for a, b in zip(m.train_metric_, m.train_metric_[1:]))
+    proba = m.predict_proba(dev(X))
+    assert torch.allclose(proba.sum(dim=1), torch.ones(5000, dtype=torch.float64, device="cuda"))
+    assert (m.predict(dev(X)).cpu().numpy() == y).mean() > 0.5
+
+
+def test_bad_arguments_are_errors(lb):
+    from legateboost_b200.tree import build_tree_arrays
+
+    X = dev(np.zeros((10, 3), dtype=np.float32))
+    g = dev(np.zeros((10, 1)))
+    with pytest.raises(lb.library.LbkError):
+        build_tree_arrays(X, g, g, max_depth=2, split_samples=5000, seed=0, row_offset=0, dataset_rows=10)
+    with pytest.raises(lb.library.LbkError):
+        build_tree_arrays(X, g, g, max_depth=2, split_samples=16, seed=0, row_offset=5, dataset_rows=10)
