@@ -89,7 +89,8 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
   // quantised pairs and root sums
   QuantParams* qp = s.alloc<QuantParams>(1);
   int2* gpair     = s.alloc<int2>(static_cast<size_t>(N) * K);
-  Quantise(ctx, s, g, h, ldg, a.row_offset, N, K, a.seed, gpair, tree.node_sums, qp, stream);
+  int* max_abs    = s.alloc<int>(2);
+  Quantise(ctx, s, g, h, ldg, a.row_offset, N, K, a.seed, gpair, tree.node_sums, qp, max_abs, stream);
   RootLeaf(tree, K, qp, a.l1_regularization, a.l2_regularization, stream);
 
   // histogram cache rule (reference: build_tree.cu:1000-1017); identical on every rank
@@ -189,6 +190,7 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
       lv.row_ptr              = row_ptr;
       lv.gpair                = gpair;
       lv.gpair_f              = nullptr;
+      lv.max_abs              = max_abs;
       lv.row_index            = rows_a;
       lv.seg                  = seg_a;
       lv.n_nodes              = n_nodes;
@@ -399,7 +401,8 @@ int lbk_quantise(lbk_context* ctx, const double* g, const double* h, int64_t ldg
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     lbk::Scratch s(ctx, stream);
     lbk::Quantise(ctx, s, g, h, ldg, row_offset, n_local_rows, n_outputs, seed, reinterpret_cast<int2*>(gpair),
-                  reinterpret_cast<lbk::GPairI64*>(root_sums), reinterpret_cast<lbk::QuantParams*>(scale), stream);
+                  reinterpret_cast<lbk::GPairI64*>(root_sums), reinterpret_cast<lbk::QuantParams*>(scale),
+                  s.alloc<int>(2), stream);
   });
 }
 
@@ -461,6 +464,7 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
     lv.row_ptr              = row_ptr;
     lv.gpair                = a->mode == 0 ? static_cast<const int2*>(gp) : nullptr;
     lv.gpair_f              = a->mode == 1 ? static_cast<const float2*>(gp) : nullptr;
+    lv.max_abs              = nullptr;
     lv.row_index            = row_index;
     lv.seg                  = seg;
     lv.n_nodes              = a->n_nodes;

@@ -12,25 +12,39 @@
 //     one row at a time with ONE LANE PER FEATURE, and the private histogram is laid out
 //     [bin][lane]: lane l always hits shared-memory bank l, so the two atomics a warp issues per
 //     row are conflict free whatever the bins are, and no two lanes of a warp share an address;
-//   * the row index and the quantised pair of a row are staged once per 512 rows into shared
-//     memory (coalesced index load, one gather per row) and re-read by broadcast;
-//   * accumulation is in int32 like the reference, but guarded: the sum of |q| over everything
-//     accumulated since the last flush is tracked per block and the private histogram is flushed
-//     before it could reach 2^31, so no partial sum can wrap;
+//   * the kernel is bound by the shared-memory instruction pipe (two atomics per row and warp are
+//     unavoidable: 64-bit and float shared atomics are compare-and-swap loops on this part), so
+//     everything else a row needs comes from ONE 16-byte shared load: rows are staged as 64-byte
+//     records of four chunks [8 bin bytes | grad | hess], the eight lanes that own those bins read
+//     their chunk together;
+//   * staging is software pipelined through registers: the rows of a node are scattered, so
+//     every 32-byte row of a group is its own gather; each thread fetches 16 bin bytes (and the
+//     row's pair) two tiles ahead with L1-bypassing loads and writes them into the record format
+//     one tile later, so a whole 256-row tile per block is always in flight while another is
+//     consumed (cp.async of 8-byte pieces through the small L1 left beside 224 KB of shared
+//     memory was measured 8x slower);
+//   * accumulation is in int32 like the reference, but guarded: with m = the largest |q| of the
+//     call, at most floor((2^31-1)/m) rows are accumulated between flushes, so no partial sum can
+//     wrap whatever the bins are;
 //   * work is cut into (node, row chunk, feature group, output) tickets sized on the device so
 //     that every level gives each resident block about two tickets; blocks draw tickets from an
-//     atomic counter (persistent grid = 3 blocks per SM, limited by 72 KB of shared memory);
+//     atomic counter (persistent grid, two 512-thread blocks per SM at 256 bins);
 //   * a node whose rows fit one chunk owns its output region and flushes with plain stores;
 //     otherwise the flush uses 64-bit global atomics; chunks of <= 128 rows skip shared memory.
+#include <cstdlib>
+
 #include "device_utils.cuh"
 #include "internal.h"
 
 namespace lbk {
 namespace {
 
-constexpr int kHistThreads = 256;
+constexpr int kHistThreads = 512;
 constexpr int kHistWarps   = kHistThreads / 32;
-constexpr int kStageRows   = 512;   // rows staged per sub-tile
+constexpr int kTileRows    = 32;    // rows per staged batch (one batch per warp)
+constexpr int kRecBytes    = 64;    // staged record: 4 x [8 bins | grad | hess]
+constexpr int kTileBytes   = kTileRows * kRecBytes;
+constexpr int kBuffers     = kHistWarps;  // one batch buffer per warp
 constexpr int kDirectRows  = 128;   // chunks up to this size go straight to global atomics
 constexpr int kMinChunk    = 2048;
 constexpr int kSmemBins    = 256;   // bins per feature held by the private histogram
@@ -46,16 +60,38 @@ struct HistParams {
   const int32_t* slot_of_node;  // may be null = identity
   int n_nodes;
   const int32_t* chunk_off;  // [n_nodes+1]
-  const int32_t* plan;       // [0] rows per chunk, [1] total chunks
+  const int32_t* plan;       // [0] rows per chunk, [1] total chunks, [3] rows between flushes
   unsigned int* ticket;
   void* out;
 };
 
+// largest |grad| and |hess| of a set of quantised pairs (for the stage-level entry point; the
+// tree builder gets them from the quantiser)
+__global__ void k_max_abs(const int2* __restrict__ gpair, int64_t n, int* __restrict__ max_abs)
+{
+  int mg = 0, mh = 0;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int2 v = gpair[i];
+    // |INT32_MIN| does not fit: saturate
+    mg = max(mg, v.x == INT32_MIN ? INT32_MAX : abs(v.x));
+    mh = max(mh, v.y == INT32_MIN ? INT32_MAX : abs(v.y));
+  }
+  for (int off = 16; off >= 1; off >>= 1) {
+    mg = max(mg, __shfl_down_sync(0xffffffffu, mg, off));
+    mh = max(mh, __shfl_down_sync(0xffffffffu, mh, off));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicMax(max_abs, mg);
+    atomicMax(max_abs + 1, mh);
+  }
+}
+
 // Single block: rows per chunk for this level and the chunk offsets of every built node.
 __global__ void __launch_bounds__(1024)
   k_hist_plan(const int32_t* __restrict__ seg, const int32_t* __restrict__ slot_of_node, int n_nodes, int GK,
-              int target_tickets, int32_t* __restrict__ chunk_off, int32_t* __restrict__ plan,
-              unsigned int* __restrict__ ticket)
+              int target_tickets, const int* __restrict__ max_abs, int32_t* __restrict__ chunk_off,
+              int32_t* __restrict__ plan, unsigned int* __restrict__ ticket)
 {
   __shared__ long long red[32];
   __shared__ int wsum[32];
@@ -75,7 +111,7 @@ __global__ void __launch_bounds__(1024)
     for (int w = 0; w < (blockDim.x >> 5); ++w) total += red[w];
     long long ch = (total * GK + target_tickets - 1) / target_tickets;
     if (ch < kMinChunk) ch = kMinChunk;
-    ch = (ch + kStageRows - 1) / kStageRows * kStageRows;
+    ch = (ch + kTileRows - 1) / kTileRows * kTileRows;
     if (ch > (1ll << 30)) ch = 1ll << 30;
     ch_s  = static_cast<int>(ch);
     carry = 0;
@@ -117,6 +153,9 @@ __global__ void __launch_bounds__(1024)
   if (tid == 0) {
     plan[0] = ch;
     plan[1] = carry;
+    int m   = 1;
+    if (max_abs) m = max(1, max(max_abs[0], max_abs[1]));
+    plan[3] = max_abs ? 2147483647 / m : 2147483647;
     *ticket = 0;
   }
 }
@@ -165,15 +204,15 @@ __global__ void __launch_bounds__(kHistThreads)
   using in_t   = typename A::in_t;
   using out_t  = typename A::out_t;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  smem_t* hg   = reinterpret_cast<smem_t*>(smem_raw);
-  smem_t* hh   = hg + (kSmem ? p.mb * kGroup : 0);
-  int4* stage  = reinterpret_cast<int4*>(hh + (kSmem ? p.mb * kGroup : 0));
+  smem_t* hg           = reinterpret_cast<smem_t*>(smem_raw);
+  smem_t* hh           = hg + (kSmem ? p.mb * kGroup : 0);
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(hh + (kSmem ? p.mb * kGroup : 0));
   __shared__ unsigned int s_ticket;
-  __shared__ long long s_red[2][kHistWarps];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int CH           = p.plan[0];
   const int total_chunks = p.plan[1];
+  const int rows_safe    = p.plan[3];
   const long long total  = static_cast<long long>(total_chunks) * p.G * p.K;
   const BinT* bins       = static_cast<const BinT*>(p.bins);
   const in_t* gpair      = static_cast<const in_t*>(p.gpair);
@@ -205,20 +244,20 @@ __global__ void __launch_bounds__(kHistThreads)
     const int fbeg    = active ? p.row_ptr[feat] : 0;
     const int fbins   = active ? p.row_ptr[feat + 1] - fbeg : 0;
     out_t* obase      = out + (static_cast<int64_t>(slot) * p.K + k) * p.B + fbeg;
-    const BinT* gbins = bins + static_cast<int64_t>(g) * p.n_rows * kGroup + lane;
+    const BinT* gbins = bins + static_cast<int64_t>(g) * p.n_rows * kGroup;
 
     auto direct_rows = [&](int b, int e) {
       for (int r = b + warp; r < e; r += kHistWarps) {
         const int ridx = p.row_index[r];
         const in_t v   = gpair[static_cast<int64_t>(ridx) * p.K + k];
         if (active) {
-          const int bin = gbins[static_cast<int64_t>(ridx) * kGroup];
+          const int bin = gbins[static_cast<int64_t>(ridx) * kGroup + lane];
           A::add_global(obase + bin, v.x, v.y);
         }
       }
     };
 
-    if (!kSmem || re - rb <= kDirectRows) {
+    if (!kSmem || re - rb <= kDirectRows || rows_safe < kTileRows) {
       direct_rows(rb, re);
       continue;
     }
@@ -235,85 +274,87 @@ __global__ void __launch_bounds__(kHistThreads)
         }
       }
     };
-    for (int e = tid; e < hist_words; e += kHistThreads) {
-      hg[e] = smem_t(0);
-      hh[e] = smem_t(0);
-    }
-    long long run_g = 0, run_h = 0;
-    for (int st = rb; st < re; st += kStageRows) {
-      const int n = min(kStageRows, re - st);
-      __syncthreads();  // previous sub-tile fully consumed (and zeroing done) before restaging
-      long long ag = 0, ah = 0;
-      for (int i = tid; i < n; i += kHistThreads) {
-        const int ridx = p.row_index[st + i];
-        const in_t v   = gpair[static_cast<int64_t>(ridx) * p.K + k];
-        int4 rec;
-        rec.x = ridx;
-        if (kFloat) {
-          rec.y = __float_as_int(v.x);
-          rec.z = __float_as_int(v.y);
-        } else {
-          rec.y = v.x;
-          rec.z = v.y;
-          ag += llabs(static_cast<long long>(v.x));
-          ah += llabs(static_cast<long long>(v.y));
-        }
-        rec.w    = 0;
-        stage[i] = rec;
+    auto zero = [&]() {
+      for (int e = tid; e < hist_words; e += kHistThreads) {
+        hg[e] = smem_t(0);
+        hh[e] = smem_t(0);
       }
-      bool direct_tile = false;
-      if (!kFloat) {
-        for (int off = 16; off >= 1; off >>= 1) {
-          ag += __shfl_down_sync(0xffffffffu, ag, off);
-          ah += __shfl_down_sync(0xffffffffu, ah, off);
-        }
-        if (lane == 0) {
-          s_red[0][warp] = ag;
-          s_red[1][warp] = ah;
-        }
+    };
+    zero();
+    __syncthreads();
+
+    // Every warp runs its own pipeline over 32-row batches of the chunk (no block barrier inside):
+    // lane l stages chunk l%4 of rows l/4, l/4+8, l/4+16, l/4+24 of the batch: 8 bin bytes plus the
+    // row's pair, fetched with L1-bypassing loads one batch ahead (row ids two batches ahead) and
+    // written as one 16-byte chunk each, so a warp store covers 512 contiguous bytes.
+    unsigned char* wt  = tiles + warp * (32 * kRecBytes);
+    const int qoff     = (lane >> 3) * 16;  // this lane's chunk inside a record when consuming
+    const int shift    = (lane & 3) * 8;
+    const bool hiw     = (lane & 4) != 0;
+    const int seg_rows = rows_safe >= (1 << 30) ? (1 << 30) : (rows_safe & ~31);
+    for (int sb = rb; sb < re; sb += seg_rows) {
+      const int se = min(re, sb + seg_rows);
+      if (sb > rb) {
         __syncthreads();
-        long long tg = 0, th = 0;
+        flush(true);
+        use_atomics = true;
+        __syncthreads();
+        zero();
+        __syncthreads();
+      }
+      const int nb = (se - sb + 31) >> 5;
+      int ridx[4], ridx_n[4];
+      uint2 vb[4];
+      int2 vg[4];
+      auto load_ridx = [&](int batch, int (&out)[4]) {
 #pragma unroll
-        for (int w = 0; w < kHistWarps; ++w) {
-          tg += s_red[0][w];
-          th += s_red[1][w];
+        for (int j = 0; j < 4; ++j) {
+          const int r = sb + batch * 32 + (lane >> 2) + 8 * j;
+          out[j]      = (batch < nb && r < se) ? __ldcg(p.row_index + r) : -1;
         }
-        const long long lim = 2147483647ll;
-        if (tg > lim || th > lim) {
-          direct_tile = true;  // this sub-tile alone could wrap an int32: add it with 64-bit atomics
-        } else if (run_g + tg > lim || run_h + th > lim) {
-          flush(true);
-          use_atomics = true;
-          __syncthreads();
-          for (int e = tid; e < hist_words; e += kHistThreads) {
-            hg[e] = smem_t(0);
-            hh[e] = smem_t(0);
+      };
+      auto load_data = [&](const int (&rid)[4]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (rid[j] >= 0) {
+            vb[j] = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(gbins) +
+                                                          static_cast<int64_t>(rid[j]) * kGroup + (lane & 3) * 8));
+            vg[j] = __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid[j]) * p.K + k));
           }
-          run_g = tg;
-          run_h = th;
-        } else {
-          run_g += tg;
-          run_h += th;
         }
-        if (direct_tile) use_atomics = true;
+      };
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        vb[j] = make_uint2(0, 0);
+        vg[j] = make_int2(0, 0);
       }
-      __syncthreads();
-      if (direct_tile) {
-        direct_rows(st, st + n);
-        continue;
-      }
-#pragma unroll 4
-      for (int r = warp; r < n; r += kHistWarps) {
-        const int4 rec = stage[r];
-        if (active) {
-          const int bin = gbins[static_cast<int64_t>(rec.x) * kGroup];
-          const int idx = bin * kGroup + lane;
-          if (kFloat) {
-            atomicAdd(reinterpret_cast<float*>(hg) + idx, __int_as_float(rec.y));
-            atomicAdd(reinterpret_cast<float*>(hh) + idx, __int_as_float(rec.z));
-          } else {
-            atomicAdd(reinterpret_cast<int*>(hg) + idx, rec.y);
-            atomicAdd(reinterpret_cast<int*>(hh) + idx, rec.z);
+      load_ridx(warp, ridx);
+      load_data(ridx);
+      load_ridx(warp + kHistWarps, ridx_n);
+      for (int b = warp; b < nb; b += kHistWarps) {
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          reinterpret_cast<int4*>(wt)[lane + 32 * j] =
+            make_int4(static_cast<int>(vb[j].x), static_cast<int>(vb[j].y), vg[j].x, vg[j].y);
+        __syncwarp();
+        load_data(ridx_n);                            // batch b + 16
+        load_ridx(b + 2 * kHistWarps, ridx_n);        // row ids of batch b + 32
+        const int n = min(32, se - (sb + b * 32));
+        const unsigned char* tb = wt + qoff;
+#pragma unroll 8
+        for (int r = 0; r < n; ++r) {
+          const int4 rec = *reinterpret_cast<const int4*>(tb + r * kRecBytes);
+          if (active) {
+            const unsigned w = hiw ? static_cast<unsigned>(rec.y) : static_cast<unsigned>(rec.x);
+            const int idx    = static_cast<int>((w >> shift) & 255u) * kGroup + lane;
+            if (kFloat) {
+              atomicAdd(reinterpret_cast<float*>(hg) + idx, __int_as_float(rec.z));
+              atomicAdd(reinterpret_cast<float*>(hh) + idx, __int_as_float(rec.w));
+            } else {
+              atomicAdd(reinterpret_cast<int*>(hg) + idx, rec.z);
+              atomicAdd(reinterpret_cast<int*>(hh) + idx, rec.w);
+            }
           }
         }
       }
@@ -431,13 +472,28 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
-  const size_t smem    = smem_path ? static_cast<size_t>(p.mb) * kGroup * 8 + kStageRows * sizeof(int4) : 0;
-  int blocks_per_sm    = smem_path ? static_cast<int>((ctx->max_smem_optin) / (smem + 1024)) : 8;
-  if (blocks_per_sm > 8) blocks_per_sm = 8;
+  const size_t smem    = smem_path ? static_cast<size_t>(p.mb) * kGroup * 8 + kBuffers * kTileBytes : 0;
+  int blocks_per_sm    = smem_path ? static_cast<int>((ctx->max_smem_optin) / (smem + 1024)) : 4;
+  if (blocks_per_sm > 2048 / kHistThreads) blocks_per_sm = 2048 / kHistThreads;
   if (blocks_per_sm < 1) blocks_per_sm = 1;
   const int grid = ctx->sm_count * blocks_per_sm;
 
-  k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, p.G * p.K, grid * 2, chunk_off, plan, p.ticket);
+  const int* max_abs = lv.max_abs;
+  if (!lv.float_mode && max_abs == nullptr) {
+    // the caller gave quantised pairs without their largest magnitude: find it
+    int* m = s.alloc<int>(2);
+    LBK_CUDA(cudaMemsetAsync(m, 0, 2 * sizeof(int), stream));
+    const int64_t n = lv.n_rows * lv.K;
+    if (n > 0) {
+      k_max_abs<<<ctx->sm_count * 8, 256, 0, stream>>>(lv.gpair, n, m);
+      LBK_LAUNCH_CHECK();
+    }
+    max_abs = m;
+  }
+  double mult = 2.0;
+  if (const char* e = getenv("LBK_HIST_TICKETS_PER_BLOCK")) mult = atof(e);
+  k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, p.G * p.K, static_cast<int>(grid * mult) + 1,
+                                      lv.float_mode ? nullptr : max_abs, chunk_off, plan, p.ticket);
   LBK_LAUNCH_CHECK();
 
 #define LBK_HIST_LAUNCH(BinT, FL, SM)                                                                              \

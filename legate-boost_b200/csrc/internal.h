@@ -124,7 +124,7 @@ void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposal
 // quantise.cu
 void Quantise(lbk_context* ctx, Scratch& s, const double* g, const double* h, int64_t ldg, int64_t row_offset,
               int64_t n_local, int K, int seed, int2* gpair, GPairI64* root_sums, QuantParams* params,
-              cudaStream_t stream);
+              int* max_abs /* device [2] */, cudaStream_t stream);
 // histogram.cu
 struct HistLevel {
   const void* bins;
@@ -135,6 +135,7 @@ struct HistLevel {
   const int32_t* row_ptr;
   const int2* gpair;       // int path
   const float2* gpair_f;   // float path
+  const int* max_abs;      // device [2]: largest |grad|, |hess| of gpair (null: computed by the call)
   const int32_t* row_index;
   const int32_t* seg;      // [n_level_nodes+1] offsets for nodes node_begin.. of the level range
   int n_nodes;             // nodes in this batch

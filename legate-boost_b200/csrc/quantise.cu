@@ -91,11 +91,12 @@ __global__ void k_make_scale(const double* __restrict__ sums /* g,h */, QuantPar
 __global__ void __launch_bounds__(256)
   k_quantise(const double* __restrict__ g, const double* __restrict__ h, int64_t ldg, int64_t row_offset,
              int64_t n_local, int K, long long seed, const QuantParams* __restrict__ qp_ptr,
-             int2* __restrict__ gpair, GPairI64* __restrict__ root_sums)
+             int2* __restrict__ gpair, GPairI64* __restrict__ root_sums, int* __restrict__ max_abs)
 {
   __shared__ long long red[2][8];
   const QuantParams qp = *qp_ptr;
   const int tid        = threadIdx.x;
+  int mg = 0, mh = 0;
   for (int k = 0; k < K; ++k) {
     long long sg = 0, sh = 0;
     for (int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x) + tid; row < n_local;
@@ -106,6 +107,8 @@ __global__ void __launch_bounds__(256)
       gpair[row * K + k] = q;
       sg += q.x;
       sh += q.y;
+      mg = max(mg, q.x == INT32_MIN ? INT32_MAX : abs(q.x));
+      mh = max(mh, q.y == INT32_MIN ? INT32_MAX : abs(q.y));
     }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) {
@@ -128,13 +131,21 @@ __global__ void __launch_bounds__(256)
     }
     __syncthreads();
   }
+  for (int off = 16; off >= 1; off >>= 1) {
+    mg = max(mg, __shfl_down_sync(0xffffffffu, mg, off));
+    mh = max(mh, __shfl_down_sync(0xffffffffu, mh, off));
+  }
+  if ((tid & 31) == 0) {
+    atomicMax(max_abs, mg);
+    atomicMax(max_abs + 1, mh);
+  }
 }
 
 }  // namespace
 
 void Quantise(lbk_context* ctx, Scratch& s, const double* g, const double* h, int64_t ldg, int64_t row_offset,
               int64_t n_local, int K, int seed, int2* gpair, GPairI64* root_sums, QuantParams* params,
-              cudaStream_t stream)
+              int* max_abs, cudaStream_t stream)
 {
   // canonical |g|,|h| sums
   int64_t n        = n_local * K;
@@ -172,12 +183,13 @@ void Quantise(lbk_context* ctx, Scratch& s, const double* g, const double* h, in
   k_make_scale<<<1, 1, 0, stream>>>(sums, params);
   LBK_LAUNCH_CHECK();
   LBK_CUDA(cudaMemsetAsync(root_sums, 0, sizeof(GPairI64) * K, stream));
+  LBK_CUDA(cudaMemsetAsync(max_abs, 0, 2 * sizeof(int), stream));
   if (n_local > 0) {
     int64_t blocks = (n_local + 255) / 256;
     const int64_t cap = static_cast<int64_t>(ctx->sm_count) * 8;
     if (blocks > cap) blocks = cap;
     k_quantise<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(g, h, ldg, row_offset, n_local, K,
-                                                                  static_cast<long long>(seed), params, gpair, root_sums);
+                                                                  static_cast<long long>(seed), params, gpair, root_sums, max_abs);
     LBK_LAUNCH_CHECK();
   }
   AllReduce(ctx, root_sums, static_cast<size_t>(2) * K, LBK_I64, LBK_SUM, stream);
