@@ -65,6 +65,22 @@ struct HistParams {
   void* out;
 };
 
+__device__ inline unsigned SmemAddr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+__device__ inline int4 LdsV4(unsigned addr)
+{
+  int4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ inline void RedShared(unsigned addr, int v)
+{
+  asm volatile("red.shared.add.s32 [%0], %1;\n" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ inline void RedShared(unsigned addr, float v)
+{
+  asm volatile("red.shared.add.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
+
 // largest |grad| and |hess| of a set of quantised pairs (for the stage-level entry point; the
 // tree builder gets them from the quantiser)
 __global__ void k_max_abs(const int2* __restrict__ gpair, int64_t n, int* __restrict__ max_abs)
@@ -196,7 +212,7 @@ struct Acc<true> {
 };
 
 template <typename BinT, bool kFloat, bool kSmem>
-__global__ void __launch_bounds__(kHistThreads)
+__global__ void __launch_bounds__(kHistThreads, 2)
   k_hist(const HistParams p)
 {
   using A      = Acc<kFloat>;
@@ -205,8 +221,9 @@ __global__ void __launch_bounds__(kHistThreads)
   using out_t  = typename A::out_t;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   smem_t* hg           = reinterpret_cast<smem_t*>(smem_raw);
-  smem_t* hh           = hg + (kSmem ? p.mb * kGroup : 0);
-  unsigned char* tiles = reinterpret_cast<unsigned char*>(hh + (kSmem ? p.mb * kGroup : 0));
+  constexpr int hist_rows = kSmem ? kSmemBins : 0;  // every byte value is a valid row
+  smem_t* hh           = hg + hist_rows * kGroup;
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(hh + hist_rows * kGroup);
   __shared__ unsigned int s_ticket;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -288,9 +305,10 @@ __global__ void __launch_bounds__(kHistThreads)
     // row's pair, fetched with L1-bypassing loads one batch ahead (row ids two batches ahead) and
     // written as one 16-byte chunk each, so a warp store covers 512 contiguous bytes.
     unsigned char* wt  = tiles + warp * (32 * kRecBytes);
-    const int qoff     = (lane >> 3) * 16;  // this lane's chunk inside a record when consuming
-    const int shift    = (lane & 3) * 8;
-    const bool hiw     = (lane & 4) != 0;
+    const unsigned tb_s    = SmemAddr(wt) + (lane >> 3) * 16;  // this lane's chunk inside a record
+    const unsigned bsel    = (lane & 7) * 0x1111u;             // byte (lane % 8) of the chunk's 8 bins
+    const unsigned hg_lane = SmemAddr(hg) + lane * 4;
+    const unsigned hh_off  = static_cast<unsigned>(hist_rows) * kGroup * 4;
     const int seg_rows = rows_safe >= (1 << 30) ? (1 << 30) : (rows_safe & ~31);
     for (int sb = rb; sb < re; sb += seg_rows) {
       const int se = min(re, sb + seg_rows);
@@ -341,21 +359,31 @@ __global__ void __launch_bounds__(kHistThreads)
         load_data(ridx_n);                            // batch b + 16
         load_ridx(b + 2 * kHistWarps, ridx_n);        // row ids of batch b + 32
         const int n = min(32, se - (sb + b * 32));
-        const unsigned char* tb = wt + qoff;
-#pragma unroll 8
-        for (int r = 0; r < n; ++r) {
-          const int4 rec = *reinterpret_cast<const int4*>(tb + r * kRecBytes);
-          if (active) {
-            const unsigned w = hiw ? static_cast<unsigned>(rec.y) : static_cast<unsigned>(rec.x);
-            const int idx    = static_cast<int>((w >> shift) & 255u) * kGroup + lane;
-            if (kFloat) {
-              atomicAdd(reinterpret_cast<float*>(hg) + idx, __int_as_float(rec.z));
-              atomicAdd(reinterpret_cast<float*>(hh) + idx, __int_as_float(rec.w));
-            } else {
-              atomicAdd(reinterpret_cast<int*>(hg) + idx, rec.z);
-              atomicAdd(reinterpret_cast<int*>(hh) + idx, rec.w);
-            }
+        // One 16-byte shared load gives a lane its bin byte and the row's pair; the two
+        // reductions go to hist[bin][lane] (bank = lane).  Lanes beyond the last feature read bin
+        // 0 of their padding byte and accumulate into a column that is never flushed.
+        auto consume = [&](const int4& rec) {
+          const unsigned bin  = __byte_perm(static_cast<unsigned>(rec.x), static_cast<unsigned>(rec.y), bsel) & 255u;
+          const unsigned addr = hg_lane + bin * (kGroup * 4);
+          if (kFloat) {
+            RedShared(addr, __int_as_float(rec.z));
+            RedShared(addr + hh_off, __int_as_float(rec.w));
+          } else {
+            RedShared(addr, rec.z);
+            RedShared(addr + hh_off, rec.w);
           }
+        };
+        if (n == 32) {
+#pragma unroll
+          for (int r0 = 0; r0 < 32; r0 += 8) {
+            int4 rec[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rec[i] = LdsV4(tb_s + (r0 + i) * kRecBytes);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) consume(rec[i]);
+          }
+        } else {
+          for (int r = 0; r < n; ++r) consume(LdsV4(tb_s + r * kRecBytes));
         }
       }
     }
@@ -472,7 +500,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
-  const size_t smem    = smem_path ? static_cast<size_t>(p.mb) * kGroup * 8 + kBuffers * kTileBytes : 0;
+  const size_t smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * 8 + kBuffers * kTileBytes : 0;
   int blocks_per_sm    = smem_path ? static_cast<int>((ctx->max_smem_optin) / (smem + 1024)) : 4;
   if (blocks_per_sm > 2048 / kHistThreads) blocks_per_sm = 2048 / kHistThreads;
   if (blocks_per_sm < 1) blocks_per_sm = 1;
