@@ -42,9 +42,8 @@ namespace {
 constexpr int kHistThreads = 512;
 constexpr int kHistWarps   = kHistThreads / 32;
 constexpr int kTileRows    = 32;    // rows per staged batch (one batch per warp)
-constexpr int kRecBytes    = 64;    // staged record: 4 x [8 bins | grad | hess]
-constexpr int kTileBytes   = kTileRows * kRecBytes;
-constexpr int kBuffers     = kHistWarps;  // one batch buffer per warp
+constexpr int kBatchBytes  = kTileRows * (kGroup + 8);  // 32 bin bytes + one pair per row
+constexpr int kWarpRingBytes = 2 * kBatchBytes;         // two batches per warp
 constexpr int kDirectRows  = 128;   // chunks up to this size go straight to global atomics
 constexpr int kMinChunk    = 2048;
 constexpr int kSmemBins    = 256;   // bins per feature held by the private histogram
@@ -65,6 +64,32 @@ struct HistParams {
   void* out;
 };
 
+__device__ inline void CpAsync16(unsigned smem_dst, const void* gsrc)
+{
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ inline void CpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ inline void CpAsyncWait()
+{
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ inline unsigned LdsU8(unsigned addr)
+{
+  unsigned v;
+  asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ inline int2 LdsV2(unsigned addr)
+{
+  int2 v;
+  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+  return v;
+}
+__device__ inline void StsV2(unsigned addr, int2 v)
+{
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
+}
 __device__ inline unsigned SmemAddr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 __device__ inline int4 LdsV4(unsigned addr)
 {
@@ -300,15 +325,17 @@ __global__ void __launch_bounds__(kHistThreads, 2)
     zero();
     __syncthreads();
 
-    // Every warp runs its own pipeline over 32-row batches of the chunk (no block barrier inside):
-    // lane l stages chunk l%4 of rows l/4, l/4+8, l/4+16, l/4+24 of the batch: 8 bin bytes plus the
-    // row's pair, fetched with L1-bypassing loads one batch ahead (row ids two batches ahead) and
-    // written as one 16-byte chunk each, so a warp store covers 512 contiguous bytes.
-    unsigned char* wt  = tiles + warp * (32 * kRecBytes);
-    const unsigned tb_s    = SmemAddr(wt) + (lane >> 3) * 16;  // this lane's chunk inside a record
-    const unsigned bsel    = (lane & 7) * 0x1111u;             // byte (lane % 8) of the chunk's 8 bins
-    const unsigned hg_lane = SmemAddr(hg) + lane * 4;
-    const unsigned hh_off  = static_cast<unsigned>(hist_rows) * kGroup * 4;
+    // Every warp runs its own pipeline over 32-row batches of the chunk (no block barrier inside).
+    // Per warp there is a two-deep ring in shared memory; a batch is 32 rows x 32 bin bytes plus
+    // 32 pairs.  While batch b is consumed, the bins of the warp's next batch travel from global
+    // to shared memory asynchronously (cp.async, 16 bytes per lane: one instruction moves 16 rows),
+    // its pairs sit in registers (one gather per lane) and the row ids of the batch after that
+    // are being loaded.
+    unsigned char* ring     = tiles + warp * kWarpRingBytes;
+    const unsigned ring_s   = SmemAddr(ring);
+    const unsigned hg_lane  = SmemAddr(hg) + lane * 4;
+    const unsigned hh_off   = static_cast<unsigned>(hist_rows) * kGroup * 4;
+    const unsigned char* gb = reinterpret_cast<const unsigned char*>(gbins);
     const int seg_rows = rows_safe >= (1 << 30) ? (1 << 30) : (rows_safe & ~31);
     for (int sb = rb; sb < re; sb += seg_rows) {
       const int se = min(re, sb + seg_rows);
@@ -321,71 +348,73 @@ __global__ void __launch_bounds__(kHistThreads, 2)
         __syncthreads();
       }
       const int nb = (se - sb + 31) >> 5;
-      int ridx[4], ridx_n[4];
-      uint2 vb[4];
-      int2 vg[4];
-      auto load_ridx = [&](int batch, int (&out)[4]) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int r = sb + batch * 32 + (lane >> 2) + 8 * j;
-          out[j]      = (batch < nb && r < se) ? __ldcg(p.row_index + r) : -1;
-        }
+      auto load_rid = [&](int batch) -> int {
+        const int r = sb + batch * 32 + lane;
+        return (batch < nb && r < se) ? __ldcg(p.row_index + r) : -1;
       };
-      auto load_data = [&](const int (&rid)[4]) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (rid[j] >= 0) {
-            vb[j] = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned char*>(gbins) +
-                                                          static_cast<int64_t>(rid[j]) * kGroup + (lane & 3) * 8));
-            vg[j] = __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid[j]) * p.K + k));
-          }
-        }
+      auto load_pair = [&](int rid) -> int2 {
+        return rid >= 0 ? __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid) * p.K + k))
+                        : make_int2(0, 0);
       };
+      auto issue_bins = [&](int rid, int buf) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        vb[j] = make_uint2(0, 0);
-        vg[j] = make_int2(0, 0);
-      }
-      load_ridx(warp, ridx);
-      load_data(ridx);
-      load_ridx(warp + kHistWarps, ridx_n);
+        for (int j = 0; j < 2; ++j) {
+          const int piece = lane + 32 * j;  // row = piece / 2, half = piece % 2
+          const int rsrc  = __shfl_sync(0xffffffffu, rid, piece >> 1);
+          if (rsrc >= 0)
+            CpAsync16(ring_s + buf * kBatchBytes + piece * 16, gb + static_cast<int64_t>(rsrc) * kGroup + (piece & 1) * 16);
+        }
+        CpAsyncCommit();
+      };
+      int rid_next = load_rid(warp);
+      issue_bins(rid_next, 0);
+      int2 gp_cur = load_pair(rid_next);
+      rid_next    = load_rid(warp + kHistWarps);
+      int buf     = 0;
       for (int b = warp; b < nb; b += kHistWarps) {
+        issue_bins(rid_next, buf ^ 1);              // batch b + 16
+        const int2 gp_next = load_pair(rid_next);
+        rid_next           = load_rid(b + 2 * kHistWarps);
+        const unsigned bins_s = ring_s + buf * kBatchBytes;
+        const unsigned gp_s   = bins_s + 32 * kGroup;
+        StsV2(gp_s + lane * 8, gp_cur);
+        CpAsyncWait<1>();
         __syncwarp();
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          reinterpret_cast<int4*>(wt)[lane + 32 * j] =
-            make_int4(static_cast<int>(vb[j].x), static_cast<int>(vb[j].y), vg[j].x, vg[j].y);
-        __syncwarp();
-        load_data(ridx_n);                            // batch b + 16
-        load_ridx(b + 2 * kHistWarps, ridx_n);        // row ids of batch b + 32
         const int n = min(32, se - (sb + b * 32));
-        // One 16-byte shared load gives a lane its bin byte and the row's pair; the two
-        // reductions go to hist[bin][lane] (bank = lane).  Lanes beyond the last feature read bin
-        // 0 of their padding byte and accumulate into a column that is never flushed.
-        auto consume = [&](const int4& rec) {
-          const unsigned bin  = __byte_perm(static_cast<unsigned>(rec.x), static_cast<unsigned>(rec.y), bsel) & 255u;
+        // per row: one byte load (this lane's bin), one broadcast 8-byte load (the pair), two
+        // reductions into hist[bin][lane] (bank = lane).  Lanes beyond the last feature see the
+        // zero padding byte and accumulate into a column that is never flushed.
+        auto consume = [&](unsigned bin, const int2& v) {
           const unsigned addr = hg_lane + bin * (kGroup * 4);
           if (kFloat) {
-            RedShared(addr, __int_as_float(rec.z));
-            RedShared(addr + hh_off, __int_as_float(rec.w));
+            RedShared(addr, __int_as_float(v.x));
+            RedShared(addr + hh_off, __int_as_float(v.y));
           } else {
-            RedShared(addr, rec.z);
-            RedShared(addr + hh_off, rec.w);
+            RedShared(addr, v.x);
+            RedShared(addr + hh_off, v.y);
           }
         };
         if (n == 32) {
 #pragma unroll
           for (int r0 = 0; r0 < 32; r0 += 8) {
-            int4 rec[8];
+            unsigned bin[8];
+            int2 v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) rec[i] = LdsV4(tb_s + (r0 + i) * kRecBytes);
+            for (int i = 0; i < 8; ++i) {
+              bin[i] = LdsU8(bins_s + (r0 + i) * kGroup + lane);
+              v[i]   = LdsV2(gp_s + (r0 + i) * 8);
+            }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) consume(rec[i]);
+            for (int i = 0; i < 8; ++i) consume(bin[i], v[i]);
           }
         } else {
-          for (int r = 0; r < n; ++r) consume(LdsV4(tb_s + r * kRecBytes));
+          for (int r = 0; r < n; ++r) consume(LdsU8(bins_s + r * kGroup + lane), LdsV2(gp_s + r * 8));
         }
+        __syncwarp();
+        gp_cur = gp_next;
+        buf ^= 1;
       }
+      CpAsyncWait<0>();
     }
     __syncthreads();
     flush(use_atomics);
@@ -500,7 +529,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
-  const size_t smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * 8 + kBuffers * kTileBytes : 0;
+  const size_t smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * 8 + kHistWarps * kWarpRingBytes : 0;
   int blocks_per_sm    = smem_path ? static_cast<int>((ctx->max_smem_optin) / (smem + 1024)) : 4;
   if (blocks_per_sm > 2048 / kHistThreads) blocks_per_sm = 2048 / kHistThreads;
   if (blocks_per_sm < 1) blocks_per_sm = 1;
