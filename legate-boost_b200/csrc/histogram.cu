@@ -12,23 +12,24 @@
 //     one row at a time with ONE LANE PER FEATURE, and the private histogram is laid out
 //     [bin][lane]: lane l always hits shared-memory bank l, so the two atomics a warp issues per
 //     row are conflict free whatever the bins are, and no two lanes of a warp share an address;
-//   * the kernel is bound by the shared-memory instruction pipe (two atomics per row and warp are
-//     unavoidable: 64-bit and float shared atomics are compare-and-swap loops on this part), so
-//     everything else a row needs comes from ONE 16-byte shared load: rows are staged as 64-byte
-//     records of four chunks [8 bin bytes | grad | hess], the eight lanes that own those bins read
-//     their chunk together;
-//   * staging is software pipelined through registers: the rows of a node are scattered, so
-//     every 32-byte row of a group is its own gather; each thread fetches 16 bin bytes (and the
-//     row's pair) two tiles ahead with L1-bypassing loads and writes them into the record format
-//     one tile later, so a whole 256-row tile per block is always in flight while another is
-//     consumed (cp.async of 8-byte pieces through the small L1 left beside 224 KB of shared
-//     memory was measured 8x slower);
+//   * the kernel is bound by the load/store pipe of the SM, not by HBM: the two reductions a warp
+//     issues per row are unavoidable (64-bit shared atomics are compare-and-swap loops on this
+//     part), so everything else is kept small: per row one byte load (the lane's bin) and half a
+//     broadcast 16-byte load (the pairs of two rows);
+//   * every warp runs its own pipeline over 32-row batches (no block barrier in the main loop):
+//     the rows of a node are scattered, so each 32-byte row of a group is its own gather; the bins
+//     of the warp's next batch travel global -> shared asynchronously (cp.async.cg, 16 bytes per
+//     lane, one instruction moves 16 rows and bypasses the small L1 left beside the histograms)
+//     into a two-deep per-warp ring, the pairs of that batch wait in one register pair per lane,
+//     and the row ids of the batch after that are being loaded; with 32 warps per SM that keeps
+//     64 KB per SM in flight;
 //   * accumulation is in int32 like the reference, but guarded: with m = the largest |q| of the
 //     call, at most floor((2^31-1)/m) rows are accumulated between flushes, so no partial sum can
 //     wrap whatever the bins are;
-//   * work is cut into (node, row chunk, feature group, output) tickets sized on the device so
-//     that every level gives each resident block about two tickets; blocks draw tickets from an
-//     atomic counter (persistent grid, two 512-thread blocks per SM at 256 bins);
+//   * work is cut into (node, row chunk, feature group, output) tickets sized on the device:
+//     one chunk per node when the level has at least as many (node, group, output) triples as
+//     resident blocks, else chunks that give every resident block about one ticket; blocks draw
+//     tickets from an atomic counter (persistent grid, two 512-thread blocks per SM);
 //   * a node whose rows fit one chunk owns its output region and flushes with plain stores;
 //     otherwise the flush uses 64-bit global atomics; chunks of <= 128 rows skip shared memory.
 #include <cstdlib>
@@ -139,10 +140,12 @@ __global__ void __launch_bounds__(1024)
   __shared__ int carry;
   __shared__ int ch_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // rows to process, with the number of non-empty built nodes in the top 20 bits
   long long rows = 0;
   for (int j = tid; j < n_nodes; j += blockDim.x) {
     const bool built = slot_of_node == nullptr || slot_of_node[j] >= 0;
-    if (built) rows += seg[j + 1] - seg[j];
+    const int r      = seg[j + 1] - seg[j];
+    if (built && r > 0) rows += r + (1ll << 40);
   }
   for (int off = 16; off >= 1; off >>= 1) rows += __shfl_down_sync(0xffffffffu, rows, off);
   if (lane == 0) red[warp] = rows;
@@ -150,7 +153,12 @@ __global__ void __launch_bounds__(1024)
   if (tid == 0) {
     long long total = 0;
     for (int w = 0; w < (blockDim.x >> 5); ++w) total += red[w];
+    const long long nodes = total >> 40;
+    total &= (1ll << 40) - 1;
     long long ch = (total * GK + target_tickets - 1) / target_tickets;
+    // enough nodes to fill the machine: one chunk per node, so that every node is flushed
+    // once, with plain stores
+    if (nodes * GK >= target_tickets) ch = 1ll << 30;
     if (ch < kMinChunk) ch = kMinChunk;
     ch = (ch + kTileRows - 1) / kTileRows * kTileRows;
     if (ch > (1ll << 30)) ch = 1ll << 30;
@@ -398,14 +406,16 @@ __global__ void __launch_bounds__(kHistThreads, 2)
 #pragma unroll
           for (int r0 = 0; r0 < 32; r0 += 8) {
             unsigned bin[8];
-            int2 v[8];
+            int4 v[4];  // one broadcast 16-byte load brings the pairs of two rows
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              bin[i] = LdsU8(bins_s + (r0 + i) * kGroup + lane);
-              v[i]   = LdsV2(gp_s + (r0 + i) * 8);
+            for (int i = 0; i < 8; ++i) bin[i] = LdsU8(bins_s + (r0 + i) * kGroup + lane);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = LdsV4(gp_s + (r0 + 2 * i) * 8);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              consume(bin[2 * i], make_int2(v[i].x, v[i].y));
+              consume(bin[2 * i + 1], make_int2(v[i].z, v[i].w));
             }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) consume(bin[i], v[i]);
           }
         } else {
           for (int r = 0; r < n; ++r) consume(LdsU8(bins_s + r * kGroup + lane), LdsV2(gp_s + r * 8));
@@ -547,7 +557,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
     }
     max_abs = m;
   }
-  double mult = 2.0;
+  double mult = 1.0;
   if (const char* e = getenv("LBK_HIST_TICKETS_PER_BLOCK")) mult = atof(e);
   k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, p.G * p.K, static_cast<int>(grid * mult) + 1,
                                       lv.float_mode ? nullptr : max_abs, chunk_off, plan, p.ticket);
