@@ -203,6 +203,22 @@ typedef struct lbk_histogram_args {
 
 int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* args);
 
+/* The same histogram build for callers that cannot allocate device memory at the time of the
+ * call (inside a host callback on a stream, under a runtime that has already handed out the whole
+ * memory budget, or in a process whose device footprint must stay fixed after start-up).  It has
+ * no counterpart in the reference.  No context is needed and nothing is allocated or freed: the
+ * per-call scratch lives in a fixed array of about 16 KB inside the library image, present once
+ * on every GPU that loads the library until the process exits.
+ * Limits: n_nodes <= LBK_NOALLOC_MAX_NODES, n_features <= LBK_NOALLOC_MAX_FEATURES, device
+ * pointers only (host_buffers = 0); anything larger is rejected with LBK_ERR_ARGUMENT.
+ * The first call on a device looks up the array's device address; make that call before any
+ * stream capture.  All calls on a device share the array, so calls that overlap on the GPU
+ * race: issue them on one stream.  The call returns after the stream has drained; the error text
+ * is read with lbk_last_error(NULL). */
+#define LBK_NOALLOC_MAX_NODES 4096
+#define LBK_NOALLOC_MAX_FEATURES 4096
+int lbk_histogram_noalloc(int device, const lbk_histogram_args* args);
+
 /* Group rows by node id (stable): row_index/seg as lbk_histogram expects.  node_of_row values
  * outside [node_begin, node_begin+n_nodes) are dropped.  (Reference: the radix sort of
  * (node,row) pairs in UpdatePositions, build_tree.cu:1050-1079.) */

@@ -33,6 +33,8 @@
 //   * a node whose rows fit one chunk owns its output region and flushes with plain stores;
 //     otherwise the flush uses 64-bit global atomics; chunks of <= 128 rows skip shared memory.
 #include <cstdlib>
+#include <mutex>
+#include <string>
 
 #include "device_utils.cuh"
 #include "internal.h"
@@ -608,3 +610,150 @@ void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t
 }
 
 }  // namespace lbk
+
+// ---------------------------------------------------------------------------------------------
+// lbk_histogram_noalloc: the histogram build for callers that must not allocate device memory.
+//
+// Who needs it: code that runs where cudaMalloc / cudaFree are off limits - inside a stream
+// callback or another thread's critical section where the allocator's implicit device
+// synchronisation would deadlock or stall every stream, under a memory budget that a runtime
+// has already handed out completely (a task variant registered without the right to allocate),
+// or in a process that wants its device footprint fixed after start-up.  lbk_histogram takes its
+// per-call scratch (chunk offsets, the level plan, the largest magnitudes) from the context's
+// pool; this entry point keeps that scratch in a fixed array inside the library image instead
+// and needs no context at all.
+//
+// Limits and rules
+//   * at most LBK_NOALLOC_MAX_NODES nodes and LBK_NOALLOC_MAX_FEATURES features per call,
+//     device pointers only (host_buffers must be 0); larger calls are rejected with
+//     LBK_ERR_ARGUMENT before anything is launched;
+//   * the array (about 16 KB) exists once per GPU that loads the library, until the process ends;
+//   * the first call on a device looks the array's device address up (the array's name is only a
+//     host-side handle; kernels get the address found here).  Make that first call before any
+//     stream capture;
+//   * all calls on a device share the array: what has to start at zero is cleared by each call, and
+//     two calls whose kernels overlap on the GPU (different streams, different threads) race -
+//     serialise them on one stream.
+namespace lbk {
+namespace {
+
+constexpr int kNoAllocMaxNodes    = LBK_NOALLOC_MAX_NODES;
+constexpr int kNoAllocMaxFeatures = LBK_NOALLOC_MAX_FEATURES;
+constexpr int kNoAllocPlanOffset  = kNoAllocMaxNodes + 4;   // chunk offsets first, then plan[4], max_abs[2]
+constexpr int kNoAllocInts        = kNoAllocPlanOffset + 8;
+
+static __device__ __align__(256) int32_t g_hist_scratch[kNoAllocInts];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+int32_t* g_scratch_addr[kMaxDevices] = {};
+
+// Device address of the scratch array on `device`, which must be the current device.
+int32_t* HistScratchAddress(int device)
+{
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[device] == nullptr) {
+    void* ptr = nullptr;
+    LBK_CUDA(cudaGetSymbolAddress(&ptr, g_hist_scratch));
+    g_scratch_addr[device] = static_cast<int32_t*>(ptr);
+  }
+  return g_scratch_addr[device];
+}
+
+}  // namespace
+}  // namespace lbk
+
+extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
+{
+  using namespace lbk;
+  return Guard(nullptr, [&] {
+    LBK_EXPECT(a != nullptr, "null argument");
+    LBK_EXPECT(device >= 0 && device < kMaxDevices, "device index out of range");
+    LBK_EXPECT(a->host_buffers == 0, "lbk_histogram_noalloc takes device pointers only");
+    LBK_EXPECT(a->bins && a->row_ptr && a->row_index && a->seg && a->hist, "null argument");
+    LBK_EXPECT(a->mode == 0 || a->mode == 1, "mode must be 0 or 1");
+    LBK_EXPECT(a->mode == 0 ? a->gpair != nullptr : a->gpair_f32 != nullptr, "missing gradient pairs");
+    LBK_EXPECT(a->bin_bytes == 1 || a->bin_bytes == 2, "bin_bytes must be 1 or 2");
+    LBK_EXPECT(a->n_features >= 1 && a->n_outputs >= 1 && a->total_bins >= a->n_features, "bad shape");
+    LBK_EXPECT(a->n_nodes >= 1 && a->n_nodes <= kNoAllocMaxNodes,
+               "lbk_histogram_noalloc handles at most " + std::to_string(kNoAllocMaxNodes) + " nodes per call");
+    LBK_EXPECT(a->n_features <= kNoAllocMaxFeatures,
+               "lbk_histogram_noalloc handles at most " + std::to_string(kNoAllocMaxFeatures) + " features per call");
+    LBK_CUDA(cudaSetDevice(device));
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    int32_t* scratch    = HistScratchAddress(device);
+    int32_t* chunk_off  = scratch;
+    int32_t* plan       = scratch + kNoAllocPlanOffset;
+    int* max_abs        = reinterpret_cast<int*>(plan + 4);
+
+    const int F = a->n_features, K = a->n_outputs, B = a->total_bins;
+    int32_t rp[kNoAllocMaxFeatures + 1];
+    LBK_CUDA(cudaMemcpyAsync(rp, a->row_ptr, sizeof(int32_t) * (F + 1), cudaMemcpyDeviceToHost, stream));
+    LBK_CUDA(cudaStreamSynchronize(stream));
+    LBK_EXPECT(rp[F] == B, "total_bins does not match row_ptr");
+    int mb = 1;
+    for (int f = 0; f < F; ++f) mb = rp[f + 1] - rp[f] > mb ? rp[f + 1] - rp[f] : mb;
+    LBK_EXPECT(a->bin_bytes == 2 || mb <= 256, "one-byte bins need <= 256 proposals per feature");
+
+    int sm_count = 0, max_smem_optin = 0;
+    LBK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+    LBK_CUDA(cudaDeviceGetAttribute(&max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+
+    const bool float_mode = a->mode == 1;
+    HistParams p;
+    p.bins         = a->bins;
+    p.n_rows       = a->n_rows;
+    p.F            = F;
+    p.K            = K;
+    p.B            = B;
+    p.G            = (F + kGroup - 1) / kGroup;
+    p.row_ptr      = a->row_ptr;
+    p.gpair        = float_mode ? static_cast<const void*>(a->gpair_f32) : static_cast<const void*>(a->gpair);
+    p.row_index    = a->row_index;
+    p.seg          = a->seg;
+    p.slot_of_node = nullptr;
+    p.n_nodes      = a->n_nodes;
+    p.chunk_off    = chunk_off;
+    p.plan         = plan;
+    p.ticket       = reinterpret_cast<unsigned int*>(plan + 2);
+    p.out          = a->hist;
+    const bool smem_path = a->bin_bytes == 1 && mb <= kSmemBins;
+    p.mb                 = smem_path ? mb : 0;
+    const size_t smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * 8 + kHistWarps * kWarpRingBytes : 0;
+    int blocks_per_sm    = smem_path ? static_cast<int>(max_smem_optin / (smem + 1024)) : 4;
+    if (blocks_per_sm > 2048 / kHistThreads) blocks_per_sm = 2048 / kHistThreads;
+    if (blocks_per_sm < 1) blocks_per_sm = 1;
+    const int grid = sm_count * blocks_per_sm;
+
+    // the array keeps what the previous call left: clear the words that accumulate
+    LBK_CUDA(cudaMemsetAsync(plan, 0, sizeof(int32_t) * 8, stream));
+    LBK_CUDA(cudaMemsetAsync(a->hist, 0, sizeof(GPairI64) * a->n_nodes * K * B, stream));
+    if (!float_mode) {
+      const int64_t n = a->n_rows * K;
+      if (n > 0) {
+        k_max_abs<<<sm_count * 8, 256, 0, stream>>>(static_cast<const int2*>(p.gpair), n, max_abs);
+        LBK_LAUNCH_CHECK();
+      }
+    }
+    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, p.G * p.K, grid + 1, float_mode ? nullptr : max_abs,
+                                        chunk_off, plan, p.ticket);
+    LBK_LAUNCH_CHECK();
+#define LBK_HIST_LAUNCH(BinT, FL, SM)                                                                              \
+  do {                                                                                                             \
+    if (smem > 48 * 1024)                                                                                          \
+      LBK_CUDA(cudaFuncSetAttribute(k_hist<BinT, FL, SM>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                                    static_cast<int>(smem)));                                                      \
+    k_hist<BinT, FL, SM><<<grid, kHistThreads, smem, stream>>>(p);                                                 \
+  } while (0)
+    if (smem_path) {
+      if (float_mode) LBK_HIST_LAUNCH(uint8_t, true, true); else LBK_HIST_LAUNCH(uint8_t, false, true);
+    } else if (a->bin_bytes == 1) {
+      if (float_mode) LBK_HIST_LAUNCH(uint8_t, true, false); else LBK_HIST_LAUNCH(uint8_t, false, false);
+    } else {
+      if (float_mode) LBK_HIST_LAUNCH(uint16_t, true, false); else LBK_HIST_LAUNCH(uint16_t, false, false);
+    }
+#undef LBK_HIST_LAUNCH
+    LBK_LAUNCH_CHECK();
+    LBK_CUDA(cudaStreamSynchronize(stream));
+  });
+}

@@ -20,7 +20,7 @@ EXPORTS = [
     "lbk_version", "lbk_context_create", "lbk_context_destroy", "lbk_last_error", "lbk_context_trim",
     "lbk_comm_unique_id", "lbk_comm_init", "lbk_comm_attach_nccl", "lbk_comm_set_callback",
     "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
-    "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_group_rows",
+    "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_histogram_noalloc", "lbk_group_rows",
 ]
 
 
@@ -101,6 +101,7 @@ def load():
             lib.lbk_build_tree.argtypes = [C.c_void_p, C.POINTER(BuildTreeArgs)]
             lib.lbk_predict.argtypes = [C.c_void_p, C.POINTER(PredictArgs)]
             lib.lbk_histogram.argtypes = [C.c_void_p, C.POINTER(HistogramArgs)]
+            lib.lbk_histogram_noalloc.argtypes = [C.c_int, C.POINTER(HistogramArgs)]
             lib.lbk_split_proposals.argtypes = [
                 C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int,
                 C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]
