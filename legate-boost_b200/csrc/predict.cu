@@ -53,18 +53,20 @@ __global__ void __launch_bounds__(128)
 {
   constexpr int RB = 128;  // rows per block = threads per block
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* xs        = reinterpret_cast<T*>(smem_raw);                                   // [F][RB]
-  double* accs = reinterpret_cast<double*>(smem_raw + (kStage ? sizeof(T) * F * RB : 0));  // [K][RB]
+  constexpr int RBP = RB + 1;  // row pitch of the staged tile: consecutive features fall in consecutive banks
+  T* xs        = reinterpret_cast<T*>(smem_raw);                                    // [F][RBP]
+  double* accs = reinterpret_cast<double*>(smem_raw + (kStage ? (sizeof(T) * F * RBP + 15) / 16 * 16 : 0));  // [K][RB]
   const int tid        = threadIdx.x;
   const int64_t row0   = static_cast<int64_t>(blockIdx.x) * RB;
   const int64_t row    = row0 + tid;
   const int rows_here  = static_cast<int>((n_rows - row0) < RB ? (n_rows - row0) : RB);
   if (kStage) {
-    // thread t stages row t: its reads of consecutive features hit the same sectors repeatedly
-    // (served by L1), its shared-memory writes go to bank t%32
-    if (tid < rows_here) {
-      const T* xr = X + row * ldx;
-      for (int f = 0; f < F; ++f) xs[f * RB + tid] = xr[f];
+    // a warp stages whole rows: coalesced reads along the features, transposed writes whose
+    // pitch of RB+1 elements spreads consecutive features over consecutive banks
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int r = warp; r < rows_here; r += RB / 32) {
+      const T* xrow = X + (row0 + r) * ldx;
+      for (int f = lane; f < F; f += 32) xs[f * RBP + r] = xrow[f];
     }
     __syncthreads();
   }
@@ -86,7 +88,7 @@ __global__ void __launch_bounds__(128)
       const PNode n = nodes[off + pos];
       // a split node on the last level of the arrays has no children to go to: stop there
       if (n.feature == -1 || 2 * pos + 2 >= mn) break;
-      const double xv = static_cast<double>(kStage ? xs[n.feature * RB + tid] : xr[n.feature]);
+      const double xv = static_cast<double>(kStage ? xs[n.feature * RBP + tid] : xr[n.feature]);
       pos             = xv <= n.split ? 2 * pos + 1 : 2 * pos + 2;
     }
     const double* lf = leaves + static_cast<int64_t>(off + pos) * K;
@@ -138,7 +140,7 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
   LBK_LAUNCH_CHECK();
 
   constexpr int RB      = 128;
-  const size_t x_bytes  = sizeof(T) * static_cast<size_t>(F) * RB;
+  const size_t x_bytes  = (sizeof(T) * static_cast<size_t>(F) * (RB + 1) + 15) / 16 * 16;
   const size_t a_bytes  = K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
   const size_t budget   = static_cast<size_t>(ctx->max_smem_optin) - 1024;
   const bool stage      = x_bytes <= budget;

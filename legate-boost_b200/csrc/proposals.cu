@@ -259,7 +259,10 @@ void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposal
   const bool use_smem   = smem <= 96 * 1024;
   const int warps_per_b = 8;
   int64_t blocks_x      = (n_rows + warps_per_b * 8 - 1) / (warps_per_b * 8);  // ~8 rows per warp
-  if (blocks_x > 65535 * 16) blocks_x = 65535 * 16;
+  // a block copies its group's proposals (up to 32 KB) into shared memory once and then walks
+  // the rows with a grid stride: keep the grid near the number of resident blocks
+  const int64_t resident = 148 * 8 / (G > 8 ? 8 : G);
+  if (blocks_x > resident) blocks_x = resident;
   if (blocks_x < 1) blocks_x = 1;
   dim3 grid(static_cast<unsigned>(blocks_x), G);
 #define LBK_BIN_LAUNCH(BinT)                                                                              \
