@@ -160,33 +160,77 @@ __global__ void k_write_proposals(const T* __restrict__ uniq, int S, const int32
   }
 }
 
-// One warp per row, one lane per feature of the group.  The group's slice of the proposal
-// CSR sits in shared memory when it fits.
-template <typename T, typename BinT, bool kUseSmem>
+// One warp per row, one lane per feature of the group.
+//
+// Shared-memory variant: the proposals of the group are kept transposed and padded, sp[j][lane] =
+// proposal j of the lane's feature (+inf beyond the feature's last one, P = power of two rows), so
+// that every probe of lane l goes to bank l: the eight probes of a lower_bound cost eight
+// conflict-free wavefronts per warp and row instead of eight 3-4-way conflicted ones.  The search
+// is the branchless form "pos += step while sp[pos+step-1] < x", which returns the number of
+// proposals below x, i.e. the index of the first proposal >= x.
+template <typename T, typename BinT>
 __global__ void __launch_bounds__(256)
-  k_bin(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, const T* __restrict__ proposals,
-        const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins)
+  k_bin_smem(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, const T* __restrict__ proposals,
+             const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins, int P)
 {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* sp           = reinterpret_cast<T*>(smem_raw);
-  const int g     = blockIdx.y;
-  const int f0    = g * kGroup;
-  const int lane  = threadIdx.x & 31;
-  const int f     = f0 + lane;
-  const int fend  = min(F, f0 + kGroup);
-  const int gbase = row_ptr[f0];
-  if (kUseSmem) {
-    const int gcount = row_ptr[fend] - gbase;
-    for (int i = threadIdx.x; i < gcount; i += blockDim.x) sp[i] = proposals[gbase + i];
-    __syncthreads();
+  T* sp          = reinterpret_cast<T*>(smem_raw);
+  const int g    = blockIdx.y;
+  const int f0   = g * kGroup;
+  const int lane = threadIdx.x & 31;
+  for (int idx = threadIdx.x; idx < P * kGroup; idx += blockDim.x) {
+    const int j = idx >> 5, f = f0 + (idx & 31);
+    T v = static_cast<T>(INFINITY);
+    if (f < F) {
+      const int b = row_ptr[f];
+      if (j < row_ptr[f + 1] - b) v = proposals[b + j];
+    }
+    sp[idx] = v;
   }
+  __syncthreads();
+  const bool active = f0 + lane < F;
+  const T* spl      = sp + lane;
+  BinT* out         = bins + static_cast<int64_t>(g) * n_rows * kGroup;
+  constexpr int U   = 4;  // rows per warp in flight
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const int64_t w0          = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  for (int64_t base = w0 * U; base < n_rows; base += warps_total * U) {
+    T x[U];
+    int pos[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t row = base + u;
+      x[u]   = (active && row < n_rows) ? X[row * ldx + f0 + lane] : static_cast<T>(-INFINITY);
+      pos[u] = 0;
+    }
+    for (int step = P >> 1; step >= 1; step >>= 1) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (spl[(pos[u] + step - 1) * kGroup] < x[u]) pos[u] += step;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (base + u < n_rows) out[(base + u) * kGroup + lane] = static_cast<BinT>(pos[u]);
+  }
+}
+
+// Global-memory variant for features with more proposals than shared memory holds.
+template <typename T, typename BinT>
+__global__ void __launch_bounds__(256)
+  k_bin_global(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, const T* __restrict__ proposals,
+               const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins)
+{
+  const int g    = blockIdx.y;
+  const int f0   = g * kGroup;
+  const int lane = threadIdx.x & 31;
+  const int f    = f0 + lane;
   const bool active = f < F;
   int begin = 0, n = 0;
   if (active) {
     begin = row_ptr[f];
     n     = row_ptr[f + 1] - begin;
   }
-  const T* p = kUseSmem ? sp + (begin - gbase) : proposals + begin;
+  const T* p = proposals + begin;
   BinT* out  = bins + static_cast<int64_t>(g) * n_rows * kGroup;
   const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   for (int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5); row < n_rows;
@@ -255,13 +299,13 @@ void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposal
 {
   if (n_rows <= 0) return;
   const int G           = (F + kGroup - 1) / kGroup;
-  const size_t smem     = sizeof(T) * static_cast<size_t>(kGroup) * max_bins_per_feature;
+  const int P           = NextPow2(max_bins_per_feature);
+  const size_t smem     = sizeof(T) * static_cast<size_t>(kGroup) * P;
   const bool use_smem   = smem <= 96 * 1024;
-  const int warps_per_b = 8;
-  int64_t blocks_x      = (n_rows + warps_per_b * 8 - 1) / (warps_per_b * 8);  // ~8 rows per warp
-  // a block copies its group's proposals (up to 32 KB) into shared memory once and then walks
-  // the rows with a grid stride: keep the grid near the number of resident blocks
-  const int64_t resident = 148 * 8 / (G > 8 ? 8 : G);
+  // a block fills its table once and then walks the rows with a grid stride: keep the grid near
+  // the number of resident blocks
+  int64_t blocks_x      = (n_rows + 63) / 64;
+  const int64_t resident = 148 * 6 / (G > 6 ? 6 : G);
   if (blocks_x > resident) blocks_x = resident;
   if (blocks_x < 1) blocks_x = 1;
   dim3 grid(static_cast<unsigned>(blocks_x), G);
@@ -269,12 +313,12 @@ void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposal
   do {                                                                                                    \
     if (use_smem) {                                                                                       \
       if (smem > 48 * 1024)                                                                               \
-        LBK_CUDA(cudaFuncSetAttribute(k_bin<T, BinT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+        LBK_CUDA(cudaFuncSetAttribute(k_bin_smem<T, BinT>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                       static_cast<int>(smem)));                                           \
-      k_bin<T, BinT, true><<<grid, 256, smem, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,           \
-                                                         static_cast<BinT*>(bins));                       \
+      k_bin_smem<T, BinT><<<grid, 256, smem, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,            \
+                                                        static_cast<BinT*>(bins), P);                     \
     } else {                                                                                              \
-      k_bin<T, BinT, false><<<grid, 256, 0, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,             \
+      k_bin_global<T, BinT><<<grid, 256, 0, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,             \
                                                        static_cast<BinT*>(bins));                         \
     }                                                                                                     \
   } while (0)
