@@ -64,9 +64,21 @@ __global__ void __launch_bounds__(128)
     // a warp stages whole rows: coalesced reads along the features, transposed writes whose
     // pitch of RB+1 elements spreads consecutive features over consecutive banks
     const int lane = tid & 31, warp = tid >> 5;
-    for (int r = warp; r < rows_here; r += RB / 32) {
-      const T* xrow = X + (row0 + r) * ldx;
-      for (int f = lane; f < F; f += 32) xs[f * RBP + r] = xrow[f];
+    constexpr int NW = RB / 32, U = 8;  // eight independent row loads in flight per lane
+    for (int rb = warp; rb < rows_here; rb += NW * U) {
+      for (int f = lane; f < F; f += 32) {
+        T v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int r = rb + u * NW;
+          if (r < rows_here) v[u] = __ldcs(X + (row0 + r) * ldx + f);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int r = rb + u * NW;
+          if (r < rows_here) xs[f * RBP + r] = v[u];
+        }
+      }
     }
     __syncthreads();
   }
