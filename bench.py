@@ -121,36 +121,72 @@ def algorithmic_bytes(n_rows):
     return n_rows * (HIST_FEATURES + 8 + 4) + HIST_NODES * HIST_FEATURES * HIST_BINS * 16
 
 
+def _ref_hist_lib():
+    """The reference's own CPU histogram step (stub-compiled), or None when it was not built."""
+    import ctypes as C
+
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_hist.so")
+    if not os.path.exists(path):
+        return None
+    lib = C.CDLL(path)
+    lib.ref_compute_histogram.restype = C.c_double
+    return lib
+
+
 def cpu_hist_sample(n_rows_sample, seed, threads):
-    """The histogram of the oracle (a restatement of the reference CPU loop, build_tree.cc:267-280)
-    timed on `threads` host threads over row shards of one sample, partial histograms summed in
-    process.  Returns (rows*features/s, description)."""
-    from oracle import oracle as O
+    """CPU histogram of one row sample of the level-7 batch on `threads` host threads, one rank
+    per thread on a row shard, partial histograms summed in process (the stand-in for the CPU
+    all-reduce).  Uses the reference's own ComputeHistogram (src/models/tree/build_tree.cc:258-289,
+    stub-compiled) when that build is present, else the oracle's restatement of the same loop.
+    Returns (rows*features/s, seconds, kind)."""
+    import ctypes as C
 
     rs = np.random.default_rng(seed)
     bins = rs.integers(0, HIST_BINS, size=(n_rows_sample, HIST_FEATURES), dtype=np.uint8)
-    row_ptr = (np.arange(HIST_FEATURES + 1) * HIST_BINS).astype(np.int32)
-    g = rs.normal(size=(n_rows_sample, 1)).astype(np.float32)
-    h = np.ones((n_rows_sample, 1), dtype=np.float32)
+    g = rs.normal(size=(n_rows_sample, 1))
+    h = np.ones((n_rows_sample, 1))
     node = rs.integers(0, HIST_NODES, size=n_rows_sample).astype(np.int32) + (HIST_NODES - 1)
-    O.lib()
+    ref = _ref_hist_lib()
     parts = [None] * threads
+    inner = [0.0] * threads
+    shape = (HIST_NODES, 1, HIST_FEATURES * HIST_BINS, 2)
+    if ref is not None:
+        kind = "reference"
 
-    def work(t):
-        b, e = shard_rows(n_rows_sample, t, threads)
-        parts[t] = O.histogram_d(bins[b:e], row_ptr, g[b:e], h[b:e], node[b:e], HIST_NODES - 1, 2 * HIST_NODES - 1)
+        def work(t):
+            b, e = shard_rows(n_rows_sample, t, threads)
+            out = np.zeros(shape)
+            bb, gg, hh, nn = (np.ascontiguousarray(a[b:e]) for a in (bins, g, h, node))
+            inner[t] = ref.ref_compute_histogram(
+                bb.ctypes.data_as(C.c_void_p), C.c_int64(e - b), C.c_int(HIST_FEATURES), C.c_int(HIST_BINS),
+                gg.ctypes.data_as(C.c_void_p), hh.ctypes.data_as(C.c_void_p), C.c_int(1),
+                nn.ctypes.data_as(C.c_void_p), C.c_int(HIST_NODES - 1), C.c_int(2 * HIST_NODES - 1),
+                out.ctypes.data_as(C.c_void_p))
+            parts[t] = out
+    else:
+        kind = "port"
+        from oracle import oracle as O
 
-    t0 = time.perf_counter()
+        O.lib()
+        row_ptr = (np.arange(HIST_FEATURES + 1) * HIST_BINS).astype(np.int32)
+
+        def work(t):
+            b, e = shard_rows(n_rows_sample, t, threads)
+            t0 = time.perf_counter()
+            parts[t] = O.histogram_d(bins[b:e], row_ptr, g[b:e], h[b:e], node[b:e], HIST_NODES - 1, 2 * HIST_NODES - 1)
+            inner[t] = time.perf_counter() - t0
+
     ths = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
     for t in ths:
         t.start()
     for t in ths:
         t.join()
+    t0 = time.perf_counter()
     total = parts[0]
     for p in parts[1:]:
         total += p
-    dt = time.perf_counter() - t0
-    return n_rows_sample * HIST_FEATURES / dt, dt
+    dt = max(inner) + (time.perf_counter() - t0)  # slowest rank + the sum over ranks
+    return n_rows_sample * HIST_FEATURES / dt, dt, kind
 
 
 def run_reference(args):
@@ -162,21 +198,21 @@ def run_reference(args):
     sample = 2_000_000
     for _ in range(args.warmup if args.warmup < 2 else 1):
         cpu_hist_sample(200_000, 1, threads)
-    vals = []
     t_all = 0.0
+    kind = "port"
     for i in range(args.steps):
-        v, dt = cpu_hist_sample(sample, 1 + i, threads)
-        vals.append(v)
+        v, dt, kind = cpu_hist_sample(sample, 1 + i, threads)
         t_all += dt
     value = sample * HIST_FEATURES * args.steps / t_all
     line = {
         "impl": "reference", "metric": "histogram rows*features/s", "value": value, "unit": "row-features/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": "histogram build, level 7 (128 nodes), %d features x %d bins, float64 accumulation"
-                               % (HIST_FEATURES, HIST_BINS)},
-        "cpu_baseline": {"value": value, "unit": "row-features/s", "cores": threads, "kind": "port",
-                         "sample": "%d-row sample of the 10M-row batch per step, %d threads on row shards" % (sample, threads)},
+        "config": {"workload": "histogram build, level 7 (128 nodes), %d rows x %d features x %d bins per step, "
+                               "float64 accumulation on the host" % (sample, HIST_FEATURES, HIST_BINS)},
+        "cpu_baseline": {"value": value, "unit": "row-features/s", "cores": threads, "kind": kind,
+                         "sample": "%d-row sample of the 10M-row batch per step, %d ranks (threads) on row shards, "
+                                   "time = slowest rank inside ComputeHistogram + in-process sum" % (sample, threads)},
         "e2e": {"value": value, "unit": "row-features/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -296,9 +332,9 @@ def run_hist(args):
         }
         if not args.no_cpu and world >= 1:
             threads = os.cpu_count() or 1
-            v, dt = cpu_hist_sample(1_000_000, 7, threads)
-            line["cpu_baseline"] = {"value": v, "unit": "row-features/s", "cores": threads, "kind": "port",
-                                    "sample": "one 1M-row sample of the batch, %d threads on row shards (%.1f s)" % (threads, dt)}
+            v, dt, kind = cpu_hist_sample(2_000_000, 7, threads)
+            line["cpu_baseline"] = {"value": v, "unit": "row-features/s", "cores": threads, "kind": kind,
+                                    "sample": "one 2M-row sample of the batch, %d ranks (threads) on row shards (%.2f s)" % (threads, dt)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
