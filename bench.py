@@ -60,7 +60,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -311,11 +311,9 @@ def run_hist(args):
         peak, which = measured_peaks()
         kms = ksum / args.steps
         achieved = algorithmic_bytes(n_rows) / (kms * 1e-3) / 1e9
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", "hist_traffic.json")
-        if os.path.exists(tpath):
-            with open(tpath) as f:
-                traffic = json.load(f).get("int32" if mode == 0 else "float32")
+        # DRAM traffic of one launch, from the ncu capture of the 2 M-row case summarised in
+        # profiles/k_hist_config2_ncu_full.md (363.1 B read per row, 55.5 MB written), scaled by rows
+        traffic = n_rows * 363.1 + 55.5e6 if mode == 0 else None
         line = {
             "metric": "histogram rows*features/s", "value": value, "unit": "row-features/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
@@ -328,7 +326,7 @@ def run_hist(args):
                        "l2": "160 MB flush buffer written between timed steps; inputs (1.4 GB) exceed L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_source": which, "kernel": "k_hist", "kernel_ms": kms},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * args.steps,
         }
         if not args.no_cpu and world >= 1:
             threads = os.cpu_count() or 1
@@ -429,7 +427,7 @@ def run_predict(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="hist", choices=["hist", "train", "predict"])

@@ -4,22 +4,45 @@
 // launch per tree, each re-reading and re-writing pred; rows walk from node 0 while
 // feature[pos] != -1 (at most 100 steps), going left iff (double)x <= split_value[pos].
 //
-// Design for B200: ONE launch for the whole ensemble.  The trees are first packed into one
-// array of 16-byte nodes (split, feature) plus one leaf array, so a step of the walk is one
-// 16-byte load that stays in L1/L2 (500 depth-8 trees are 4 MB).  A block stages a tile of rows
-// of X in shared memory, feature-major, so the lane that owns row r always reads bank r%32
-// whatever feature its node asks for; every row is read from HBM exactly once, predictions are
-// accumulated in float64 in tree order and written exactly once.
+// Design for B200: ONE launch for the whole ensemble, everything a step of the walk touches lives
+// in shared memory.
+//   * A block owns a tile of rows (one thread per row) and stages it once, feature-major with a
+//     pitch of rows+1, so the thread of row r reads bank (f+r)%32: every row of X is read from HBM
+//     exactly once, coalesced.
+//   * The trees are first packed into one array of small nodes: for float32 X a node is 8 bytes
+//     (float split, int feature) - "x <= split" with x a float is the same test as
+//     "x <= the largest float not above split", so the split is rounded down once at packing time
+//     and the walk compares floats; for float64 X a node is 16 bytes.
+//   * Trees are brought into shared memory four at a time (cp.async, double buffered) together
+//     with their leaf values; a thread walks the four trees of a group as four independent
+//     chains, which hides the shared-memory latency that a single dependent chain exposes.
+//   * Predictions are accumulated in float64 in tree order (bit-identical to the reference's
+//     tree-by-tree accumulation) and written once.
+// A fallback kernel with the nodes in global memory covers shapes whose tile or trees do not fit.
 #include "device_utils.cuh"
 #include "internal.h"
 
 namespace lbk {
 namespace {
 
-struct PNode {
+// `foff` = feature index times a caller-chosen multiplier (the byte pitch of the staged tile for
+// the tiled kernel, 1 for the fallback), or -1 for a leaf
+struct Node8 {
+  float split;
+  int foff;
+};
+struct Node16 {
   double split;
-  int feature;
+  int foff;
   int pad;
+};
+template <typename T>
+struct NodeOf {
+  using type = Node16;
+};
+template <>
+struct NodeOf<float> {
+  using type = Node8;
 };
 
 struct TreePtrs {
@@ -30,41 +53,124 @@ struct TreePtrs {
   int node_off;  // offset of this tree's first node in the packed arrays
 };
 
-__global__ void k_pack_trees(const TreePtrs* __restrict__ trees, int K, PNode* __restrict__ nodes,
+__device__ inline void MakeNode(Node8& n, double split, int foff)
+{
+  n.split = __double2float_rd(split);  // x <= split  <=>  x <= round-down(split) for float x
+  n.foff  = foff;
+}
+__device__ inline void MakeNode(Node16& n, double split, int foff)
+{
+  n.split = split;
+  n.foff  = foff;
+  n.pad   = 0;
+}
+
+// A split node whose children would fall outside the arrays is treated as a leaf, so a walk can
+// never leave the tree whatever the input arrays hold.
+template <typename NodeT>
+__global__ void k_pack_trees(const TreePtrs* __restrict__ trees, int K, int F, int xmul, NodeT* __restrict__ nodes,
                              double* __restrict__ leaves)
 {
   const TreePtrs t = trees[blockIdx.x];
   for (int i = threadIdx.x; i < t.max_nodes; i += blockDim.x) {
-    PNode n;
-    n.split   = t.split[i];
-    n.feature = t.feature[i];
-    n.pad     = 0;
+    int f = t.feature[i];
+    if (2 * i + 2 >= t.max_nodes || f < 0 || f >= F) f = -1;
+    NodeT n;
+    MakeNode(n, t.split[i], f < 0 ? -1 : f * xmul);
     nodes[t.node_off + i] = n;
   }
   for (int64_t i = threadIdx.x; i < static_cast<int64_t>(t.max_nodes) * K; i += blockDim.x)
     leaves[static_cast<int64_t>(t.node_off) * K + i] = t.leaf[i];
 }
 
-template <typename T, bool kStage>
-__global__ void __launch_bounds__(128)
-  k_predict(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
-            const TreePtrs* __restrict__ trees, const PNode* __restrict__ nodes, const double* __restrict__ leaves,
-            double* __restrict__ pred, int64_t ldp, int acc_in_smem)
+__device__ inline void CpAsync16(unsigned smem_dst, const void* gsrc)
 {
-  constexpr int RB = 128;  // rows per block = threads per block
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ inline void CpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ inline void CpAsyncWaitAll() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+__device__ inline void LdsNode(unsigned addr, float& split, int& foff)
+{
+  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];\n" : "=f"(split), "=r"(foff) : "r"(addr));
+}
+__device__ inline void LdsNode(unsigned addr, double& split, int& foff)
+{
+  int pad;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n"
+               : "=r"(reinterpret_cast<int2&>(split).x), "=r"(reinterpret_cast<int2&>(split).y), "=r"(foff), "=r"(pad)
+               : "r"(addr));
+}
+__device__ inline float LdsX(unsigned addr, float)
+{
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ inline double LdsX(unsigned addr, double)
+{
+  double v;
+  asm volatile("ld.shared.f64 %0, [%1];\n" : "=d"(v) : "r"(addr));
+  return v;
+}
+__device__ inline double LdsF64(unsigned addr)
+{
+  double v;
+  asm volatile("ld.shared.f64 %0, [%1];\n" : "=d"(v) : "r"(addr));
+  return v;
+}
+
+constexpr int kTreeGroup = 4;
+
+// Tiled kernel.  Shared memory: X tile [F][RB+1] | accumulators [K][RB] (K > 1) |
+// 2 x kTreeGroup x slot, slot = m_pad nodes (+ m_pad leaf values when K == 1); m_pad is even and
+// every tree starts at an even node offset, so all copies are 16-byte aligned.
+template <typename T, int RB>
+__global__ void __launch_bounds__(RB)
+  k_predict_tiled(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
+                  const TreePtrs* __restrict__ trees, const typename NodeOf<T>::type* __restrict__ nodes,
+                  const double* __restrict__ leaves, double* __restrict__ pred, int64_t ldp, int m_pad, int max_steps)
+{
+  using NodeT = typename NodeOf<T>::type;
+  constexpr int RBP = RB + 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  constexpr int RBP = RB + 1;  // row pitch of the staged tile: consecutive features fall in consecutive banks
-  T* xs        = reinterpret_cast<T*>(smem_raw);                                    // [F][RBP]
-  double* accs = reinterpret_cast<double*>(smem_raw + (kStage ? (sizeof(T) * F * RBP + 15) / 16 * 16 : 0));  // [K][RB]
-  const int tid        = threadIdx.x;
-  const int64_t row0   = static_cast<int64_t>(blockIdx.x) * RB;
-  const int64_t row    = row0 + tid;
-  const int rows_here  = static_cast<int>((n_rows - row0) < RB ? (n_rows - row0) : RB);
-  if (kStage) {
-    // a warp stages whole rows: coalesced reads along the features, transposed writes whose
-    // pitch of RB+1 elements spreads consecutive features over consecutive banks
+  T* xs = reinterpret_cast<T*>(smem_raw);
+  size_t off = (sizeof(T) * static_cast<size_t>(F) * RBP + 15) / 16 * 16;
+  double* accs = reinterpret_cast<double*>(smem_raw + off);
+  off += K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
+  const size_t slot_bytes = static_cast<size_t>(m_pad) * (sizeof(NodeT) + (K == 1 ? sizeof(double) : 0));
+  unsigned char* tree_s   = smem_raw + off;  // [2][kTreeGroup][slot]
+
+  const int tid       = threadIdx.x;
+  const int64_t row0  = static_cast<int64_t>(blockIdx.x) * RB;
+  const int rows_here = static_cast<int>((n_rows - row0) < RB ? (n_rows - row0) : RB);
+
+  // group of trees -> shared memory, 16 bytes per copy (nodes, then leaves when K == 1)
+  auto stage_group = [&](int group, int buf) {
+    for (int j = 0; j < kTreeGroup; ++j) {
+      const int t = group * kTreeGroup + j;
+      if (t >= n_trees) break;
+      const TreePtrs tp   = trees[t];
+      unsigned char* dst  = tree_s + (static_cast<size_t>(buf) * kTreeGroup + j) * slot_bytes;
+      const unsigned d_s  = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+      const int mp         = (tp.max_nodes + 1) & ~1;  // the packed arrays are padded to even counts
+      const int node_units = mp * static_cast<int>(sizeof(NodeT)) / 16;
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(nodes + tp.node_off);
+      for (int i = tid; i < node_units; i += RB) CpAsync16(d_s + i * 16, src + static_cast<size_t>(i) * 16);
+      if (K == 1) {
+        const unsigned l_s = d_s + static_cast<unsigned>(m_pad * sizeof(NodeT));
+        const unsigned char* lsrc = reinterpret_cast<const unsigned char*>(leaves + tp.node_off);
+        for (int i = tid; i < mp / 2; i += RB) CpAsync16(l_s + i * 16, lsrc + static_cast<size_t>(i) * 16);
+      }
+    }
+    CpAsyncCommit();
+  };
+  stage_group(0, 0);
+
+  // stage the X tile: a warp reads whole rows (coalesced), eight rows in flight per lane
+  {
     const int lane = tid & 31, warp = tid >> 5;
-    constexpr int NW = RB / 32, U = 8;  // eight independent row loads in flight per lane
+    constexpr int NW = RB / 32, U = 8;
     for (int rb = warp; rb < rows_here; rb += NW * U) {
       for (int f = lane; f < F; f += 32) {
         T v[U];
@@ -80,43 +186,127 @@ __global__ void __launch_bounds__(128)
         }
       }
     }
-    __syncthreads();
   }
-  if (tid >= rows_here) return;
-  const T* xr = X + row * ldx;
-  double acc0 = 0.0;
-  if (K > 1) {
-    if (acc_in_smem) {
-      for (int k = 0; k < K; ++k) accs[k * RB + tid] = 0.0;
+  if (K > 1)
+    for (int k = 0; k < K; ++k) accs[k * RB + tid] = 0.0;
+
+  // The walk works on 32-bit shared addresses.  `p8` is the node index times 8: the byte offset
+  // of the leaf value and (times sizeof(NodeT)/8) of the node.  A leaf keeps its position, so every
+  // tree of a group takes the same fixed number of steps and the chains stay independent.
+  constexpr unsigned kNodeShift = sizeof(NodeT) == 16 ? 1 : 0;
+  const unsigned xcol_s = static_cast<unsigned>(__cvta_generic_to_shared(xs + tid));
+  const unsigned tree0  = static_cast<unsigned>(__cvta_generic_to_shared(tree_s));
+  const unsigned leaf_o = static_cast<unsigned>(m_pad * sizeof(NodeT));
+  double acc0           = 0.0;
+  const int n_groups    = (n_trees + kTreeGroup - 1) / kTreeGroup;
+  for (int g = 0; g < n_groups; ++g) {
+    const int buf = g & 1;
+    CpAsyncWaitAll();
+    __syncthreads();  // group g has landed (and the X tile, on the first pass)
+    if (g + 1 < n_groups) stage_group(g + 1, buf ^ 1);
+    const unsigned gbase = tree0 + static_cast<unsigned>(buf * kTreeGroup * slot_bytes);
+    const int nt         = min(kTreeGroup, n_trees - g * kTreeGroup);
+    if (tid < rows_here) {
+      unsigned p8[kTreeGroup];
+#pragma unroll
+      for (int j = 0; j < kTreeGroup; ++j) p8[j] = 0;
+      if (nt == kTreeGroup) {
+        for (int step = 0; step < max_steps; ++step) {
+#pragma unroll
+          for (int j = 0; j < kTreeGroup; ++j) {
+            T split;
+            int foff;
+            LdsNode(gbase + j * static_cast<unsigned>(slot_bytes) + (p8[j] << kNodeShift), split, foff);
+            if (foff >= 0) {
+              const T x = LdsX(xcol_s + foff, T());
+              p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
+            }
+          }
+        }
+      } else {
+        for (int step = 0; step < max_steps; ++step) {
+          for (int j = 0; j < nt; ++j) {
+            T split;
+            int foff;
+            LdsNode(gbase + j * static_cast<unsigned>(slot_bytes) + (p8[j] << kNodeShift), split, foff);
+            if (foff >= 0) {
+              const T x = LdsX(xcol_s + foff, T());
+              p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kTreeGroup; ++j) {
+        if (j < nt) {
+          if (K == 1) {
+            acc0 += LdsF64(gbase + j * static_cast<unsigned>(slot_bytes) + leaf_o + p8[j]);
+          } else {
+            const double* lf = leaves + static_cast<int64_t>(trees[g * kTreeGroup + j].node_off + (p8[j] >> 3)) * K;
+            for (int k = 0; k < K; ++k) accs[k * RB + tid] += lf[k];
+          }
+        }
+      }
+    }
+    __syncthreads();  // everyone is done with buffer `buf` before it is refilled
+  }
+  if (tid < rows_here) {
+    const int64_t row = row0 + tid;
+    if (K == 1) {
+      pred[row * ldp] = acc0;
     } else {
-      for (int k = 0; k < K; ++k) pred[row * ldp + k] = 0.0;
+      for (int k = 0; k < K; ++k) pred[row * ldp + k] = accs[k * RB + tid];
     }
   }
+}
+
+// Fallback: nodes and leaves stay in global memory, X is read directly.
+template <typename T>
+__global__ void __launch_bounds__(128)
+  k_predict_global(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
+                   const TreePtrs* __restrict__ trees, const typename NodeOf<T>::type* __restrict__ nodes,
+                   const double* __restrict__ leaves, double* __restrict__ pred, int64_t ldp)
+{
+  using NodeT       = typename NodeOf<T>::type;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= n_rows) return;
+  const T* xr = X + row * ldx;
+  for (int k = 0; k < K; ++k) pred[row * ldp + k] = 0.0;
   for (int t = 0; t < n_trees; ++t) {
     const int off = trees[t].node_off;
-    const int mn  = trees[t].max_nodes;
     int pos       = 0;
     for (int depth = 0; depth < 100; ++depth) {
-      const PNode n = nodes[off + pos];
-      // a split node on the last level of the arrays has no children to go to: stop there
-      if (n.feature == -1 || 2 * pos + 2 >= mn) break;
-      const double xv = static_cast<double>(kStage ? xs[n.feature * RBP + tid] : xr[n.feature]);
-      pos             = xv <= n.split ? 2 * pos + 1 : 2 * pos + 2;
+      const NodeT n = nodes[off + pos];
+      if (n.foff < 0) break;
+      pos = 2 * pos + 1 + (xr[n.foff] <= n.split ? 0 : 1);
     }
     const double* lf = leaves + static_cast<int64_t>(off + pos) * K;
-    if (K == 1) {
-      acc0 += lf[0];
-    } else if (acc_in_smem) {
-      for (int k = 0; k < K; ++k) accs[k * RB + tid] += lf[k];
-    } else {
-      for (int k = 0; k < K; ++k) pred[row * ldp + k] += lf[k];
-    }
+    for (int k = 0; k < K; ++k) pred[row * ldp + k] += lf[k];
   }
-  if (K == 1) {
-    pred[row * ldp] = acc0;
-  } else if (acc_in_smem) {
-    for (int k = 0; k < K; ++k) pred[row * ldp + k] = accs[k * RB + tid];
-  }
+  (void)F;
+}
+
+template <typename T, int RB>
+size_t TiledSmem(int F, int K, int m_pad)
+{
+  using NodeT = typename NodeOf<T>::type;
+  const size_t x_bytes    = (sizeof(T) * static_cast<size_t>(F) * (RB + 1) + 15) / 16 * 16;
+  const size_t a_bytes    = K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
+  const size_t slot_bytes = static_cast<size_t>(m_pad) * (sizeof(NodeT) + (K == 1 ? sizeof(double) : 0));
+  return x_bytes + a_bytes + 2 * kTreeGroup * slot_bytes;
+}
+
+template <typename T, int RB>
+void LaunchTiled(const T* X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees, const TreePtrs* d_trees,
+                 const typename NodeOf<T>::type* nodes, const double* leaves, double* pred, int64_t ldp, int m_pad,
+                 int max_steps, size_t smem, cudaStream_t stream)
+{
+  if (smem > 48 * 1024)
+    LBK_CUDA(cudaFuncSetAttribute(k_predict_tiled<T, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  const unsigned grid = static_cast<unsigned>((n_rows + RB - 1) / RB);
+  k_predict_tiled<T, RB><<<grid, RB, smem, stream>>>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp,
+                                                      m_pad, max_steps);
+  LBK_LAUNCH_CHECK();
 }
 
 }  // namespace
@@ -126,6 +316,7 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
                    const double* const* leaf, const int32_t* const* feat, const double* const* split,
                    const int32_t* max_nodes, double* pred, int64_t ldp, cudaStream_t stream)
 {
+  using NodeT = typename NodeOf<T>::type;
   if (n_rows < 1) return;  // an empty shard returns at once (reference: predict.cu:35)
   if (n_trees == 0) {
     LBK_CUDA(cudaMemset2DAsync(pred, sizeof(double) * ldp, 0, sizeof(double) * K, n_rows, stream));
@@ -133,6 +324,7 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
   }
   std::vector<TreePtrs> h(n_trees);
   int64_t total_nodes = 0;
+  int m_max           = 1;
   for (int t = 0; t < n_trees; ++t) {
     LBK_EXPECT(leaf[t] && feat[t] && split[t] && max_nodes[t] >= 1, "bad tree arrays");
     h[t].leaf      = leaf[t];
@@ -141,35 +333,43 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
     h[t].max_nodes = max_nodes[t];
     LBK_EXPECT(total_nodes + max_nodes[t] < (int64_t{1} << 31), "ensemble too large");
     h[t].node_off = static_cast<int>(total_nodes);
-    total_nodes += max_nodes[t];
+    total_nodes += (max_nodes[t] + 1) & ~1;  // even offsets keep every tree 16-byte aligned
+    m_max = max_nodes[t] > m_max ? max_nodes[t] : m_max;
   }
+  const int m_pad = (m_max + 1) & ~1;
+  // a walk takes at most floor(log2(M)) steps through an array of M heap-ordered nodes (the
+  // reference's own cap is 100)
+  int max_steps = 0;
+  while ((2 << max_steps) <= m_max) ++max_steps;
+  if (max_steps > 100) max_steps = 100;
+
+  // largest row tile whose X slice, accumulators and two tree groups fit in shared memory
+  const size_t budget = static_cast<size_t>(ctx->max_smem_optin) - 1024;
+  int rb              = 0;
+  if (TiledSmem<T, 256>(F, K, m_pad) <= budget) rb = 256;
+  else if (TiledSmem<T, 128>(F, K, m_pad) <= budget) rb = 128;
+  else if (TiledSmem<T, 64>(F, K, m_pad) <= budget) rb = 64;
+  else if (TiledSmem<T, 32>(F, K, m_pad) <= budget) rb = 32;
+  if (rb > 0) LBK_EXPECT(static_cast<int64_t>(F) * (rb + 1) * static_cast<int64_t>(sizeof(T)) < (int64_t{1} << 31), "tile too large");
+
   TreePtrs* d_trees = s.alloc<TreePtrs>(n_trees);
-  PNode* nodes      = s.alloc<PNode>(total_nodes);
+  NodeT* nodes      = s.alloc<NodeT>(total_nodes);
   double* leaves    = s.alloc<double>(total_nodes * K);
   LBK_CUDA(cudaMemcpyAsync(d_trees, h.data(), sizeof(TreePtrs) * n_trees, cudaMemcpyHostToDevice, stream));
   LBK_CUDA(cudaStreamSynchronize(stream));  // h is a local; the copy must have read it
-  k_pack_trees<<<n_trees, 256, 0, stream>>>(d_trees, K, nodes, leaves);
+  const int xmul = rb > 0 ? (rb + 1) * static_cast<int>(sizeof(T)) : 1;
+  k_pack_trees<NodeT><<<n_trees, 256, 0, stream>>>(d_trees, K, F, xmul, nodes, leaves);
   LBK_LAUNCH_CHECK();
 
-  constexpr int RB      = 128;
-  const size_t x_bytes  = (sizeof(T) * static_cast<size_t>(F) * (RB + 1) + 15) / 16 * 16;
-  const size_t a_bytes  = K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
-  const size_t budget   = static_cast<size_t>(ctx->max_smem_optin) - 1024;
-  const bool stage      = x_bytes <= budget;
-  const int acc_in_smem = (K > 1 && (stage ? x_bytes : 0) + a_bytes <= budget) ? 1 : 0;
-  const size_t smem     = (stage ? x_bytes : 0) + (acc_in_smem ? a_bytes : 0);
-  const unsigned grid   = static_cast<unsigned>((n_rows + RB - 1) / RB);
-  if (stage) {
-    if (smem > 48 * 1024)
-      LBK_CUDA(cudaFuncSetAttribute(k_predict<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    k_predict<T, true><<<grid, RB, smem, stream>>>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp,
-                                                    acc_in_smem);
-  } else {
-    if (smem > 48 * 1024)
-      LBK_CUDA(cudaFuncSetAttribute(k_predict<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    k_predict<T, false><<<grid, RB, smem, stream>>>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp,
-                                                     acc_in_smem);
+  switch (rb) {
+    case 256: LaunchTiled<T, 256>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp, m_pad, max_steps, TiledSmem<T, 256>(F, K, m_pad), stream); return;
+    case 128: LaunchTiled<T, 128>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp, m_pad, max_steps, TiledSmem<T, 128>(F, K, m_pad), stream); return;
+    case 64: LaunchTiled<T, 64>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp, m_pad, max_steps, TiledSmem<T, 64>(F, K, m_pad), stream); return;
+    case 32: LaunchTiled<T, 32>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp, m_pad, max_steps, TiledSmem<T, 32>(F, K, m_pad), stream); return;
+    default: break;
   }
+  const unsigned grid = static_cast<unsigned>((n_rows + 127) / 128);
+  k_predict_global<T><<<grid, 128, 0, stream>>>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp);
   LBK_LAUNCH_CHECK();
 }
 
