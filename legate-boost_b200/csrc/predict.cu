@@ -13,9 +13,13 @@
 //     (float split, int feature) - "x <= split" with x a float is the same test as
 //     "x <= the largest float not above split", so the split is rounded down once at packing time
 //     and the walk compares floats; for float64 X a node is 16 bytes.
-//   * Trees are brought into shared memory four at a time (cp.async, double buffered) together
-//     with their leaf values; a thread walks the four trees of a group as four independent
-//     chains, which hides the shared-memory latency that a single dependent chain exposes.
+//   * At packing time every tree is completed to the depth S of the deepest one: below a leaf
+//     the nodes become pass-through nodes (split = +inf) and the leaf's value is copied to the
+//     bottom level.  A walk is then exactly S steps of "load node, load x, compare, descend" with
+//     no leaf test, and only the bottom level of leaf values is kept.
+//   * Trees are brought into shared memory in groups of up to eight (cp.async, double buffered)
+//     together with their bottom-level leaf values; a thread walks the trees of a group as
+//     independent chains, which hides the shared-memory latency that one dependent chain exposes.
 //   * Predictions are accumulated in float64 in tree order (bit-identical to the reference's
 //     tree-by-tree accumulation) and written once.
 // A fallback kernel with the nodes in global memory covers shapes whose tile or trees do not fit.
@@ -120,16 +124,51 @@ __device__ inline double LdsF64(unsigned addr)
   return v;
 }
 
-constexpr int kTreeGroup = 4;
+// Completed-tree packing for the tiled kernel.  For tree t: nodes_c[t*NI + i], i < 2^S - 1, are the
+// internal levels of a complete tree of depth S; leaves_c[(t*NL + j)*K + k], j < 2^S, the values of
+// its bottom level.  A node whose children would fall outside the input arrays, or whose feature
+// id is outside [0, F), counts as a leaf, so a walk can never leave the arrays.
+template <typename NodeT>
+__global__ void k_pack_complete(const TreePtrs* __restrict__ trees, int K, int F, int xmul, int S, int NI, int NL,
+                                NodeT* __restrict__ nodes_c, double* __restrict__ leaves_c)
+{
+  const TreePtrs t = trees[blockIdx.x];
+  const int M      = t.max_nodes;
+  const int total  = (2 << S) - 1;  // nodes of the complete tree
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int L = 31 - __clz(i + 1);
+    int cover   = -1;  // first leaf on the path root -> i
+    for (int l = 0; l <= L; ++l) {
+      const int a   = ((i + 1) >> (L - l)) - 1;
+      const int f   = a < M ? t.feature[a] : -1;
+      if (a >= M || f < 0 || f >= F || 2 * a + 2 >= M) {
+        cover = a;
+        break;
+      }
+    }
+    if (L < S) {
+      NodeT n;
+      if (cover >= 0) {
+        MakeNode(n, static_cast<double>(INFINITY), 0);  // pass-through: always descends left
+      } else {
+        MakeNode(n, t.split[i], t.feature[i] * xmul);
+      }
+      nodes_c[static_cast<int64_t>(blockIdx.x) * NI + i] = n;
+    } else {
+      const int j = i - ((1 << S) - 1);
+      for (int k = 0; k < K; ++k)
+        leaves_c[(static_cast<int64_t>(blockIdx.x) * NL + j) * K + k] = t.leaf[static_cast<int64_t>(cover) * K + k];
+    }
+  }
+}
 
 // Tiled kernel.  Shared memory: X tile [F][RB+1] | accumulators [K][RB] (K > 1) |
-// 2 x kTreeGroup x slot, slot = m_pad nodes (+ m_pad leaf values when K == 1); m_pad is even and
-// every tree starts at an even node offset, so all copies are 16-byte aligned.
-template <typename T, int RB>
+// NBUF x TG x slot, slot = NI nodes (+ NL leaf values when K == 1).
+template <typename T, int RB, int TG>
 __global__ void __launch_bounds__(RB)
   k_predict_tiled(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
-                  const TreePtrs* __restrict__ trees, const typename NodeOf<T>::type* __restrict__ nodes,
-                  const double* __restrict__ leaves, double* __restrict__ pred, int64_t ldp, int m_pad, int max_steps)
+                  const typename NodeOf<T>::type* __restrict__ nodes_c, const double* __restrict__ leaves_c,
+                  double* __restrict__ pred, int64_t ldp, int S, int NI, int NL)
 {
   using NodeT = typename NodeOf<T>::type;
   constexpr int RBP = RB + 1;
@@ -138,29 +177,28 @@ __global__ void __launch_bounds__(RB)
   size_t off = (sizeof(T) * static_cast<size_t>(F) * RBP + 15) / 16 * 16;
   double* accs = reinterpret_cast<double*>(smem_raw + off);
   off += K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
-  const size_t slot_bytes = static_cast<size_t>(m_pad) * (sizeof(NodeT) + (K == 1 ? sizeof(double) : 0));
-  unsigned char* tree_s   = smem_raw + off;  // [2][kTreeGroup][slot]
+  const unsigned node_bytes = static_cast<unsigned>(NI * sizeof(NodeT));
+  const unsigned slot_bytes = node_bytes + (K == 1 ? static_cast<unsigned>(NL * sizeof(double)) : 0u);
+  unsigned char* tree_s     = smem_raw + off;
 
   const int tid       = threadIdx.x;
   const int64_t row0  = static_cast<int64_t>(blockIdx.x) * RB;
   const int rows_here = static_cast<int>((n_rows - row0) < RB ? (n_rows - row0) : RB);
+  const unsigned tree0 = static_cast<unsigned>(__cvta_generic_to_shared(tree_s));
+  const int n_groups   = (n_trees + TG - 1) / TG;
 
   // group of trees -> shared memory, 16 bytes per copy (nodes, then leaves when K == 1)
   auto stage_group = [&](int group, int buf) {
-    for (int j = 0; j < kTreeGroup; ++j) {
-      const int t = group * kTreeGroup + j;
+    for (int j = 0; j < TG; ++j) {
+      const int t = group * TG + j;
       if (t >= n_trees) break;
-      const TreePtrs tp   = trees[t];
-      unsigned char* dst  = tree_s + (static_cast<size_t>(buf) * kTreeGroup + j) * slot_bytes;
-      const unsigned d_s  = static_cast<unsigned>(__cvta_generic_to_shared(dst));
-      const int mp         = (tp.max_nodes + 1) & ~1;  // the packed arrays are padded to even counts
-      const int node_units = mp * static_cast<int>(sizeof(NodeT)) / 16;
-      const unsigned char* src = reinterpret_cast<const unsigned char*>(nodes + tp.node_off);
-      for (int i = tid; i < node_units; i += RB) CpAsync16(d_s + i * 16, src + static_cast<size_t>(i) * 16);
+      const unsigned d_s       = tree0 + static_cast<unsigned>(buf * TG + j) * slot_bytes;
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(nodes_c + static_cast<int64_t>(t) * NI);
+      for (unsigned i = tid; i < node_bytes / 16; i += RB) CpAsync16(d_s + i * 16, src + static_cast<size_t>(i) * 16);
       if (K == 1) {
-        const unsigned l_s = d_s + static_cast<unsigned>(m_pad * sizeof(NodeT));
-        const unsigned char* lsrc = reinterpret_cast<const unsigned char*>(leaves + tp.node_off);
-        for (int i = tid; i < mp / 2; i += RB) CpAsync16(l_s + i * 16, lsrc + static_cast<size_t>(i) * 16);
+        const unsigned char* lsrc = reinterpret_cast<const unsigned char*>(leaves_c + static_cast<int64_t>(t) * NL);
+        for (unsigned i = tid; i < static_cast<unsigned>(NL) / 2; i += RB)
+          CpAsync16(d_s + node_bytes + i * 16, lsrc + static_cast<size_t>(i) * 16);
       }
     }
     CpAsyncCommit();
@@ -190,59 +228,55 @@ __global__ void __launch_bounds__(RB)
   if (K > 1)
     for (int k = 0; k < K; ++k) accs[k * RB + tid] = 0.0;
 
-  // The walk works on 32-bit shared addresses.  `p8` is the node index times 8: the byte offset
-  // of the leaf value and (times sizeof(NodeT)/8) of the node.  A leaf keeps its position, so every
-  // tree of a group takes the same fixed number of steps and the chains stay independent.
+  // The walk works on 32-bit shared addresses.  `p8` is the heap index of the current node times 8
+  // (times sizeof(NodeT)/8 it is the node's byte offset); after S steps it points into the bottom
+  // level, whose values start at heap index 2^S - 1.
   constexpr unsigned kNodeShift = sizeof(NodeT) == 16 ? 1 : 0;
-  const unsigned xcol_s = static_cast<unsigned>(__cvta_generic_to_shared(xs + tid));
-  const unsigned tree0  = static_cast<unsigned>(__cvta_generic_to_shared(tree_s));
-  const unsigned leaf_o = static_cast<unsigned>(m_pad * sizeof(NodeT));
-  double acc0           = 0.0;
-  const int n_groups    = (n_trees + kTreeGroup - 1) / kTreeGroup;
+  const unsigned xcol_s   = static_cast<unsigned>(__cvta_generic_to_shared(xs + tid));
+  const unsigned leaf_adj = node_bytes - 8u * ((1u << S) - 1u);
+  const bool one_buffer   = n_groups == 1;
+  double acc0             = 0.0;
   for (int g = 0; g < n_groups; ++g) {
-    const int buf = g & 1;
+    const int buf = one_buffer ? 0 : (g & 1);
     CpAsyncWaitAll();
     __syncthreads();  // group g has landed (and the X tile, on the first pass)
     if (g + 1 < n_groups) stage_group(g + 1, buf ^ 1);
-    const unsigned gbase = tree0 + static_cast<unsigned>(buf * kTreeGroup * slot_bytes);
-    const int nt         = min(kTreeGroup, n_trees - g * kTreeGroup);
+    const unsigned gbase = tree0 + static_cast<unsigned>(buf * TG) * slot_bytes;
+    const int nt         = min(TG, n_trees - g * TG);
     if (tid < rows_here) {
-      unsigned p8[kTreeGroup];
+      unsigned p8[TG];
 #pragma unroll
-      for (int j = 0; j < kTreeGroup; ++j) p8[j] = 0;
-      if (nt == kTreeGroup) {
-        for (int step = 0; step < max_steps; ++step) {
+      for (int j = 0; j < TG; ++j) p8[j] = 0;
+      if (nt == TG) {
+        for (int step = 0; step < S; ++step) {
 #pragma unroll
-          for (int j = 0; j < kTreeGroup; ++j) {
+          for (int j = 0; j < TG; ++j) {
             T split;
             int foff;
-            LdsNode(gbase + j * static_cast<unsigned>(slot_bytes) + (p8[j] << kNodeShift), split, foff);
-            if (foff >= 0) {
-              const T x = LdsX(xcol_s + foff, T());
-              p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
-            }
+            LdsNode(gbase + j * slot_bytes + (p8[j] << kNodeShift), split, foff);
+            const T x = LdsX(xcol_s + foff, T());
+            p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
           }
         }
       } else {
-        for (int step = 0; step < max_steps; ++step) {
+        for (int step = 0; step < S; ++step) {
           for (int j = 0; j < nt; ++j) {
             T split;
             int foff;
-            LdsNode(gbase + j * static_cast<unsigned>(slot_bytes) + (p8[j] << kNodeShift), split, foff);
-            if (foff >= 0) {
-              const T x = LdsX(xcol_s + foff, T());
-              p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
-            }
+            LdsNode(gbase + j * slot_bytes + (p8[j] << kNodeShift), split, foff);
+            const T x = LdsX(xcol_s + foff, T());
+            p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
           }
         }
       }
 #pragma unroll
-      for (int j = 0; j < kTreeGroup; ++j) {
+      for (int j = 0; j < TG; ++j) {
         if (j < nt) {
           if (K == 1) {
-            acc0 += LdsF64(gbase + j * static_cast<unsigned>(slot_bytes) + leaf_o + p8[j]);
+            acc0 += LdsF64(gbase + j * slot_bytes + leaf_adj + p8[j]);
           } else {
-            const double* lf = leaves + static_cast<int64_t>(trees[g * kTreeGroup + j].node_off + (p8[j] >> 3)) * K;
+            const int64_t lj = static_cast<int64_t>(g * TG + j) * NL + ((p8[j] >> 3) - ((1u << S) - 1u));
+            const double* lf = leaves_c + lj * K;
             for (int k = 0; k < K; ++k) accs[k * RB + tid] += lf[k];
           }
         }
@@ -260,10 +294,10 @@ __global__ void __launch_bounds__(RB)
   }
 }
 
-// Fallback: nodes and leaves stay in global memory, X is read directly.
+// Fallback: original (uncompleted) trees, nodes and leaves in global memory, X read directly.
 template <typename T>
 __global__ void __launch_bounds__(128)
-  k_predict_global(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
+  k_predict_global(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int K, int n_trees,
                    const TreePtrs* __restrict__ trees, const typename NodeOf<T>::type* __restrict__ nodes,
                    const double* __restrict__ leaves, double* __restrict__ pred, int64_t ldp)
 {
@@ -283,29 +317,29 @@ __global__ void __launch_bounds__(128)
     const double* lf = leaves + static_cast<int64_t>(off + pos) * K;
     for (int k = 0; k < K; ++k) pred[row * ldp + k] += lf[k];
   }
-  (void)F;
 }
 
-template <typename T, int RB>
-size_t TiledSmem(int F, int K, int m_pad)
+template <typename T>
+size_t TiledSmem(int rb, int tg, int nbuf, int F, int K, int NI, int NL)
 {
   using NodeT = typename NodeOf<T>::type;
-  const size_t x_bytes    = (sizeof(T) * static_cast<size_t>(F) * (RB + 1) + 15) / 16 * 16;
-  const size_t a_bytes    = K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
-  const size_t slot_bytes = static_cast<size_t>(m_pad) * (sizeof(NodeT) + (K == 1 ? sizeof(double) : 0));
-  return x_bytes + a_bytes + 2 * kTreeGroup * slot_bytes;
+  const size_t x_bytes    = (sizeof(T) * static_cast<size_t>(F) * (rb + 1) + 15) / 16 * 16;
+  const size_t a_bytes    = K > 1 ? sizeof(double) * static_cast<size_t>(K) * rb : 0;
+  const size_t slot_bytes = static_cast<size_t>(NI) * sizeof(NodeT) + (K == 1 ? static_cast<size_t>(NL) * sizeof(double) : 0);
+  return x_bytes + a_bytes + static_cast<size_t>(nbuf) * tg * slot_bytes;
 }
 
-template <typename T, int RB>
-void LaunchTiled(const T* X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees, const TreePtrs* d_trees,
-                 const typename NodeOf<T>::type* nodes, const double* leaves, double* pred, int64_t ldp, int m_pad,
-                 int max_steps, size_t smem, cudaStream_t stream)
+template <typename T, int RB, int TG>
+void LaunchTiled(const T* X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
+                 const typename NodeOf<T>::type* nodes_c, const double* leaves_c, double* pred, int64_t ldp, int S,
+                 int NI, int NL, size_t smem, cudaStream_t stream)
 {
   if (smem > 48 * 1024)
-    LBK_CUDA(cudaFuncSetAttribute(k_predict_tiled<T, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    LBK_CUDA(cudaFuncSetAttribute(k_predict_tiled<T, RB, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
   const unsigned grid = static_cast<unsigned>((n_rows + RB - 1) / RB);
-  k_predict_tiled<T, RB><<<grid, RB, smem, stream>>>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp,
-                                                      m_pad, max_steps);
+  k_predict_tiled<T, RB, TG><<<grid, RB, smem, stream>>>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S,
+                                                          NI, NL);
   LBK_LAUNCH_CHECK();
 }
 
@@ -333,44 +367,70 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
     h[t].max_nodes = max_nodes[t];
     LBK_EXPECT(total_nodes + max_nodes[t] < (int64_t{1} << 31), "ensemble too large");
     h[t].node_off = static_cast<int>(total_nodes);
-    total_nodes += (max_nodes[t] + 1) & ~1;  // even offsets keep every tree 16-byte aligned
+    total_nodes += max_nodes[t];
     m_max = max_nodes[t] > m_max ? max_nodes[t] : m_max;
   }
-  const int m_pad = (m_max + 1) & ~1;
-  // a walk takes at most floor(log2(M)) steps through an array of M heap-ordered nodes (the
-  // reference's own cap is 100)
-  int max_steps = 0;
-  while ((2 << max_steps) <= m_max) ++max_steps;
-  if (max_steps > 100) max_steps = 100;
+  // a walk through M heap-ordered nodes takes at most S = floor(log2(M)) steps
+  int S = 0;
+  while ((2 << S) <= m_max) ++S;
+  const int NI = (1 << S) > 2 ? (1 << S) : 2;  // internal nodes 2^S - 1, padded to a 16-byte multiple
+  const int NL = NI;                           // bottom level 2^S values, same padding
 
-  // largest row tile whose X slice, accumulators and two tree groups fit in shared memory
+  // tile shape: rows per block RB, trees per group TG, one or two group buffers
   const size_t budget = static_cast<size_t>(ctx->max_smem_optin) - 1024;
-  int rb              = 0;
-  if (TiledSmem<T, 256>(F, K, m_pad) <= budget) rb = 256;
-  else if (TiledSmem<T, 128>(F, K, m_pad) <= budget) rb = 128;
-  else if (TiledSmem<T, 64>(F, K, m_pad) <= budget) rb = 64;
-  else if (TiledSmem<T, 32>(F, K, m_pad) <= budget) rb = 32;
-  if (rb > 0) LBK_EXPECT(static_cast<int64_t>(F) * (rb + 1) * static_cast<int64_t>(sizeof(T)) < (int64_t{1} << 31), "tile too large");
+  int rb = 0, tg = 0;
+  size_t smem = 0;
+  if (S <= 14) {
+    const int rbs[4] = {256, 128, 64, 32};
+    const int tgs[4] = {8, 4, 2, 1};
+    for (int ri = 0; ri < 4 && rb == 0; ++ri) {
+      if (static_cast<int64_t>(F) * (rbs[ri] + 1) * static_cast<int64_t>(sizeof(T)) >= (int64_t{1} << 30)) continue;
+      for (int ti = 0; ti < 4; ++ti) {
+        if (tgs[ti] > n_trees && tgs[ti] > 1) continue;  // no wider than the ensemble
+        const int nbuf = n_trees > tgs[ti] ? 2 : 1;
+        const size_t need = TiledSmem<T>(rbs[ri], tgs[ti], nbuf, F, K, NI, NL);
+        if (need <= budget) {
+          rb   = rbs[ri];
+          tg   = tgs[ti];
+          smem = need;
+          break;
+        }
+      }
+    }
+  }
 
   TreePtrs* d_trees = s.alloc<TreePtrs>(n_trees);
-  NodeT* nodes      = s.alloc<NodeT>(total_nodes);
-  double* leaves    = s.alloc<double>(total_nodes * K);
   LBK_CUDA(cudaMemcpyAsync(d_trees, h.data(), sizeof(TreePtrs) * n_trees, cudaMemcpyHostToDevice, stream));
   LBK_CUDA(cudaStreamSynchronize(stream));  // h is a local; the copy must have read it
-  const int xmul = rb > 0 ? (rb + 1) * static_cast<int>(sizeof(T)) : 1;
-  k_pack_trees<NodeT><<<n_trees, 256, 0, stream>>>(d_trees, K, F, xmul, nodes, leaves);
-  LBK_LAUNCH_CHECK();
 
-  switch (rb) {
-    case 256: LaunchTiled<T, 256>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp, m_pad, max_steps, TiledSmem<T, 256>(F, K, m_pad), stream); return;
-    case 128: LaunchTiled<T, 128>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp, m_pad, max_steps, TiledSmem<T, 128>(F, K, m_pad), stream); return;
-    case 64: LaunchTiled<T, 64>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp, m_pad, max_steps, TiledSmem<T, 64>(F, K, m_pad), stream); return;
-    case 32: LaunchTiled<T, 32>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp, m_pad, max_steps, TiledSmem<T, 32>(F, K, m_pad), stream); return;
-    default: break;
+  if (rb == 0) {
+    NodeT* nodes   = s.alloc<NodeT>(total_nodes);
+    double* leaves = s.alloc<double>(total_nodes * K);
+    k_pack_trees<NodeT><<<n_trees, 256, 0, stream>>>(d_trees, K, F, 1, nodes, leaves);
+    LBK_LAUNCH_CHECK();
+    const unsigned grid = static_cast<unsigned>((n_rows + 127) / 128);
+    k_predict_global<T><<<grid, 128, 0, stream>>>(X, ldx, n_rows, K, n_trees, d_trees, nodes, leaves, pred, ldp);
+    LBK_LAUNCH_CHECK();
+    return;
   }
-  const unsigned grid = static_cast<unsigned>((n_rows + 127) / 128);
-  k_predict_global<T><<<grid, 128, 0, stream>>>(X, ldx, n_rows, F, K, n_trees, d_trees, nodes, leaves, pred, ldp);
+  NodeT* nodes_c   = s.alloc<NodeT>(static_cast<size_t>(n_trees) * NI);
+  double* leaves_c = s.alloc<double>(static_cast<size_t>(n_trees) * NL * K);
+  k_pack_complete<NodeT><<<n_trees, 256, 0, stream>>>(d_trees, K, F, (rb + 1) * static_cast<int>(sizeof(T)), S, NI, NL,
+                                                      nodes_c, leaves_c);
   LBK_LAUNCH_CHECK();
+#define LBK_PREDICT_CASE(RB_, TG_)                                                                                  \
+  if (rb == RB_ && tg == TG_) {                                                                                     \
+    LaunchTiled<T, RB_, TG_>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S, NI, NL, smem, stream); \
+    return;                                                                                                         \
+  }
+#define LBK_PREDICT_ROW(RB_) LBK_PREDICT_CASE(RB_, 8) LBK_PREDICT_CASE(RB_, 4) LBK_PREDICT_CASE(RB_, 2) LBK_PREDICT_CASE(RB_, 1)
+  LBK_PREDICT_ROW(256)
+  LBK_PREDICT_ROW(128)
+  LBK_PREDICT_ROW(64)
+  LBK_PREDICT_ROW(32)
+#undef LBK_PREDICT_ROW
+#undef LBK_PREDICT_CASE
+  throw Error(LBK_ERR_ARGUMENT, "predict: no kernel for the chosen tile");
 }
 
 template void PredictLaunch<float>(lbk_context*, Scratch&, const float*, int64_t, int64_t, int, int, int,
