@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(256)
   const bool active = f0 + lane < F;
   const T* spl      = sp + lane;
   BinT* out         = bins + static_cast<int64_t>(g) * n_rows * kGroup;
-  constexpr int U   = 4;  // rows per warp in flight
+  constexpr int U   = 8;  // rows per warp in flight
   const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   const int64_t w0          = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5);
   for (int64_t base = w0 * U; base < n_rows; base += warps_total * U) {
@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t row = base + u;
-      x[u]   = (active && row < n_rows) ? X[row * ldx + f0 + lane] : static_cast<T>(-INFINITY);
+      x[u]   = (active && row < n_rows) ? __ldcs(X + row * ldx + f0 + lane) : static_cast<T>(-INFINITY);
       pos[u] = 0;
     }
     for (int step = P >> 1; step >= 1; step >>= 1) {
