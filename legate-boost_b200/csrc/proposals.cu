@@ -160,6 +160,19 @@ __global__ void k_write_proposals(const T* __restrict__ uniq, int S, const int32
   }
 }
 
+__device__ inline float LdsT(unsigned addr, float)
+{
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ inline double LdsT(unsigned addr, double)
+{
+  double v;
+  asm volatile("ld.shared.f64 %0, [%1];\n" : "=d"(v) : "r"(addr));
+  return v;
+}
+
 // One warp per row, one lane per feature of the group.
 //
 // Shared-memory variant: the proposals of the group are kept transposed and padded, sp[j][lane] =
@@ -189,28 +202,55 @@ __global__ void __launch_bounds__(256)
   }
   __syncthreads();
   const bool active = f0 + lane < F;
-  const T* spl      = sp + lane;
-  BinT* out         = bins + static_cast<int64_t>(g) * n_rows * kGroup;
+  // The search runs on byte offsets into this lane's column of the table (pitch = one table row).
+  // The three top levels of the search (seven pivots) are held in registers: they are the same
+  // for every row a lane sees, which leaves log2(P) - 3 shared-memory probes per element.
+  constexpr unsigned kPitch = kGroup * sizeof(T);
+  const unsigned col_s      = static_cast<unsigned>(__cvta_generic_to_shared(sp + lane));
+  const bool top3           = P >= 8;
+  T piv[7];
+#pragma unroll
+  for (int i = 0; i < 7; ++i) piv[i] = top3 ? sp[((i + 1) * (P >> 3) - 1) * kGroup + lane] : static_cast<T>(INFINITY);
+  const unsigned half = (P >> 1) * kPitch, quarter = (P >> 2) * kPitch, eighth = (P >> 3) * kPitch;
+  BinT* out         = bins + static_cast<int64_t>(g) * n_rows * kGroup + lane;
+  const T* xin      = X + f0 + lane;
   constexpr int U   = 8;  // rows per warp in flight
   const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   const int64_t w0          = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5);
   for (int64_t base = w0 * U; base < n_rows; base += warps_total * U) {
     T x[U];
-    int pos[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t row = base + u;
-      x[u]   = (active && row < n_rows) ? __ldcs(X + row * ldx + f0 + lane) : static_cast<T>(-INFINITY);
-      pos[u] = 0;
-    }
-    for (int step = P >> 1; step >= 1; step >>= 1) {
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (spl[(pos[u] + step - 1) * kGroup] < x[u]) pos[u] += step;
-    }
+    unsigned posb[U];
+    const T* xr = xin + base * ldx;
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      if (base + u < n_rows) out[(base + u) * kGroup + lane] = static_cast<BinT>(pos[u]);
+      x[u] = (active && base + u < n_rows) ? __ldcs(xr + u * ldx) : static_cast<T>(-INFINITY);
+    int first_step = P >> 1;
+    if (top3) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const bool c1 = piv[3] < x[u];                       // proposal P/2 - 1
+        const T p2    = c1 ? piv[5] : piv[1];                // 3P/4 - 1 or P/4 - 1
+        const bool c2 = p2 < x[u];
+        const T p3    = c1 ? (c2 ? piv[6] : piv[4]) : (c2 ? piv[2] : piv[0]);
+        const bool c3 = p3 < x[u];
+        posb[u]       = (c1 ? half : 0u) + (c2 ? quarter : 0u) + (c3 ? eighth : 0u);
+      }
+      first_step = P >> 4;
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) posb[u] = 0;
+    }
+    for (int step = first_step; step >= 1; step >>= 1) {
+      const unsigned probe = col_s + static_cast<unsigned>(step - 1) * kPitch;
+      const unsigned adv   = static_cast<unsigned>(step) * kPitch;
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (LdsT(probe + posb[u], T()) < x[u]) posb[u] += adv;
+    }
+    BinT* orow = out + base * kGroup;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (base + u < n_rows) orow[u * kGroup] = static_cast<BinT>(posb[u] / kPitch);
   }
 }
 
