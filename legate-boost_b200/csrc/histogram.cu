@@ -44,9 +44,8 @@ namespace {
 
 constexpr int kHistThreads = 512;
 constexpr int kHistWarps   = kHistThreads / 32;
-constexpr int kTileRows    = 32;    // rows per staged batch (one batch per warp)
-constexpr int kBatchBytes  = kTileRows * (kGroup + 8);  // 32 bin bytes + one pair per row
-constexpr int kWarpRingBytes = 2 * kBatchBytes;         // two batches per warp
+constexpr int kTileRows    = 32;    // chunk sizes are multiples of this
+constexpr int kBatchRows   = 16;    // rows a warp takes per step of its pipeline (one per lane pair)
 constexpr int kDirectRows  = 128;   // chunks up to this size go straight to global atomics
 constexpr int kMinChunk    = 2048;
 constexpr int kSmemBins    = 256;   // bins per feature held by the private histogram
@@ -254,11 +253,11 @@ __global__ void __launch_bounds__(kHistThreads, 2)
   using smem_t = typename A::smem_t;
   using in_t   = typename A::in_t;
   using out_t  = typename A::out_t;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  smem_t* hg           = reinterpret_cast<smem_t*>(smem_raw);
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  // the column arithmetic of the main loop needs the histogram on a 128-byte boundary
+  smem_t* hg = reinterpret_cast<smem_t*>(smem_raw + ((128u - (SmemAddr(smem_raw) & 127u)) & 127u));
   constexpr int hist_rows = kSmem ? kSmemBins : 0;  // every byte value is a valid row
   smem_t* hh           = hg + hist_rows * kGroup;
-  unsigned char* tiles = reinterpret_cast<unsigned char*>(hh + hist_rows * kGroup);
   __shared__ unsigned int s_ticket;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -335,17 +334,21 @@ __global__ void __launch_bounds__(kHistThreads, 2)
     zero();
     __syncthreads();
 
-    // Every warp runs its own pipeline over 32-row batches of the chunk (no block barrier inside).
-    // Per warp there is a two-deep ring in shared memory; a batch is 32 rows x 32 bin bytes plus
-    // 32 pairs.  While batch b is consumed, the bins of the warp's next batch travel from global
-    // to shared memory asynchronously (cp.async, 16 bytes per lane: one instruction moves 16 rows),
-    // its pairs sit in registers (one gather per lane) and the row ids of the batch after that
-    // are being loaded.
-    unsigned char* ring     = tiles + warp * kWarpRingBytes;
-    const unsigned ring_s   = SmemAddr(ring);
-    const unsigned hg_lane  = SmemAddr(hg) + lane * 4;
+    // Every warp runs its own pipeline over 16-row batches of the chunk (no block barrier inside,
+    // no staging in shared memory).  A lane PAIR owns one row of the batch: the even lane loads the
+    // first 16 bin bytes of the row's 32, the odd lane the other 16, straight from global memory
+    // into registers (one 16-byte load per lane, 16 rows = 16 full sectors per instruction).  In
+    // step j of 16 the pair with row slot s handles feature (j xor s) of its half, so that the 32
+    // lanes of a warp always update 32 different columns = 32 different banks, whatever the bins.
+    // The bytes are permuted once per batch (word swaps + one byte permute per word) so that step
+    // j reads the static byte j.  Per 32 updates that leaves the two reductions and nothing else on
+    // the load/store pipe.
+    const unsigned slot16   = lane >> 1, half = lane & 1;
+    const unsigned wsel     = slot16 >> 2, bsel = slot16 & 3;
+    const unsigned perm     = bsel == 0 ? 0x3210u : bsel == 1 ? 0x2301u : bsel == 2 ? 0x1032u : 0x0123u;
+    const unsigned lanebase = SmemAddr(hg) + half * 64 + slot16 * 4;  // hg is 128-byte aligned
     const unsigned hh_off   = static_cast<unsigned>(hist_rows) * kGroup * 4;
-    const unsigned char* gb = reinterpret_cast<const unsigned char*>(gbins);
+    const unsigned char* gb = reinterpret_cast<const unsigned char*>(gbins) + half * 16;
     const int seg_rows = rows_safe >= (1 << 30) ? (1 << 30) : (rows_safe & ~31);
     for (int sb = rb; sb < re; sb += seg_rows) {
       const int se = min(re, sb + seg_rows);
@@ -357,45 +360,37 @@ __global__ void __launch_bounds__(kHistThreads, 2)
         zero();
         __syncthreads();
       }
-      const int nb = (se - sb + 31) >> 5;
+      const int nb = (se - sb + kBatchRows - 1) / kBatchRows;
       auto load_rid = [&](int batch) -> int {
-        const int r = sb + batch * 32 + lane;
+        const int r = sb + batch * kBatchRows + static_cast<int>(slot16);
         return (batch < nb && r < se) ? __ldcg(p.row_index + r) : -1;
       };
-      auto load_pair = [&](int rid) -> int2 {
-        return rid >= 0 ? __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid) * p.K + k))
-                        : make_int2(0, 0);
-      };
-      auto issue_bins = [&](int rid, int buf) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int piece = lane + 32 * j;  // row = piece / 2, half = piece % 2
-          const int rsrc  = __shfl_sync(0xffffffffu, rid, piece >> 1);
-          if (rsrc >= 0)
-            CpAsync16(ring_s + buf * kBatchBytes + piece * 16, gb + static_cast<int64_t>(rsrc) * kGroup + (piece & 1) * 16);
+      // rows beyond the end carry zero pairs and bin 0: they add nothing
+      auto load_row = [&](int rid, int4& w, int2& v) {
+        if (rid >= 0) {
+          w = __ldcs(reinterpret_cast<const int4*>(gb + static_cast<int64_t>(rid) * kGroup));
+          v = __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid) * p.K + k));
+        } else {
+          w = make_int4(0, 0, 0, 0);
+          v = make_int2(0, 0);
         }
-        CpAsyncCommit();
       };
-      int rid_next = load_rid(warp);
-      issue_bins(rid_next, 0);
-      int2 gp_cur = load_pair(rid_next);
-      rid_next    = load_rid(warp + kHistWarps);
-      int buf     = 0;
-      for (int b = warp; b < nb; b += kHistWarps) {
-        issue_bins(rid_next, buf ^ 1);              // batch b + 16
-        const int2 gp_next = load_pair(rid_next);
-        rid_next           = load_rid(b + 2 * kHistWarps);
-        const unsigned bins_s = ring_s + buf * kBatchBytes;
-        const unsigned gp_s   = bins_s + 32 * kGroup;
-        StsV2(gp_s + lane * 8, gp_cur);
-        CpAsyncWait<1>();
-        __syncwarp();
-        const int n = min(32, se - (sb + b * 32));
-        // per row: one byte load (this lane's bin), one broadcast 8-byte load (the pair), two
-        // reductions into hist[bin][lane] (bank = lane).  Lanes beyond the last feature see the
-        // zero padding byte and accumulate into a column that is never flushed.
-        auto consume = [&](unsigned bin, const int2& v) {
-          const unsigned addr = hg_lane + bin * (kGroup * 4);
+      auto consume = [&](const int4& w, const int2& v) {
+        unsigned x[4];
+        x[0] = (wsel & 1) ? w.y : w.x;
+        x[1] = (wsel & 1) ? w.x : w.y;
+        x[2] = (wsel & 1) ? w.w : w.z;
+        x[3] = (wsel & 1) ? w.z : w.w;
+        if (wsel & 2) {
+          unsigned t = x[0]; x[0] = x[2]; x[2] = t;
+          t = x[1]; x[1] = x[3]; x[3] = t;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = __byte_perm(x[i], 0u, perm);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const unsigned bin  = __byte_perm(x[j >> 2], 0u, 0x4440u | (j & 3));
+          const unsigned addr = (bin * (kGroup * 4) + lanebase) ^ (4u * j);
           if (kFloat) {
             RedShared(addr, __int_as_float(v.x));
             RedShared(addr + hh_off, __int_as_float(v.y));
@@ -403,30 +398,20 @@ __global__ void __launch_bounds__(kHistThreads, 2)
             RedShared(addr, v.x);
             RedShared(addr + hh_off, v.y);
           }
-        };
-        if (n == 32) {
-#pragma unroll
-          for (int r0 = 0; r0 < 32; r0 += 8) {
-            unsigned bin[8];
-            int4 v[4];  // one broadcast 16-byte load brings the pairs of two rows
-#pragma unroll
-            for (int i = 0; i < 8; ++i) bin[i] = LdsU8(bins_s + (r0 + i) * kGroup + lane);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) v[i] = LdsV4(gp_s + (r0 + 2 * i) * 8);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              consume(bin[2 * i], make_int2(v[i].x, v[i].y));
-              consume(bin[2 * i + 1], make_int2(v[i].z, v[i].w));
-            }
-          }
-        } else {
-          for (int r = 0; r < n; ++r) consume(LdsU8(bins_s + r * kGroup + lane), LdsV2(gp_s + r * 8));
         }
-        __syncwarp();
-        gp_cur = gp_next;
-        buf ^= 1;
+      };
+      int4 w0, w1, w2;
+      int2 v0, v1, v2;
+      load_row(load_rid(warp), w0, v0);
+      load_row(load_rid(warp + kHistWarps), w1, v1);
+      int rid_next = load_rid(warp + 2 * kHistWarps);
+      for (int b = warp; b < nb; b += kHistWarps) {
+        load_row(rid_next, w2, v2);  // batch b + 2 * kHistWarps
+        rid_next = load_rid(b + 3 * kHistWarps);
+        consume(w0, v0);
+        w0 = w1; v0 = v1;
+        w1 = w2; v1 = v2;
       }
-      CpAsyncWait<0>();
     }
     __syncthreads();
     flush(use_atomics);
@@ -435,6 +420,30 @@ __global__ void __launch_bounds__(kHistThreads, 2)
 
 // ---- row grouping (utility for the stage-level API) -------------------------------------------
 constexpr int kGroupTile = 4096;
+
+// Kernel, dynamic shared memory and persistent grid (resident blocks of the whole device, from the
+// occupancy calculator) for one combination of bin width, pair type and path.
+struct HistLaunch {
+  void (*fn)(HistParams);
+  size_t smem;
+  int grid;
+};
+
+HistLaunch PickHistKernel(bool smem_path, int bin_bytes, bool float_mode, int sm_count)
+{
+  HistLaunch h;
+  h.smem = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * 8 + 128 : 0;
+  if (smem_path) h.fn = float_mode ? k_hist<uint8_t, true, true> : k_hist<uint8_t, false, true>;
+  else if (bin_bytes == 1) h.fn = float_mode ? k_hist<uint8_t, true, false> : k_hist<uint8_t, false, false>;
+  else h.fn = float_mode ? k_hist<uint16_t, true, false> : k_hist<uint16_t, false, false>;
+  if (h.smem > 48 * 1024)
+    LBK_CUDA(cudaFuncSetAttribute(h.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(h.smem)));
+  int per_sm = 0;
+  LBK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, h.fn, kHistThreads, h.smem));
+  if (per_sm < 1) per_sm = 1;
+  h.grid = sm_count * per_sm;
+  return h;
+}
 
 __global__ void k_group_count(const int32_t* __restrict__ node_of_row, int64_t n_rows, int node_begin, int n_nodes,
                               int32_t* __restrict__ counts /* [blocks][n_nodes] */)
@@ -541,11 +550,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
-  const size_t smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * 8 + kHistWarps * kWarpRingBytes : 0;
-  int blocks_per_sm    = smem_path ? static_cast<int>((ctx->max_smem_optin) / (smem + 1024)) : 4;
-  if (blocks_per_sm > 2048 / kHistThreads) blocks_per_sm = 2048 / kHistThreads;
-  if (blocks_per_sm < 1) blocks_per_sm = 1;
-  const int grid = ctx->sm_count * blocks_per_sm;
+  const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, ctx->sm_count);
 
   const int* max_abs = lv.max_abs;
   if (!lv.float_mode && max_abs == nullptr) {
@@ -561,26 +566,11 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   }
   double mult = 1.0;
   if (const char* e = getenv("LBK_HIST_TICKETS_PER_BLOCK")) mult = atof(e);
-  k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, p.G * p.K, static_cast<int>(grid * mult) + 1,
+  k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, p.G * p.K, static_cast<int>(hl.grid * mult) + 1,
                                       lv.float_mode ? nullptr : max_abs, chunk_off, plan, p.ticket);
   LBK_LAUNCH_CHECK();
-
-#define LBK_HIST_LAUNCH(BinT, FL, SM)                                                                              \
-  do {                                                                                                             \
-    if (smem > 48 * 1024)                                                                                          \
-      LBK_CUDA(cudaFuncSetAttribute(k_hist<BinT, FL, SM>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
-                                    static_cast<int>(smem)));                                                      \
-    k_hist<BinT, FL, SM><<<grid, kHistThreads, smem, stream>>>(p);                                                 \
-  } while (0)
   if (ctx->profile) LBK_CUDA(cudaEventRecord(ctx->ev_start, stream));
-  if (smem_path) {
-    if (lv.float_mode) LBK_HIST_LAUNCH(uint8_t, true, true); else LBK_HIST_LAUNCH(uint8_t, false, true);
-  } else if (lv.bin_bytes == 1) {
-    if (lv.float_mode) LBK_HIST_LAUNCH(uint8_t, true, false); else LBK_HIST_LAUNCH(uint8_t, false, false);
-  } else {
-    if (lv.float_mode) LBK_HIST_LAUNCH(uint16_t, true, false); else LBK_HIST_LAUNCH(uint16_t, false, false);
-  }
-#undef LBK_HIST_LAUNCH
+  hl.fn<<<hl.grid, kHistThreads, hl.smem, stream>>>(p);
   LBK_LAUNCH_CHECK();
   if (ctx->profile) {
     LBK_CUDA(cudaEventRecord(ctx->ev_stop, stream));
@@ -695,9 +685,8 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     for (int f = 0; f < F; ++f) mb = rp[f + 1] - rp[f] > mb ? rp[f + 1] - rp[f] : mb;
     LBK_EXPECT(a->bin_bytes == 2 || mb <= 256, "one-byte bins need <= 256 proposals per feature");
 
-    int sm_count = 0, max_smem_optin = 0;
+    int sm_count = 0;
     LBK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
-    LBK_CUDA(cudaDeviceGetAttribute(&max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
 
     const bool float_mode = a->mode == 1;
     HistParams p;
@@ -719,11 +708,7 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     p.out          = a->hist;
     const bool smem_path = a->bin_bytes == 1 && mb <= kSmemBins;
     p.mb                 = smem_path ? mb : 0;
-    const size_t smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * 8 + kHistWarps * kWarpRingBytes : 0;
-    int blocks_per_sm    = smem_path ? static_cast<int>(max_smem_optin / (smem + 1024)) : 4;
-    if (blocks_per_sm > 2048 / kHistThreads) blocks_per_sm = 2048 / kHistThreads;
-    if (blocks_per_sm < 1) blocks_per_sm = 1;
-    const int grid = sm_count * blocks_per_sm;
+    const HistLaunch hl  = PickHistKernel(smem_path, a->bin_bytes, float_mode, sm_count);
 
     // the array keeps what the previous call left: clear the words that accumulate
     LBK_CUDA(cudaMemsetAsync(plan, 0, sizeof(int32_t) * 8, stream));
@@ -735,24 +720,10 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
         LBK_LAUNCH_CHECK();
       }
     }
-    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, p.G * p.K, grid + 1, float_mode ? nullptr : max_abs,
+    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, p.G * p.K, hl.grid + 1, float_mode ? nullptr : max_abs,
                                         chunk_off, plan, p.ticket);
     LBK_LAUNCH_CHECK();
-#define LBK_HIST_LAUNCH(BinT, FL, SM)                                                                              \
-  do {                                                                                                             \
-    if (smem > 48 * 1024)                                                                                          \
-      LBK_CUDA(cudaFuncSetAttribute(k_hist<BinT, FL, SM>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
-                                    static_cast<int>(smem)));                                                      \
-    k_hist<BinT, FL, SM><<<grid, kHistThreads, smem, stream>>>(p);                                                 \
-  } while (0)
-    if (smem_path) {
-      if (float_mode) LBK_HIST_LAUNCH(uint8_t, true, true); else LBK_HIST_LAUNCH(uint8_t, false, true);
-    } else if (a->bin_bytes == 1) {
-      if (float_mode) LBK_HIST_LAUNCH(uint8_t, true, false); else LBK_HIST_LAUNCH(uint8_t, false, false);
-    } else {
-      if (float_mode) LBK_HIST_LAUNCH(uint16_t, true, false); else LBK_HIST_LAUNCH(uint16_t, false, false);
-    }
-#undef LBK_HIST_LAUNCH
+    hl.fn<<<hl.grid, kHistThreads, hl.smem, stream>>>(p);
     LBK_LAUNCH_CHECK();
     LBK_CUDA(cudaStreamSynchronize(stream));
   });
