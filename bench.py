@@ -96,7 +96,7 @@ class ClockSampler:
 
 
 def hist_inputs(torch, n_rows, seed, device):
-    """Synthetic level-7 inputs on the device: group-major uint8 bins, node-grouped row index,
+    """Synthetic level-7 inputs on the device: row-major uint8 bins, node-grouped row index,
     quantised pairs from the library's own quantiser (scale = INT32_MAX / sum|g|, as the tree
     builder uses), float32 pairs for the float path."""
     from legateboost_b200 import stages
@@ -104,7 +104,7 @@ def hist_inputs(torch, n_rows, seed, device):
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     G = HIST_FEATURES // 32
-    bins = torch.randint(0, HIST_BINS, (G, n_rows, 32), dtype=torch.uint8, device=device, generator=gen)
+    bins = torch.randint(0, HIST_BINS, (n_rows, G * 32), dtype=torch.uint8, device=device, generator=gen)
     row_ptr = (torch.arange(HIST_FEATURES + 1, dtype=torch.int32, device=device) * HIST_BINS)
     g = torch.randn((n_rows, 1), dtype=torch.float64, device=device, generator=gen)
     h = torch.ones((n_rows, 1), dtype=torch.float64, device=device)

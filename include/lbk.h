@@ -159,9 +159,11 @@ int lbk_split_proposals(lbk_context* ctx, const void* X, int x_dtype, int64_t ld
                         void* stream);
 
 /* Bin ids (reference: SparseSplitProposals::FindBin, build_tree.h:178-185, evaluated once per
- * tree instead of once per level).  bins layout: feature groups of 32, group-major:
- *   bins[(f/32)*n_rows*32 + row*32 + f%32] = index of the first proposal >= x inside feature f.
- * bin_bytes = 1 (every feature has <= 256 proposals) or 2. */
+ * tree instead of once per level).  bins layout: row-major, every row padded with zeros to a
+ * whole number of 32-feature groups (pitch = 32 * ceil(n_features / 32) elements):
+ *   bins[row*pitch + f] = index of the first proposal >= x inside feature f.
+ * With one-byte bins the 32 ids of a (row, group) are one 32-byte sector and a row of up to 128
+ * features is one 128-byte line.  bin_bytes = 1 (every feature has <= 256 proposals) or 2. */
 int lbk_bin_matrix(lbk_context* ctx, const void* X, int x_dtype, int64_t ldx, int64_t n_rows,
                    int n_features, const void* proposals, const int32_t* row_ptr, void* bins,
                    int bin_bytes, void* stream);

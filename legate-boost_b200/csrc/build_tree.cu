@@ -223,6 +223,7 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
       PartitionLevel pl;
       pl.bins          = bins;
       pl.bin_bytes     = bin_bytes;
+      pl.bin_pitch     = static_cast<int64_t>((F + kGroup - 1) / kGroup) * kGroup;
       pl.n_rows        = N;
       pl.row_index_in  = rows_a;
       pl.seg_in        = seg_a;

@@ -61,8 +61,10 @@ struct HistParams {
   const int32_t* slot_of_node;  // may be null = identity
   int n_nodes;
   const int32_t* chunk_off;  // [n_nodes+1]
-  const int32_t* plan;       // [0] rows per chunk, [1] total chunks, [3] rows between flushes
+  const int32_t* part_off;   // [n_nodes+1] partial-sum slots before each node (nodes with > 1 chunk); may be null
+  const int32_t* plan;       // [0] rows per chunk, [1] total chunks, [3] rows between flushes, [6] slots usable
   unsigned int* ticket;
+  void* partial;             // partial-sum slots: [slot][2][mb * 32] of the accumulator type; may be null
   void* out;
 };
 
@@ -130,82 +132,166 @@ __global__ void k_max_abs(const int2* __restrict__ gpair, int64_t n, int* __rest
   }
 }
 
-// Single block: rows per chunk for this level and the chunk offsets of every built node.
+// Single block: how the rows of every built node are cut into chunks on this level.
+//
+// A ticket is (node chunk, feature group, output).  Resident blocks draw tickets from a counter, so
+// the level takes about ceil(tickets / resident) rounds of the largest ticket, or (list scheduling)
+// total work / resident + the largest ticket, whichever is smaller.  The planner evaluates that
+// bound for "one chunk per node" and for a geometric ladder of chunk sizes, with a per-ticket
+// overhead (clear, flush, partial sums) expressed in rows, and keeps the cheapest.  Chunks of a node
+// are equal in size.  A node with several chunks needs one partial-sum slot per chunk and (feature
+// group, output); candidates that need more slots than `slot_capacity` are not considered, and
+// plan[6] says whether the chosen cut can use the slots (1) or has to flush with atomics (0).
+constexpr int kPlanCandidates = 64;
+constexpr int kOverheadSingle = 2000;  // rows a block could have processed while it clears and flushes with stores
+constexpr int kOverheadMulti  = 5000;  // the same for clear + partial store + its share of the final sum (measured)
+
 __global__ void __launch_bounds__(1024)
   k_hist_plan(const int32_t* __restrict__ seg, const int32_t* __restrict__ slot_of_node, int n_nodes, int GK,
-              int target_tickets, const int* __restrict__ max_abs, int32_t* __restrict__ chunk_off,
-              int32_t* __restrict__ plan, unsigned int* __restrict__ ticket)
+              int resident, const int* __restrict__ max_abs, long long slot_capacity, int force, int32_t* __restrict__ chunk_off,
+              int32_t* __restrict__ part_off, int32_t* __restrict__ plan, unsigned int* __restrict__ ticket)
 {
   __shared__ long long red[32];
-  __shared__ int wsum[32];
-  __shared__ int carry;
-  __shared__ int ch_s;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // rows to process, with the number of non-empty built nodes in the top 20 bits
-  long long rows = 0;
-  for (int j = tid; j < n_nodes; j += blockDim.x) {
+  __shared__ int red_max[32];
+  __shared__ long long wsum[32];
+  __shared__ long long carry;
+  __shared__ long long total_s;
+  __shared__ int ch_s, cap_s, mode_s;
+  __shared__ double cand_cost[kPlanCandidates];
+  __shared__ int cand_ch[kPlanCandidates];
+  __shared__ int cand_fit[kPlanCandidates];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+  auto rows_of = [&](int j) -> int {
     const bool built = slot_of_node == nullptr || slot_of_node[j] >= 0;
     const int r      = seg[j + 1] - seg[j];
-    if (built && r > 0) rows += r + (1ll << 40);
-  }
+    return built ? r : 0;
+  };
+  long long rows = 0;
+  for (int j = tid; j < n_nodes; j += blockDim.x) rows += rows_of(j);
   for (int off = 16; off >= 1; off >>= 1) rows += __shfl_down_sync(0xffffffffu, rows, off);
   if (lane == 0) red[warp] = rows;
   __syncthreads();
   if (tid == 0) {
     long long total = 0;
-    for (int w = 0; w < (blockDim.x >> 5); ++w) total += red[w];
-    const long long nodes = total >> 40;
-    total &= (1ll << 40) - 1;
-    long long ch = (total * GK + target_tickets - 1) / target_tickets;
-    // enough nodes to fill the machine: one chunk per node, so that every node is flushed
-    // once, with plain stores
-    if (nodes * GK >= target_tickets) ch = 1ll << 30;
-    if (ch < kMinChunk) ch = kMinChunk;
-    ch = (ch + kTileRows - 1) / kTileRows * kTileRows;
-    if (ch > (1ll << 30)) ch = 1ll << 30;
-    ch_s  = static_cast<int>(ch);
+    for (int w = 0; w < n_warps; ++w) total += red[w];
+    total_s = total;
+    int m   = 1;
+    if (max_abs) m = max(1, max(max_abs[0], max_abs[1]));
+    const int safe = max_abs ? 2147483647 / m : 2147483647;
+    plan[3]        = safe;
+    // chunks that can use partial-sum slots never need a flush in the middle
+    cap_s = safe >= (1 << 30) ? (1 << 30) : (safe & ~(kTileRows - 1));
     carry = 0;
     chunk_off[0] = 0;
+    if (part_off) part_off[0] = 0;
+  }
+  __syncthreads();
+  const long long total = total_s;
+  const int cap         = cap_s;
+
+  // candidate 0: one chunk per node; candidate c > 0: total work / (resident * 2^(c / 16)) rows
+  for (int c = warp; c < kPlanCandidates; c += n_warps) {
+    long long ch = 1ll << 30;
+    if (c > 0) {
+      const double f = exp2(static_cast<double>(c - 1) / 16.0);
+      ch             = static_cast<long long>(static_cast<double>(total) * GK / (static_cast<double>(resident) * f)) + 1;
+      if (ch < kMinChunk) ch = kMinChunk;
+      ch = (ch + kTileRows - 1) / kTileRows * kTileRows;
+      if (ch > (1ll << 30)) ch = 1ll << 30;
+    }
+    const long long chs = cap >= kTileRows && ch > cap ? cap : ch;  // with slots: never beyond the safe count
+    long long tickets = 0, multi = 0, cost = 0;
+    int biggest = 0;
+    for (int j = lane; j < n_nodes; j += 32) {
+      const int r = rows_of(j);
+      if (r <= 0) continue;
+      const int nch  = static_cast<int>((r + chs - 1) / chs);
+      const int size = (r + nch - 1) / nch + (nch > 1 ? kOverheadMulti : kOverheadSingle);
+      tickets += nch;
+      if (nch > 1) multi += nch;
+      cost += static_cast<long long>(size) * nch;
+      biggest = max(biggest, size);
+    }
+    for (int off = 16; off >= 1; off >>= 1) {
+      tickets += __shfl_down_sync(0xffffffffu, tickets, off);
+      multi += __shfl_down_sync(0xffffffffu, multi, off);
+      cost += __shfl_down_sync(0xffffffffu, cost, off);
+      biggest = max(biggest, __shfl_down_sync(0xffffffffu, biggest, off));
+    }
+    if (lane == 0) {
+      const double T      = static_cast<double>(tickets) * GK;
+      const double rounds = ceil(T / resident) * biggest;
+      const double list   = static_cast<double>(cost) * GK / resident + biggest;
+      cand_cost[c]        = rounds < list ? rounds : list;
+      cand_ch[c]          = static_cast<int>(chs);
+      cand_fit[c]         = multi * GK <= slot_capacity;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int best = -1;
+    for (int c = 0; c < kPlanCandidates; ++c)
+      if (slot_capacity > 0 && cap >= kTileRows && cand_fit[c] && (best < 0 || cand_cost[c] < cand_cost[best] * 0.98)) best = c;
+    if (force >= 0 && force < kPlanCandidates && slot_capacity > 0 && cap >= kTileRows && cand_fit[force]) best = force;
+    plan[7] = best;
+    if (best >= 0) {
+      ch_s   = cand_ch[best];
+      mode_s = 1;
+    } else {
+      // no slots (or too few even for one chunk per node): the cut of the first candidates that
+      // gives every resident block about one ticket, flushed with atomics
+      long long ch = (total * GK + resident - 1) / resident;
+      long long nodes = 0;
+      for (int j = 0; j < n_nodes; ++j) nodes += rows_of(j) > 0;
+      if (nodes * GK >= resident) ch = 1ll << 30;
+      if (ch < kMinChunk) ch = kMinChunk;
+      ch = (ch + kTileRows - 1) / kTileRows * kTileRows;
+      if (ch > (1ll << 30)) ch = 1ll << 30;
+      ch_s   = static_cast<int>(ch);
+      mode_s = 0;
+    }
   }
   __syncthreads();
   const int ch = ch_s;
+  // exclusive scans over the nodes: chunks (low word) and partial-sum slots (high word)
   for (int base = 0; base < n_nodes; base += blockDim.x) {
     const int j = base + tid;
-    int c       = 0;
+    long long c = 0;
     if (j < n_nodes) {
-      const bool built = slot_of_node == nullptr || slot_of_node[j] >= 0;
-      const int r      = seg[j + 1] - seg[j];
-      c                = (built && r > 0) ? (r + ch - 1) / ch : 0;
+      const int r   = rows_of(j);
+      const int nch = r > 0 ? (r + ch - 1) / ch : 0;
+      c             = nch + (nch > 1 ? (static_cast<long long>(nch) << 32) : 0);
     }
-    int incl = c;
+    long long incl = c;
     for (int off = 1; off < 32; off <<= 1) {
-      int n = __shfl_up_sync(0xffffffffu, incl, off);
+      const long long n = __shfl_up_sync(0xffffffffu, incl, off);
       if (lane >= off) incl += n;
     }
     if (lane == 31) wsum[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-      int w  = lane < (blockDim.x >> 5) ? wsum[lane] : 0;
-      int wi = w;
+      const long long w = lane < n_warps ? wsum[lane] : 0;
+      long long wi      = w;
       for (int off = 1; off < 32; off <<= 1) {
-        int n = __shfl_up_sync(0xffffffffu, wi, off);
+        const long long n = __shfl_up_sync(0xffffffffu, wi, off);
         if (lane >= off) wi += n;
       }
       wsum[lane] = wi - w;
     }
     __syncthreads();
-    const int before = carry + wsum[warp];
-    if (j < n_nodes) chunk_off[j + 1] = before + incl;
+    const long long before = carry + wsum[warp];
+    if (j < n_nodes) {
+      chunk_off[j + 1] = static_cast<int>((before + incl) & 0xffffffffll);
+      if (part_off) part_off[j + 1] = static_cast<int>((before + incl) >> 32);
+    }
     __syncthreads();
     if (tid == blockDim.x - 1) carry = before + incl;
     __syncthreads();
   }
   if (tid == 0) {
     plan[0] = ch;
-    plan[1] = carry;
-    int m   = 1;
-    if (max_abs) m = max(1, max(max_abs[0], max_abs[1]));
-    plan[3] = max_abs ? 2147483647 / m : 2147483647;
+    plan[1] = static_cast<int>(carry & 0xffffffffll);
+    plan[6] = mode_s;
     *ticket = 0;
   }
 }
@@ -227,6 +313,12 @@ struct Acc<false> {
     *reinterpret_cast<longlong2*>(dst) = make_longlong2(g, h);
   }
   __device__ static bool nonzero(int g, int h) { return (g | h) != 0; }
+  using wide_t = long long;
+  __device__ static long long widen(int bits) { return bits; }
+  __device__ static void store_wide(out_t* dst, long long g, long long h)
+  {
+    *reinterpret_cast<longlong2*>(dst) = make_longlong2(g, h);
+  }
 };
 template <>
 struct Acc<true> {
@@ -243,32 +335,134 @@ struct Acc<true> {
     *reinterpret_cast<double2*>(dst) = make_double2(g, h);
   }
   __device__ static bool nonzero(float g, float h) { return g != 0.f || h != 0.f; }
+  using wide_t = double;
+  __device__ static double widen(int bits) { return static_cast<double>(__int_as_float(bits)); }
+  __device__ static void store_wide(out_t* dst, double g, double h)
+  {
+    *reinterpret_cast<double2*>(dst) = make_double2(g, h);
+  }
 };
 
-template <typename BinT, bool kFloat, bool kSmem>
-__global__ void __launch_bounds__(kHistThreads, 2)
-  k_hist(const HistParams p)
+// What a chunk index means: the node, the chunk's place in it, the rows.
+struct Chunk {
+  int j, ci, nchunks, slot, rb, re;
+};
+
+__device__ inline Chunk DecodeChunk(const HistParams& p, int c)
+{
+  // node that owns chunk c: last j with chunk_off[j] <= c
+  int lo = 0, hi = p.n_nodes;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.chunk_off[mid] <= c) lo = mid; else hi = mid;
+  }
+  Chunk ch;
+  ch.j       = lo;
+  ch.nchunks = p.chunk_off[lo + 1] - p.chunk_off[lo];
+  ch.slot    = p.slot_of_node ? p.slot_of_node[lo] : lo;
+  ch.ci      = c - p.chunk_off[lo];
+  // the chunks of a node are equal in size (a multiple of 32 rows, the last one takes the rest)
+  const int nrows = p.seg[lo + 1] - p.seg[lo];
+  const int size  = ch.nchunks > 1 ? ((nrows + ch.nchunks - 1) / ch.nchunks + kTileRows - 1) / kTileRows * kTileRows : nrows;
+  ch.rb = min(p.seg[lo + 1], p.seg[lo] + ch.ci * size);
+  ch.re = min(p.seg[lo + 1], ch.rb + size);
+  return ch;
+}
+
+// Rows [b, e) of one node, features [f0, f0 + 32 * groups): one lane per feature, the warps of the
+// block stride over the rows, every update is a pair of 64-bit global atomics.
+template <typename BinT, typename A>
+__device__ inline void DirectRows(const HistParams& p, int b, int e, int f0, int groups, int k,
+                                  typename A::out_t* onode, int warp, int n_warps, int lane)
+{
+  using in_t          = typename A::in_t;
+  const BinT* bins    = static_cast<const BinT*>(p.bins);
+  const in_t* gpair   = static_cast<const in_t*>(p.gpair);
+  const int64_t pitch = static_cast<int64_t>(p.G) * kGroup;
+  for (int u = 0; u < groups; ++u) {
+    const int feat = f0 + u * kGroup + lane;
+    if (feat >= p.F) continue;
+    typename A::out_t* obase = onode + p.row_ptr[feat];
+    for (int r = b + warp; r < e; r += n_warps) {
+      const int ridx = p.row_index[r];
+      const in_t v   = gpair[static_cast<int64_t>(ridx) * p.K + k];
+      const int bin  = bins[static_cast<int64_t>(ridx) * pitch + feat];
+      A::add_global(obase + bin, v.x, v.y);
+    }
+  }
+}
+
+// Bins of two bytes, or more than 256 bins in a feature: every ticket goes straight to global atomics.
+template <typename BinT, bool kFloat>
+__global__ void __launch_bounds__(kHistThreads)
+  k_hist_direct(const HistParams p)
+{
+  using A = Acc<kFloat>;
+  __shared__ unsigned int s_ticket;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const long long total = static_cast<long long>(p.plan[1]) * p.G * p.K;
+  while (true) {
+    __syncthreads();
+    if (tid == 0) s_ticket = atomicAdd(p.ticket, 1u);
+    __syncthreads();
+    const long long t = s_ticket;
+    if (t >= total) break;
+    const int k    = static_cast<int>(t % p.K);
+    const int g    = static_cast<int>((t / p.K) % p.G);
+    const Chunk ch = DecodeChunk(p, static_cast<int>(t / (static_cast<long long>(p.K) * p.G)));
+    typename A::out_t* onode = static_cast<typename A::out_t*>(p.out) + (static_cast<int64_t>(ch.slot) * p.K + k) * p.B;
+    DirectRows<BinT, A>(p, ch.rb, ch.re, g * kGroup, 1, k, onode, warp, kHistWarps, lane);
+  }
+}
+
+// One-byte bins, at most 256 per feature: private histograms in shared memory.
+//
+// W = 1: a ticket covers one 32-feature group, 512 threads, two blocks per SM.
+// W = 2: a ticket covers two neighbouring groups (64 features), 1024 threads, one block per SM.
+// The wide form exists because the load/store pipe of the SM spends one pass per distinct
+// 128-byte line a gather touches, however few bytes it takes from it: with 64 bin bytes per row
+// the row gather costs half as many passes per update, and the row ids and gradient pairs are
+// fetched once for two groups.
+//
+// Every warp runs its own pipeline over batches of 32 / (2 W) rows (no block barrier inside, no
+// staging in shared memory).  2 W lanes own one row of the batch and load its bin bytes straight
+// from global memory into registers, 16 bytes per lane.  In step j of 16 the lanes of row slot r
+// handle byte (j xor r) of their 16, and the histogram words of a bin are laid out so that the 32
+// lanes of a warp always update 32 different banks, whatever the bins:
+//   W = 1 (r < 16, quarter q < 2):  word = 16 q + byte                   (bank = word)
+//   W = 2 (r < 8,  quarter q < 4):  word = 32 (byte / 8) + 8 q + byte % 8 (bank = 8 q + byte % 8)
+// The bytes are permuted once per batch (a word swap and one byte permute per word) so that step
+// j reads the static byte j.  Per 32 updates that leaves the two reductions on the pipe.
+template <bool kFloat, int W>
+__global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
+  k_hist_smem(const HistParams p)
 {
   using A      = Acc<kFloat>;
   using smem_t = typename A::smem_t;
   using in_t   = typename A::in_t;
   using out_t  = typename A::out_t;
+  constexpr int kThreads      = kHistThreads * W;
+  constexpr int kWarps        = kThreads / 32;
+  constexpr int kCols         = kGroup * W;   // histogram words per bin
+  constexpr int kLanesPerRow  = 2 * W;
+  constexpr int kRowsPerBatch = 32 / kLanesPerRow;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  // the column arithmetic of the main loop needs the histogram on a 128-byte boundary
-  smem_t* hg = reinterpret_cast<smem_t*>(smem_raw + ((128u - (SmemAddr(smem_raw) & 127u)) & 127u));
-  constexpr int hist_rows = kSmem ? kSmemBins : 0;  // every byte value is a valid row
-  smem_t* hh           = hg + hist_rows * kGroup;
+  // the column arithmetic of the main loop needs the histogram on a 256-byte boundary
+  smem_t* hg = reinterpret_cast<smem_t*>(smem_raw + ((256u - (SmemAddr(smem_raw) & 255u)) & 255u));
+  smem_t* hh = hg + kSmemBins * kCols;  // every byte value is a valid bin row
   __shared__ unsigned int s_ticket;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int CH           = p.plan[0];
   const int total_chunks = p.plan[1];
   const int rows_safe    = p.plan[3];
-  const long long total  = static_cast<long long>(total_chunks) * p.G * p.K;
-  const BinT* bins       = static_cast<const BinT*>(p.bins);
+  const bool use_slots   = p.plan[6] != 0 && p.partial != nullptr;
+  const int GP           = (p.G + W - 1) / W;  // tickets per chunk and output
+  const long long total  = static_cast<long long>(total_chunks) * GP * p.K;
   const in_t* gpair      = static_cast<const in_t*>(p.gpair);
-  out_t* out             = static_cast<out_t*>(p.out);
-  const int hist_words   = p.mb * kGroup;
+  const int hist_words   = p.mb * kCols;
+  const int64_t pitch    = static_cast<int64_t>(p.G) * kGroup;  // bins are row-major, rows padded to whole groups
+  // feature (relative to the ticket's first) of histogram word w
+  auto feature_of_word = [](int w) -> int { return W == 1 ? w : 16 * ((w >> 3) & 3) + 8 * (w >> 5) + (w & 7); };
 
   while (true) {
     __syncthreads();
@@ -276,48 +470,32 @@ __global__ void __launch_bounds__(kHistThreads, 2)
     __syncthreads();
     const long long t = s_ticket;
     if (t >= total) break;
-    const int k = static_cast<int>(t % p.K);
-    const int g = static_cast<int>((t / p.K) % p.G);
-    const int c = static_cast<int>(t / (static_cast<long long>(p.K) * p.G));
-    // node that owns chunk c: last j with chunk_off[j] <= c
-    int lo = 0, hi = p.n_nodes;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (p.chunk_off[mid] <= c) lo = mid; else hi = mid;
-    }
-    const int j       = lo;
-    const int nchunks = p.chunk_off[j + 1] - p.chunk_off[j];
-    const int slot    = p.slot_of_node ? p.slot_of_node[j] : j;
-    const int rb      = p.seg[j] + (c - p.chunk_off[j]) * CH;
-    const int re      = min(p.seg[j + 1], rb + CH);
-    const int feat    = g * kGroup + lane;
-    const bool active = feat < p.F;
-    const int fbeg    = active ? p.row_ptr[feat] : 0;
-    const int fbins   = active ? p.row_ptr[feat + 1] - fbeg : 0;
-    out_t* obase      = out + (static_cast<int64_t>(slot) * p.K + k) * p.B + fbeg;
-    const BinT* gbins = bins + static_cast<int64_t>(g) * p.n_rows * kGroup;
+    const int k    = static_cast<int>(t % p.K);
+    const int gp   = static_cast<int>((t / p.K) % GP);
+    const Chunk ch = DecodeChunk(p, static_cast<int>(t / (static_cast<long long>(p.K) * GP)));
+    const int g0   = gp * W;
+    const int groups = min(W, p.G - g0);
+    out_t* onode   = static_cast<out_t*>(p.out) + (static_cast<int64_t>(ch.slot) * p.K + k) * p.B;
 
-    auto direct_rows = [&](int b, int e) {
-      for (int r = b + warp; r < e; r += kHistWarps) {
-        const int ridx = p.row_index[r];
-        const in_t v   = gpair[static_cast<int64_t>(ridx) * p.K + k];
-        if (active) {
-          const int bin = gbins[static_cast<int64_t>(ridx) * kGroup + lane];
-          A::add_global(obase + bin, v.x, v.y);
-        }
-      }
-    };
-
-    if (!kSmem || re - rb <= kDirectRows || rows_safe < kTileRows) {
-      direct_rows(rb, re);
+    // a chunk that will leave partial sums in a slot cannot take the direct path: the last
+    // chunk of its node stores the total and would overwrite what the atomics added
+    const bool slots = use_slots && ch.nchunks > 1 && rows_safe >= kTileRows;
+    if (rows_safe < kTileRows || (ch.re - ch.rb <= kDirectRows && !slots)) {
+      DirectRows<uint8_t, A>(p, ch.rb, ch.re, g0 * kGroup, groups, k, onode, warp, kWarps, lane);
       continue;
     }
 
-    bool use_atomics = nchunks > 1;
+    // the word a thread meets in the strided loops below is always the same one
+    const int my_word  = tid % kCols;
+    const int my_feat  = g0 * kGroup + feature_of_word(my_word);
+    const int my_fbeg  = my_feat < p.F ? p.row_ptr[my_feat] : 0;
+    const int my_fbins = my_feat < p.F ? p.row_ptr[my_feat + 1] - my_fbeg : 0;
+    bool use_atomics   = ch.nchunks > 1 && !slots;
     auto flush = [&](bool atomics) {
-      for (int e = tid; e < hist_words; e += kHistThreads) {  // e & 31 == lane for every e of a thread
-        const int bin = e >> 5;
-        if (bin < fbins) {
+      out_t* obase = onode + my_fbeg;
+      for (int e = tid; e < hist_words; e += kThreads) {  // e % kCols == my_word for every e of a thread
+        const int bin = e / kCols;
+        if (bin < my_fbins) {
           const smem_t vg = hg[e], vh = hh[e];
           if (A::nonzero(vg, vh)) {
             if (atomics) A::add_global(obase + bin, vg, vh); else A::store_global(obase + bin, vg, vh);
@@ -326,7 +504,7 @@ __global__ void __launch_bounds__(kHistThreads, 2)
       }
     };
     auto zero = [&]() {
-      for (int e = tid; e < hist_words; e += kHistThreads) {
+      for (int e = tid; e < hist_words; e += kThreads) {
         hg[e] = smem_t(0);
         hh[e] = smem_t(0);
       }
@@ -334,25 +512,17 @@ __global__ void __launch_bounds__(kHistThreads, 2)
     zero();
     __syncthreads();
 
-    // Every warp runs its own pipeline over 16-row batches of the chunk (no block barrier inside,
-    // no staging in shared memory).  A lane PAIR owns one row of the batch: the even lane loads the
-    // first 16 bin bytes of the row's 32, the odd lane the other 16, straight from global memory
-    // into registers (one 16-byte load per lane, 16 rows = 16 full sectors per instruction).  In
-    // step j of 16 the pair with row slot s handles feature (j xor s) of its half, so that the 32
-    // lanes of a warp always update 32 different columns = 32 different banks, whatever the bins.
-    // The bytes are permuted once per batch (word swaps + one byte permute per word) so that step
-    // j reads the static byte j.  Per 32 updates that leaves the two reductions and nothing else on
-    // the load/store pipe.
-    const unsigned slot16   = lane >> 1, half = lane & 1;
-    const unsigned wsel     = slot16 >> 2, bsel = slot16 & 3;
+    const unsigned rslot    = lane / kLanesPerRow, q = lane % kLanesPerRow;
+    const bool lane_on      = static_cast<int>(q >> 1) < groups;  // the group this lane's 16 bytes belong to exists
+    const unsigned wsel     = rslot >> 2, bsel = rslot & 3;
     const unsigned perm     = bsel == 0 ? 0x3210u : bsel == 1 ? 0x2301u : bsel == 2 ? 0x1032u : 0x0123u;
-    const unsigned lanebase = SmemAddr(hg) + half * 64 + slot16 * 4;  // hg is 128-byte aligned
-    const unsigned hh_off   = static_cast<unsigned>(hist_rows) * kGroup * 4;
-    const unsigned char* gb = reinterpret_cast<const unsigned char*>(gbins) + half * 16;
+    const unsigned lanebase = SmemAddr(hg) + (W == 1 ? 16 * q + rslot : 8 * q + rslot) * 4;
+    const unsigned hh_off   = static_cast<unsigned>(kSmemBins) * kCols * 4;
+    const unsigned char* gb = static_cast<const unsigned char*>(p.bins) + g0 * kGroup + q * 16;
     const int seg_rows = rows_safe >= (1 << 30) ? (1 << 30) : (rows_safe & ~31);
-    for (int sb = rb; sb < re; sb += seg_rows) {
-      const int se = min(re, sb + seg_rows);
-      if (sb > rb) {
+    for (int sb = ch.rb; sb < ch.re; sb += seg_rows) {
+      const int se = min(ch.re, sb + seg_rows);
+      if (sb > ch.rb) {
         __syncthreads();
         flush(true);
         use_atomics = true;
@@ -360,15 +530,15 @@ __global__ void __launch_bounds__(kHistThreads, 2)
         zero();
         __syncthreads();
       }
-      const int nb = (se - sb + kBatchRows - 1) / kBatchRows;
+      const int nb = (se - sb + kRowsPerBatch - 1) / kRowsPerBatch;
       auto load_rid = [&](int batch) -> int {
-        const int r = sb + batch * kBatchRows + static_cast<int>(slot16);
-        return (batch < nb && r < se) ? __ldcg(p.row_index + r) : -1;
+        const int r = sb + batch * kRowsPerBatch + static_cast<int>(rslot);
+        return (batch < nb && r < se && lane_on) ? __ldcg(p.row_index + r) : -1;
       };
       // rows beyond the end carry zero pairs and bin 0: they add nothing
       auto load_row = [&](int rid, int4& w, int2& v) {
         if (rid >= 0) {
-          w = __ldcs(reinterpret_cast<const int4*>(gb + static_cast<int64_t>(rid) * kGroup));
+          w = __ldcs(reinterpret_cast<const int4*>(gb + static_cast<int64_t>(rid) * pitch));
           v = __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid) * p.K + k));
         } else {
           w = make_int4(0, 0, 0, 0);
@@ -381,16 +551,17 @@ __global__ void __launch_bounds__(kHistThreads, 2)
         x[1] = (wsel & 1) ? w.x : w.y;
         x[2] = (wsel & 1) ? w.w : w.z;
         x[3] = (wsel & 1) ? w.z : w.w;
-        if (wsel & 2) {
-          unsigned t = x[0]; x[0] = x[2]; x[2] = t;
-          t = x[1]; x[1] = x[3]; x[3] = t;
+        if (W == 1 && (wsel & 2)) {
+          unsigned t2 = x[0]; x[0] = x[2]; x[2] = t2;
+          t2 = x[1]; x[1] = x[3]; x[3] = t2;
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) x[i] = __byte_perm(x[i], 0u, perm);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const unsigned bin  = __byte_perm(x[j >> 2], 0u, 0x4440u | (j & 3));
-          const unsigned addr = (bin * (kGroup * 4) + lanebase) ^ (4u * j);
+          const unsigned cj   = W == 1 ? 4u * j : (((j & 7u) << 2) | ((j >> 3) << 7));
+          const unsigned addr = (bin * (kCols * 4) + lanebase) ^ cj;
           if (kFloat) {
             RedShared(addr, __int_as_float(v.x));
             RedShared(addr + hh_off, __int_as_float(v.y));
@@ -400,21 +571,103 @@ __global__ void __launch_bounds__(kHistThreads, 2)
           }
         }
       };
+      // in flight per warp: the rows of the next two batches and the row ids of the two after
       int4 w0, w1, w2;
       int2 v0, v1, v2;
       load_row(load_rid(warp), w0, v0);
-      load_row(load_rid(warp + kHistWarps), w1, v1);
-      int rid_next = load_rid(warp + 2 * kHistWarps);
-      for (int b = warp; b < nb; b += kHistWarps) {
-        load_row(rid_next, w2, v2);  // batch b + 2 * kHistWarps
-        rid_next = load_rid(b + 3 * kHistWarps);
+      load_row(load_rid(warp + kWarps), w1, v1);
+      int rid_a = load_rid(warp + 2 * kWarps);
+      int rid_b = load_rid(warp + 3 * kWarps);
+      for (int b = warp; b < nb; b += kWarps) {
+        load_row(rid_a, w2, v2);  // batch b + 2 * kWarps
+        rid_a = rid_b;
+        rid_b = load_rid(b + 4 * kWarps);
         consume(w0, v0);
         w0 = w1; v0 = v1;
         w1 = w2; v1 = v2;
       }
     }
     __syncthreads();
-    flush(use_atomics);
+    if (!slots) {
+      flush(use_atomics);
+      continue;
+    }
+    // Several chunks of this node: every chunk leaves its sums in a slot; k_hist_sum adds the slots
+    // up afterwards and stores the total (no atomics on the histogram itself).
+    smem_t* part        = static_cast<smem_t*>(p.partial);
+    const size_t stride = static_cast<size_t>(hist_words) * 2;
+    const size_t first  = ((static_cast<size_t>(p.part_off[ch.j]) * p.K + k) * GP + gp);  // slot of chunk 0
+    const size_t step   = static_cast<size_t>(p.K) * GP;                                  // slot distance between chunks
+    smem_t* mine        = part + (first + ch.ci * step) * stride;
+    const int n4        = hist_words >> 2;  // 16-byte pieces: four neighbouring features of one bin
+    for (int e4 = tid; e4 < n4; e4 += kThreads) {
+      __stcg(reinterpret_cast<int4*>(mine) + e4, reinterpret_cast<const int4*>(hg)[e4]);
+      __stcg(reinterpret_cast<int4*>(mine + hist_words) + e4, reinterpret_cast<const int4*>(hh)[e4]);
+    }
+  }
+}
+
+// Adds up the partial-sum slots of every node that was cut into several chunks and stores the
+// totals.  grid = (nodes * tickets per chunk, kSumSplits); a block handles one (node, group set,
+// output) and 1/kSumSplits of its histogram words, a thread 16 bytes of every slot (four
+// neighbouring features of one bin), with four slots in flight.
+constexpr int kSumSplits  = 16;
+constexpr int kSumThreads = 256;
+
+template <bool kFloat, int W>
+__global__ void __launch_bounds__(kSumThreads)
+  k_hist_sum(const HistParams p)
+{
+  using A      = Acc<kFloat>;
+  using smem_t = typename A::smem_t;
+  using out_t  = typename A::out_t;
+  constexpr int kCols = kGroup * W;
+  if (p.plan[6] == 0) return;
+  const int GP = (p.G + W - 1) / W;
+  const int k  = blockIdx.x % p.K;
+  const int gp = (blockIdx.x / p.K) % GP;
+  const int j  = blockIdx.x / (p.K * GP);
+  const int nchunks = p.chunk_off[j + 1] - p.chunk_off[j];
+  if (nchunks <= 1) return;
+  const int slot       = p.slot_of_node ? p.slot_of_node[j] : j;
+  const int hist_words = p.mb * kCols;
+  const int n4         = hist_words >> 2;
+  const smem_t* part   = static_cast<const smem_t*>(p.partial);
+  const size_t stride  = static_cast<size_t>(hist_words) * 2;
+  const size_t first   = (static_cast<size_t>(p.part_off[j]) * p.K + k) * GP + gp;
+  const size_t step    = static_cast<size_t>(p.K) * GP;
+  out_t* onode         = static_cast<out_t*>(p.out) + (static_cast<int64_t>(slot) * p.K + k) * p.B;
+  for (int e4 = blockIdx.y * kSumThreads + threadIdx.x; e4 < n4; e4 += kSumSplits * kSumThreads) {
+    typename A::wide_t sg[4], sh[4];
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) sg[c4] = sh[c4] = 0;
+    for (int q0 = 0; q0 < nchunks; q0 += 4) {
+      int4 vg[4], vh[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (q0 + u < nchunks) {
+          const smem_t* src = part + (first + (q0 + u) * step) * stride;
+          vg[u] = __ldcg(reinterpret_cast<const int4*>(src) + e4);
+          vh[u] = __ldcg(reinterpret_cast<const int4*>(src + hist_words) + e4);
+        } else {
+          vg[u] = vh[u] = make_int4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        sg[0] += A::widen(vg[u].x); sg[1] += A::widen(vg[u].y); sg[2] += A::widen(vg[u].z); sg[3] += A::widen(vg[u].w);
+        sh[0] += A::widen(vh[u].x); sh[1] += A::widen(vh[u].y); sh[2] += A::widen(vh[u].z); sh[3] += A::widen(vh[u].w);
+      }
+    }
+    const int bin = (e4 * 4) / kCols, w0 = (e4 * 4) % kCols;
+    const int f0  = (gp * W) * kGroup + (W == 1 ? w0 : 16 * ((w0 >> 3) & 3) + 8 * (w0 >> 5) + (w0 & 7));
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const int f = f0 + c4;
+      if (f >= p.F) continue;
+      const int fbeg = p.row_ptr[f];
+      if (bin < p.row_ptr[f + 1] - fbeg && (sg[c4] != 0 || sh[c4] != 0)) A::store_wide(onode + fbeg + bin, sg[c4], sh[c4]);
+    }
   }
 }
 
@@ -425,22 +678,35 @@ constexpr int kGroupTile = 4096;
 // occupancy calculator) for one combination of bin width, pair type and path.
 struct HistLaunch {
   void (*fn)(HistParams);
+  void (*sum)(HistParams);  // adds up partial-sum slots; null for the kernels that have none
   size_t smem;
+  int threads;
   int grid;
+  int width;  // feature groups per ticket
 };
 
-HistLaunch PickHistKernel(bool smem_path, int bin_bytes, bool float_mode, int sm_count)
+HistLaunch PickHistKernel(bool smem_path, int bin_bytes, bool float_mode, int n_groups, int sm_count)
 {
   HistLaunch h;
-  h.smem = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * 8 + 128 : 0;
-  if (smem_path) h.fn = float_mode ? k_hist<uint8_t, true, true> : k_hist<uint8_t, false, true>;
-  else if (bin_bytes == 1) h.fn = float_mode ? k_hist<uint8_t, true, false> : k_hist<uint8_t, false, false>;
-  else h.fn = float_mode ? k_hist<uint16_t, true, false> : k_hist<uint16_t, false, false>;
+  h.width   = smem_path && n_groups >= 2 && getenv("LBK_HIST_NARROW") == nullptr ? 2 : 1;
+  h.threads = kHistThreads * h.width;
+  h.smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * h.width * 8 + 256 : 0;
+  h.sum = nullptr;
+  if (smem_path && h.width == 2) {
+    h.fn  = float_mode ? k_hist_smem<true, 2> : k_hist_smem<false, 2>;
+    h.sum = float_mode ? k_hist_sum<true, 2> : k_hist_sum<false, 2>;
+  } else if (smem_path) {
+    h.fn  = float_mode ? k_hist_smem<true, 1> : k_hist_smem<false, 1>;
+    h.sum = float_mode ? k_hist_sum<true, 1> : k_hist_sum<false, 1>;
+  }
+  else if (bin_bytes == 1) h.fn = float_mode ? k_hist_direct<uint8_t, true> : k_hist_direct<uint8_t, false>;
+  else h.fn = float_mode ? k_hist_direct<uint16_t, true> : k_hist_direct<uint16_t, false>;
   if (h.smem > 48 * 1024)
     LBK_CUDA(cudaFuncSetAttribute(h.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(h.smem)));
   int per_sm = 0;
-  LBK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, h.fn, kHistThreads, h.smem));
+  LBK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, h.fn, h.threads, h.smem));
   if (per_sm < 1) per_sm = 1;
+  if (!smem_path && per_sm > 4) per_sm = 4;
   h.grid = sm_count * per_sm;
   return h;
 }
@@ -542,7 +808,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   p.slot_of_node = lv.slot_of_node;
   p.n_nodes      = lv.n_nodes;
   int32_t* chunk_off = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes) + 1);
-  int32_t* plan      = s.alloc<int32_t>(4);
+  int32_t* plan      = s.alloc<int32_t>(8);
   p.chunk_off        = chunk_off;
   p.plan             = plan;
   p.ticket           = reinterpret_cast<unsigned int*>(plan + 2);
@@ -550,7 +816,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
-  const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, ctx->sm_count);
+  const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, p.G, ctx->sm_count);
 
   const int* max_abs = lv.max_abs;
   if (!lv.float_mode && max_abs == nullptr) {
@@ -564,17 +830,45 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
     }
     max_abs = m;
   }
-  double mult = 1.0;
-  if (const char* e = getenv("LBK_HIST_TICKETS_PER_BLOCK")) mult = atof(e);
-  k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, p.G * p.K, static_cast<int>(hl.grid * mult) + 1,
-                                      lv.float_mode ? nullptr : max_abs, chunk_off, plan, p.ticket);
+  const int tickets_per_chunk = (p.G + hl.width - 1) / hl.width * p.K;
+  // partial-sum slots for nodes that are cut into several chunks: ten per resident block
+  long long slot_capacity = 0;
+  p.part_off = nullptr;
+  p.partial  = nullptr;
+  int force = -1;
+  if (const char* e = getenv("LBK_HIST_FORCE")) force = atoi(e);
+  const bool want_slots = getenv("LBK_HIST_SLOTS") == nullptr || atoi(getenv("LBK_HIST_SLOTS")) != 0;
+  if (smem_path && want_slots) {
+    slot_capacity           = 10ll * hl.grid;
+    const size_t slot_bytes = static_cast<size_t>(p.mb) * kGroup * hl.width * 8;
+    int32_t* part_off       = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes) + 1);
+    p.part_off              = part_off;
+    p.partial               = s.alloc<unsigned char>(slot_bytes * slot_capacity);
+    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, tickets_per_chunk, hl.grid,
+                                        lv.float_mode ? nullptr : max_abs, slot_capacity, force, chunk_off, part_off, plan, p.ticket);
+  } else {
+    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, tickets_per_chunk, hl.grid,
+                                        lv.float_mode ? nullptr : max_abs, 0, -1, chunk_off, nullptr, plan, p.ticket);
+  }
   LBK_LAUNCH_CHECK();
   if (ctx->profile) LBK_CUDA(cudaEventRecord(ctx->ev_start, stream));
-  hl.fn<<<hl.grid, kHistThreads, hl.smem, stream>>>(p);
+  hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
   LBK_LAUNCH_CHECK();
+  if (p.partial) {
+    hl.sum<<<dim3(static_cast<unsigned>(lv.n_nodes) * tickets_per_chunk, kSumSplits), kSumThreads, 0, stream>>>(p);
+    LBK_LAUNCH_CHECK();
+  }
   if (ctx->profile) {
     LBK_CUDA(cudaEventRecord(ctx->ev_stop, stream));
     ctx->profile_recorded = true;
+  }
+  // stream ordered: the slots go back to the pool once the kernel has run
+  if (p.partial) s.free_one(p.partial);
+  if (getenv("LBK_HIST_DEBUG")) {
+    int hp[8];
+    LBK_CUDA(cudaMemcpyAsync(hp, plan, sizeof(hp), cudaMemcpyDeviceToHost, stream));
+    LBK_CUDA(cudaStreamSynchronize(stream));
+    fprintf(stderr, "hist plan: ch %d chunks %d safe %d mode %d cand %d grid %d\n", hp[0], hp[1], hp[3], hp[6], hp[7], hl.grid);
   }
 }
 
@@ -708,7 +1002,7 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     p.out          = a->hist;
     const bool smem_path = a->bin_bytes == 1 && mb <= kSmemBins;
     p.mb                 = smem_path ? mb : 0;
-    const HistLaunch hl  = PickHistKernel(smem_path, a->bin_bytes, float_mode, sm_count);
+    const HistLaunch hl  = PickHistKernel(smem_path, a->bin_bytes, float_mode, p.G, sm_count);
 
     // the array keeps what the previous call left: clear the words that accumulate
     LBK_CUDA(cudaMemsetAsync(plan, 0, sizeof(int32_t) * 8, stream));
@@ -720,11 +1014,28 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
         LBK_LAUNCH_CHECK();
       }
     }
-    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, p.G * p.K, hl.grid + 1, float_mode ? nullptr : max_abs,
-                                        chunk_off, plan, p.ticket);
+    // no partial-sum slots here (they would have to be allocated): nodes cut into chunks flush with atomics
+    p.part_off = nullptr;
+    p.partial  = nullptr;
+      k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, (p.G + hl.width - 1) / hl.width * p.K, hl.grid,
+                                        float_mode ? nullptr : max_abs, 0,
+                                        -1, chunk_off, nullptr, plan, p.ticket);
     LBK_LAUNCH_CHECK();
-    hl.fn<<<hl.grid, kHistThreads, hl.smem, stream>>>(p);
+    hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
     LBK_LAUNCH_CHECK();
     LBK_CUDA(cudaStreamSynchronize(stream));
   });
 }
+
+#ifdef LBK_HIST_TIMING
+extern "C" int lbk_debug_hist_timing(unsigned long long* out8, int reset)
+{
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out8, lbk::g_hist_timing, 64);
+  if (reset) {
+    unsigned long long z[8] = {};
+    cudaMemcpyToSymbol(lbk::g_hist_timing, z, 64);
+  }
+  return 0;
+}
+#endif

@@ -180,6 +180,7 @@ void WriteHessian(const GPairI64* node_sums, const QuantParams* qp, double* hess
 struct PartitionLevel {
   const void* bins;
   int bin_bytes;
+  int64_t bin_pitch;  // elements per row of bins (features rounded up to a multiple of kGroup)
   int64_t n_rows;
   const int32_t* row_index_in;
   const int32_t* seg_in;  // [n_nodes+1] for the level

@@ -94,7 +94,7 @@ __device__ inline int FindOwner(const int32_t* __restrict__ off, int n, int c)
 // i goes left.  Writes the masks and the chunk's left count.
 template <typename BinT>
 __global__ void __launch_bounds__(kPartThreads)
-  k_part_count(const BinT* __restrict__ bins, int64_t n_rows, const int32_t* __restrict__ row_index,
+  k_part_count(const BinT* __restrict__ bins, int64_t pitch, const int32_t* __restrict__ row_index,
                const int32_t* __restrict__ seg, const int32_t* __restrict__ chunk_off, int n_nodes, int node_begin,
                const int32_t* __restrict__ feature, const int32_t* __restrict__ split_bin,
                uint8_t* __restrict__ masks, int32_t* __restrict__ chunk_left)
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kPartThreads)
   const int sb   = split_bin[node];
   const int rb   = seg[j] + (c - chunk_off[j]) * kPartTile;
   const int re   = min(seg[j + 1], rb + kPartTile);
-  const BinT* col = bins + static_cast<int64_t>(f / kGroup) * n_rows * kGroup + (f % kGroup);
+  const BinT* col = bins + f;  // row-major bins, `pitch` elements per row
   const int tid  = threadIdx.x;
   const int r0   = rb + tid * kPartItems;
   unsigned mask  = 0;
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kPartThreads)
     const int r = r0 + i;
     if (r < re) {
       const int ridx = row_index[r];
-      const int bin  = col[static_cast<int64_t>(ridx) * kGroup];
+      const int bin  = col[static_cast<int64_t>(ridx) * pitch];
       if (bin <= sb) mask |= 1u << i;
     }
   }
@@ -233,11 +233,11 @@ void PartitionRows(lbk_context* ctx, Scratch& s, const PartitionLevel& pl, cudaS
   LBK_LAUNCH_CHECK();
   const unsigned grid = static_cast<unsigned>(max_chunks);
   if (pl.bin_bytes == 1) {
-    k_part_count<uint8_t><<<grid, kPartThreads, 0, stream>>>(static_cast<const uint8_t*>(pl.bins), pl.n_rows,
+    k_part_count<uint8_t><<<grid, kPartThreads, 0, stream>>>(static_cast<const uint8_t*>(pl.bins), pl.bin_pitch,
                                                               pl.row_index_in, pl.seg_in, chunk_off, n, pl.node_begin,
                                                               pl.feature, pl.split_bin, masks, chunk_left);
   } else {
-    k_part_count<uint16_t><<<grid, kPartThreads, 0, stream>>>(static_cast<const uint16_t*>(pl.bins), pl.n_rows,
+    k_part_count<uint16_t><<<grid, kPartThreads, 0, stream>>>(static_cast<const uint16_t*>(pl.bins), pl.bin_pitch,
                                                                pl.row_index_in, pl.seg_in, chunk_off, n, pl.node_begin,
                                                                pl.feature, pl.split_bin, masks, chunk_left);
   }

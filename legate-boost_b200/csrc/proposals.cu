@@ -212,7 +212,8 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
   for (int i = 0; i < 7; ++i) piv[i] = top3 ? sp[((i + 1) * (P >> 3) - 1) * kGroup + lane] : static_cast<T>(INFINITY);
   const unsigned half = (P >> 1) * kPitch, quarter = (P >> 2) * kPitch, eighth = (P >> 3) * kPitch;
-  BinT* out         = bins + static_cast<int64_t>(g) * n_rows * kGroup + lane;
+  const int64_t pitch = static_cast<int64_t>(gridDim.y) * kGroup;  // bins are row-major, rows padded to groups
+  BinT* out         = bins + f0 + lane;
   const T* xin      = X + f0 + lane;
   constexpr int U   = 8;  // rows per warp in flight
   const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
@@ -247,10 +248,10 @@ __global__ void __launch_bounds__(256)
       for (int u = 0; u < U; ++u)
         if (LdsT(probe + posb[u], T()) < x[u]) posb[u] += adv;
     }
-    BinT* orow = out + base * kGroup;
+    BinT* orow = out + base * pitch;
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      if (base + u < n_rows) orow[u * kGroup] = static_cast<BinT>(posb[u] / kPitch);
+      if (base + u < n_rows) orow[u * pitch] = static_cast<BinT>(posb[u] / kPitch);
   }
 }
 
@@ -271,7 +272,8 @@ __global__ void __launch_bounds__(256)
     n     = row_ptr[f + 1] - begin;
   }
   const T* p = proposals + begin;
-  BinT* out  = bins + static_cast<int64_t>(g) * n_rows * kGroup;
+  const int64_t pitch = static_cast<int64_t>(gridDim.y) * kGroup;
+  BinT* out  = bins + f0;
   const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   for (int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5); row < n_rows;
        row += warps_total) {
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(256)
       }
       bin = base + ((p[base] < x) ? 1 : 0);
     }
-    out[row * kGroup + lane] = static_cast<BinT>(bin);
+    out[row * pitch + lane] = static_cast<BinT>(bin);
   }
 }
 

@@ -26,12 +26,13 @@ def split_proposals(X, split_samples, seed, row_offset=0, dataset_rows=None, ctx
 
 
 def bin_matrix(X, proposals, row_ptr, bin_bytes=1, ctx=None):
-    """Bin ids in feature groups of 32, group-major: shape (G, N, 32) uint8 (or int16 storage)."""
+    """Bin ids, row-major with rows padded to whole 32-feature groups: shape (N, 32 * ceil(F / 32)),
+    uint8 (or int16 storage)."""
     ctx = ctx or L.context(X.device.index)
     N, F = X.shape
     G = (F + 31) // 32
     dt = torch.uint8 if bin_bytes == 1 else torch.int16
-    bins = torch.empty((G, N, 32), dtype=dt, device=X.device)
+    bins = torch.empty((N, G * 32), dtype=dt, device=X.device)
     with torch.cuda.device(X.device):
         ctx.check(ctx.lib.lbk_bin_matrix(
             ctx.handle, X.data_ptr(), _dtype_code(X), X.stride(0), N, F, proposals.data_ptr(),
@@ -39,14 +40,12 @@ def bin_matrix(X, proposals, row_ptr, bin_bytes=1, ctx=None):
     return bins
 
 
-def to_group_major(bins_row_major):
-    """(N, F) feature-relative bin ids -> the (G, N, 32) layout the kernels read."""
+def to_padded_rows(bins_row_major):
+    """(N, F) feature-relative bin ids -> the (N, 32 * ceil(F / 32)) zero-padded layout the kernels read."""
     N, F = bins_row_major.shape
     G = (F + 31) // 32
-    out = torch.zeros((G, N, 32), dtype=bins_row_major.dtype, device=bins_row_major.device)
-    for g in range(G):
-        w = min(32, F - g * 32)
-        out[g, :, :w] = bins_row_major[:, g * 32: g * 32 + w]
+    out = torch.zeros((N, G * 32), dtype=bins_row_major.dtype, device=bins_row_major.device)
+    out[:, :F] = bins_row_major
     return out
 
 
@@ -83,7 +82,7 @@ def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=Non
     ``host=True`` takes CPU tensors and lets the library do the copies (the end-to-end path)."""
     dev = bins.device
     ctx = ctx or L.context(None if host else dev.index)
-    G, N, _ = bins.shape
+    N = bins.shape[0]
     K = gpair.shape[1]
     n_nodes = seg.shape[0] - 1
     B = int(row_ptr[-1])

@@ -33,9 +33,11 @@ def tree_tuple(t):
     return (t.leaf_value, t.feature, t.split_value)
 
 
-def to_row_major(bins_g, F):
-    G, N, _ = bins_g.shape
-    return bins_g.permute(1, 0, 2).reshape(N, G * 32)[:, :F]
+def to_row_major(bins_p, F):
+    """Drops the padding columns of the kernels' layout (rows padded to whole 32-feature groups)."""
+    assert bins_p.shape[1] == (F + 31) // 32 * 32
+    assert not bins_p[:, F:].any()
+    return bins_p[:, :F]
 
 
 # ---------------------------------------------------------------------------------------------
@@ -115,7 +117,7 @@ def test_histogram_int_exact(lb, oracle, N, F, K, n_nodes, nb):
     for j in range(n_nodes):
         r = ri[sg[j]:sg[j + 1]]
         assert np.all(node[r] == j + n_nodes - 1) and np.all(np.diff(r) > 0)
-    got = stages.histogram(stages.to_group_major(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
+    got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
     assert np.array_equal(got.cpu().numpy(), want)
 
 
@@ -133,7 +135,7 @@ def test_histogram_int_no_wraparound(lb, oracle):
     q[:, 0, 0] += rs.randint(0, 1000, size=N).astype(np.int32)
     want = oracle.histogram_q(bins, row_ptr, q, node, 0, 1)
     row_index, seg = stages.group_rows(dev(node), 0, 1)
-    got = stages.histogram(stages.to_group_major(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
+    got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
     assert np.array_equal(got.cpu().numpy(), want)
 
 
@@ -146,7 +148,7 @@ def test_histogram_float_tolerance(lb, oracle, N, F, K, n_nodes):
     gh = np.stack([rs.normal(size=(N, K)), np.ones((N, K))], axis=2).astype(np.float32)
     want = oracle.histogram_d(bins, row_ptr, gh[:, :, 0].copy(), gh[:, :, 1].copy(), node, n_nodes - 1, 2 * n_nodes - 1)
     row_index, seg = stages.group_rows(dev(node), n_nodes - 1, n_nodes)
-    got = stages.histogram(stages.to_group_major(dev(bins)), dev(row_ptr), dev(gh), row_index, seg, F, mode=1)
+    got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), dev(gh), row_index, seg, F, mode=1)
     got = got.cpu().numpy()
     scale = np.abs(want).max()
     assert np.abs(got - want).max() <= 1e-5 * scale
@@ -161,7 +163,7 @@ def test_histogram_host_buffers(lb, oracle):
     q = rs.randint(-1000, 1000, size=(N, K, 2)).astype(np.int32)
     want = oracle.histogram_q(bins, row_ptr, q, node, n_nodes - 1, 2 * n_nodes - 1)
     row_index, seg = stages.group_rows(dev(node), n_nodes - 1, n_nodes)
-    bins_g = stages.to_group_major(dev(bins)).cpu().pin_memory()
+    bins_g = stages.to_padded_rows(dev(bins)).cpu().pin_memory()
     got = stages.histogram(bins_g, torch.from_numpy(row_ptr), torch.from_numpy(q).pin_memory(),
                            row_index.cpu(), seg.cpu(), F, mode=0, host=True)
     assert np.array_equal(got.numpy(), want)

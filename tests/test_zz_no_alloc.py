@@ -50,7 +50,7 @@ def test_noalloc_matches_regular_entry_point_twice():
         gpair = torch.from_numpy(q).cuda()
         node = torch.from_numpy(rs.randint(0, n_nodes, size=N).astype(np.int32) + n_nodes - 1).cuda()
         row_index, seg = stages.group_rows(node, n_nodes - 1, n_nodes)
-        bins_g = stages.to_group_major(bins)
+        bins_g = stages.to_padded_rows(bins)
         want = stages.histogram(bins_g, row_ptr, gpair, row_index, seg, F, mode=0)
         for call in range(2):
             got = torch.full_like(want, -7)  # garbage: the call must overwrite everything
