@@ -71,6 +71,8 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
   LBK_CUDA(cudaMemsetAsync(split_value, 0, sizeof(double) * M, stream));
   LBK_CUDA(cudaMemsetAsync(gain, 0, sizeof(double) * M, stream));
   LBK_CUDA(cudaMemsetAsync(tree.node_sums, 0, sizeof(GPairI64) * M * K, stream));
+  unsigned int* split_arrived = s.alloc<unsigned int>(M);  // see BestSplit
+  LBK_CUDA(cudaMemsetAsync(split_arrived, 0, sizeof(unsigned int) * M, stream));
 
   // split proposals -> B (one host synchronisation)
   T* proposals      = s.alloc<T>(static_cast<size_t>(F) * a.split_samples);
@@ -216,7 +218,7 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
         LBK_CUDA(cudaMemcpyAsync(a.trace_hist + static_cast<size_t>(nb) * node_elems * 2, level_hist,
                                  sizeof(GPairI64) * cnt * node_elems, cudaMemcpyDeviceToDevice, stream));
       }
-      BestSplit<T>(level_hist, nb, n_nodes, K, F, B, row_ptr, proposals, qp, sp, tree, stream);
+      BestSplit<T>(s, level_hist, nb, n_nodes, K, F, B, row_ptr, proposals, qp, sp, tree, split_arrived, ctx->sm_count, stream);
       s.free_one(slot_of_node);
     }
     if (depth < D - 1) {

@@ -315,9 +315,10 @@ struct Acc<false> {
   __device__ static bool nonzero(int g, int h) { return (g | h) != 0; }
   using wide_t = long long;
   __device__ static long long widen(int bits) { return bits; }
-  __device__ static void store_wide(out_t* dst, long long g, long long h)
+  __device__ static void add_wide(out_t* dst, long long g, long long h)
   {
-    *reinterpret_cast<longlong2*>(dst) = make_longlong2(g, h);
+    atomicAdd(reinterpret_cast<unsigned long long*>(&dst->grad), static_cast<unsigned long long>(g));
+    atomicAdd(reinterpret_cast<unsigned long long*>(&dst->hess), static_cast<unsigned long long>(h));
   }
 };
 template <>
@@ -337,9 +338,10 @@ struct Acc<true> {
   __device__ static bool nonzero(float g, float h) { return g != 0.f || h != 0.f; }
   using wide_t = double;
   __device__ static double widen(int bits) { return static_cast<double>(__int_as_float(bits)); }
-  __device__ static void store_wide(out_t* dst, double g, double h)
+  __device__ static void add_wide(out_t* dst, double g, double h)
   {
-    *reinterpret_cast<double2*>(dst) = make_double2(g, h);
+    atomicAdd(&dst->grad, g);
+    atomicAdd(&dst->hess, h);
   }
 };
 
@@ -607,11 +609,14 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
   }
 }
 
-// Adds up the partial-sum slots of every node that was cut into several chunks and stores the
-// totals.  grid = (nodes * tickets per chunk, kSumSplits); a block handles one (node, group set,
-// output) and 1/kSumSplits of its histogram words, a thread 16 bytes of every slot (four
-// neighbouring features of one bin), with four slots in flight.
+// Adds up the partial-sum slots of every node that was cut into several chunks and adds the
+// totals to the (zeroed) histogram.  grid = (nodes * tickets per chunk, kSumSplits, kSumParts): a
+// block handles one (node, group set, output), 1/kSumSplits of its histogram words and
+// 1/kSumParts of its slots; a thread reads 16 bytes of every slot of its part (four neighbouring
+// features of one bin), four slots in flight, and finishes with one pair of 64-bit atomics per
+// feature (kSumParts blocks meet in every word).
 constexpr int kSumSplits  = 16;
+constexpr int kSumParts   = 8;
 constexpr int kSumThreads = 256;
 
 template <bool kFloat, int W>
@@ -629,6 +634,9 @@ __global__ void __launch_bounds__(kSumThreads)
   const int j  = blockIdx.x / (p.K * GP);
   const int nchunks = p.chunk_off[j + 1] - p.chunk_off[j];
   if (nchunks <= 1) return;
+  const int per = (nchunks + kSumParts - 1) / kSumParts;
+  const int qb  = blockIdx.z * per, qe = min(nchunks, qb + per);
+  if (qb >= qe) return;
   const int slot       = p.slot_of_node ? p.slot_of_node[j] : j;
   const int hist_words = p.mb * kCols;
   const int n4         = hist_words >> 2;
@@ -641,11 +649,11 @@ __global__ void __launch_bounds__(kSumThreads)
     typename A::wide_t sg[4], sh[4];
 #pragma unroll
     for (int c4 = 0; c4 < 4; ++c4) sg[c4] = sh[c4] = 0;
-    for (int q0 = 0; q0 < nchunks; q0 += 4) {
+    for (int q0 = qb; q0 < qe; q0 += 4) {
       int4 vg[4], vh[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        if (q0 + u < nchunks) {
+        if (q0 + u < qe) {
           const smem_t* src = part + (first + (q0 + u) * step) * stride;
           vg[u] = __ldcg(reinterpret_cast<const int4*>(src) + e4);
           vh[u] = __ldcg(reinterpret_cast<const int4*>(src + hist_words) + e4);
@@ -666,7 +674,7 @@ __global__ void __launch_bounds__(kSumThreads)
       const int f = f0 + c4;
       if (f >= p.F) continue;
       const int fbeg = p.row_ptr[f];
-      if (bin < p.row_ptr[f + 1] - fbeg && (sg[c4] != 0 || sh[c4] != 0)) A::store_wide(onode + fbeg + bin, sg[c4], sh[c4]);
+      if (bin < p.row_ptr[f + 1] - fbeg && (sg[c4] != 0 || sh[c4] != 0)) A::add_wide(onode + fbeg + bin, sg[c4], sh[c4]);
     }
   }
 }
@@ -855,7 +863,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
   LBK_LAUNCH_CHECK();
   if (p.partial) {
-    hl.sum<<<dim3(static_cast<unsigned>(lv.n_nodes) * tickets_per_chunk, kSumSplits), kSumThreads, 0, stream>>>(p);
+    hl.sum<<<dim3(static_cast<unsigned>(lv.n_nodes) * tickets_per_chunk, kSumSplits, kSumParts), kSumThreads, 0, stream>>>(p);
     LBK_LAUNCH_CHECK();
   }
   if (ctx->profile) {

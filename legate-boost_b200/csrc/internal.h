@@ -170,10 +170,11 @@ void ScanLevel(const GPairI64* built, const int32_t* slot_of_node, GPairI64* lev
                const GPairI64* parent_hist /* level above, may be null */, int parent_begin,
                const GPairI64* node_sums, int node_begin, int n_nodes, int K, int F, int B,
                const int32_t* row_ptr, bool parent_available, cudaStream_t stream);
+// arrived: one counter per tree node, zero before the first call of a tree
 template <typename T>
-void BestSplit(const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B,
+void BestSplit(Scratch& s, const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B,
                const int32_t* row_ptr, const T* proposals, const QuantParams* qp, const SplitParams& sp,
-               TreeArrays tree, cudaStream_t stream);
+               TreeArrays tree, unsigned int* arrived, int sm_count, cudaStream_t stream);
 void RootLeaf(TreeArrays tree, int K, const QuantParams* qp, double l1, double l2, cudaStream_t stream);
 void WriteHessian(const GPairI64* node_sums, const QuantParams* qp, double* hessian, int64_t n, cudaStream_t stream);
 // partition.cu

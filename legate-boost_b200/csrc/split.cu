@@ -123,24 +123,40 @@ __device__ inline bool Better(const Cand& a, const Cand& b)
 
 constexpr int kSplitThreads = 256;
 
+// Candidate of one slice of a node's bins, as it travels through global memory.
+struct SliceBest {
+  double gain;
+  int bin;
+  int pad;
+};
+
+// grid = (nodes, slices): a block evaluates one slice of the node's bins (all of them when there is
+// one slice).  With several slices every block leaves its best candidate in `slice_best`, and the
+// block that arrives last (a counter per node, zeroed once per tree) picks the winner and writes
+// the tree.  Better() is a total order, so the winner does not depend on how the bins were cut.
 template <typename T>
 __global__ void __launch_bounds__(kSplitThreads)
   k_best_split(const GPairI64* __restrict__ level_hist, int node_begin, int K, int F, int B,
                const int32_t* __restrict__ row_ptr, const T* __restrict__ proposals,
                const QuantParams* __restrict__ qp_ptr, double l1, double l2, double msg,
-               const uint8_t* __restrict__ feature_set, TreeArrays tree)
+               const uint8_t* __restrict__ feature_set, TreeArrays tree, SliceBest* __restrict__ slice_best,
+               unsigned int* __restrict__ arrived)
 {
-  const int j    = blockIdx.x;
-  const int node = node_begin + j;
+  const int j      = blockIdx.x;
+  const int slices = gridDim.y;
+  const int node   = node_begin + j;
   GPairI64* node_sums = tree.node_sums;
   if (LoadPair(node_sums + static_cast<int64_t>(node) * K).hess <= 0) return;
   const QuantParams qp = *qp_ptr;
   const GPairI64* hist = level_hist + static_cast<int64_t>(j) * K * B;
   __shared__ Cand s_c[kSplitThreads / 32];
   __shared__ Cand s_best;
+  __shared__ bool s_last;
   const int tid = threadIdx.x;
+  const int per = (B + slices - 1) / slices;
+  const int b0  = blockIdx.y * per, b1 = min(B, b0 + per);
   Cand best{0.0, -1};
-  for (int b = tid; b < B; b += kSplitThreads) {
+  for (int b = b0 + tid; b < b1; b += kSplitThreads) {
     if (feature_set) {
       int lo = 0, hi = F;  // last f with row_ptr[f] <= b
       while (hi - lo > 1) {
@@ -163,22 +179,50 @@ __global__ void __launch_bounds__(kSplitThreads)
     const Cand c{gain, b};
     if (gain > 0 && Better(c, best)) best = c;
   }
+  auto warp_best = [&]() {
 #pragma unroll
-  for (int off = 16; off >= 1; off >>= 1) {
-    Cand o;
-    o.gain = __shfl_down_sync(0xffffffffu, best.gain, off);
-    o.bin  = __shfl_down_sync(0xffffffffu, best.bin, off);
-    if (Better(o, best)) best = o;
+    for (int off = 16; off >= 1; off >>= 1) {
+      Cand o;
+      o.gain = __shfl_down_sync(0xffffffffu, best.gain, off);
+      o.bin  = __shfl_down_sync(0xffffffffu, best.bin, off);
+      if (Better(o, best)) best = o;
+    }
+  };
+  auto block_best = [&]() {
+    warp_best();
+    if ((tid & 31) == 0) s_c[tid >> 5] = best;
+    __syncthreads();
+    if (tid == 0) {
+      Cand w0 = s_c[0];
+      for (int w = 1; w < kSplitThreads / 32; ++w)
+        if (Better(s_c[w], w0)) w0 = s_c[w];
+      s_best = w0;
+    }
+    __syncthreads();
+  };
+  block_best();
+  if (slices > 1) {
+    if (tid == 0) {
+      SliceBest sb;
+      sb.gain = s_best.gain;
+      sb.bin  = s_best.bin;
+      sb.pad  = 0;
+      slice_best[static_cast<int64_t>(j) * slices + blockIdx.y] = sb;
+      __threadfence();
+      s_last = atomicAdd(arrived + node, 1u) == static_cast<unsigned>(slices - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = Cand{0.0, -1};
+    for (int i = tid; i < slices; i += kSplitThreads) {
+      const volatile SliceBest* sb = slice_best + static_cast<int64_t>(j) * slices + i;
+      const Cand c{sb->gain, sb->bin};
+      if (Better(c, best)) best = c;
+    }
+    __syncthreads();
+    block_best();
   }
-  if ((tid & 31) == 0) s_c[tid >> 5] = best;
-  __syncthreads();
-  if (tid == 0) {
-    Cand b0 = s_c[0];
-    for (int w = 1; w < kSplitThreads / 32; ++w)
-      if (Better(s_c[w], b0)) b0 = s_c[w];
-    s_best = b0;
-  }
-  __syncthreads();
   const Cand nb = s_best;
   if (!(nb.gain > 1e-5)) return;
   int lo = 0, hi = F;
@@ -244,12 +288,22 @@ void ScanLevel(const GPairI64* built, const int32_t* slot_of_node, GPairI64* lev
 }
 
 template <typename T>
-void BestSplit(const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B, const int32_t* row_ptr,
-               const T* proposals, const QuantParams* qp, const SplitParams& sp, TreeArrays tree, cudaStream_t stream)
+void BestSplit(Scratch& s, const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B,
+               const int32_t* row_ptr, const T* proposals, const QuantParams* qp, const SplitParams& sp, TreeArrays tree,
+               unsigned int* arrived, int sm_count, cudaStream_t stream)
 {
-  k_best_split<T><<<n_nodes, kSplitThreads, 0, stream>>>(level_hist, node_begin, K, F, B, row_ptr, proposals, qp, sp.l1,
-                                                         sp.l2, sp.min_split_gain, sp.feature_set, tree);
+  // enough blocks for two per SM, at least one thread per bin in a block's slice
+  int slices = (2 * sm_count + n_nodes - 1) / n_nodes;
+  const int most = (B + kSplitThreads - 1) / kSplitThreads;
+  if (slices > most) slices = most;
+  if (slices > kSplitThreads) slices = kSplitThreads;
+  if (slices < 1) slices = 1;
+  SliceBest* slice_best = slices > 1 ? s.alloc<SliceBest>(static_cast<size_t>(n_nodes) * slices) : nullptr;
+  k_best_split<T><<<dim3(n_nodes, slices), kSplitThreads, 0, stream>>>(level_hist, node_begin, K, F, B, row_ptr, proposals,
+                                                                      qp, sp.l1, sp.l2, sp.min_split_gain, sp.feature_set,
+                                                                      tree, slice_best, arrived);
   LBK_LAUNCH_CHECK();
+  if (slice_best) s.free_one(slice_best);
 }
 
 void RootLeaf(TreeArrays tree, int K, const QuantParams* qp, double l1, double l2, cudaStream_t stream)
@@ -264,9 +318,9 @@ void WriteHessian(const GPairI64* node_sums, const QuantParams* qp, double* hess
   LBK_LAUNCH_CHECK();
 }
 
-template void BestSplit<float>(const GPairI64*, int, int, int, int, int, const int32_t*, const float*, const QuantParams*,
-                               const SplitParams&, TreeArrays, cudaStream_t);
-template void BestSplit<double>(const GPairI64*, int, int, int, int, int, const int32_t*, const double*,
-                                const QuantParams*, const SplitParams&, TreeArrays, cudaStream_t);
+template void BestSplit<float>(Scratch&, const GPairI64*, int, int, int, int, int, const int32_t*, const float*,
+                               const QuantParams*, const SplitParams&, TreeArrays, unsigned int*, int, cudaStream_t);
+template void BestSplit<double>(Scratch&, const GPairI64*, int, int, int, int, int, const int32_t*, const double*,
+                                const QuantParams*, const SplitParams&, TreeArrays, unsigned int*, int, cudaStream_t);
 
 }  // namespace lbk
