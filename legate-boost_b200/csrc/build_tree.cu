@@ -86,7 +86,10 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
   // binned matrix, once per tree
   const int bin_bytes = pi.max_bins_per_feature <= 256 ? 1 : 2;
   void* bins          = s.alloc_bytes(lbk_bin_matrix_bytes(N, F, bin_bytes));
-  BinMatrix<T>(X, ldx, N, F, proposals, row_ptr, bins, bin_bytes, pi.max_bins_per_feature, stream);
+  // feature-major copy for the repartition (no copy for a stump: nothing is repartitioned)
+  const int64_t pitch_t = (N + 31) / 32 * 32;
+  void* bins_t          = D > 1 ? s.alloc_bytes(static_cast<size_t>(F) * pitch_t * bin_bytes + 16) : nullptr;
+  BinMatrix<T>(X, ldx, N, F, proposals, row_ptr, bins, bins_t, pitch_t, bin_bytes, pi.max_bins_per_feature, stream);
 
   // quantised pairs and root sums
   QuantParams* qp = s.alloc<QuantParams>(1);
@@ -223,9 +226,9 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
     }
     if (depth < D - 1) {
       PartitionLevel pl;
-      pl.bins          = bins;
+      pl.bins          = bins_t;
       pl.bin_bytes     = bin_bytes;
-      pl.bin_pitch     = static_cast<int64_t>((F + kGroup - 1) / kGroup) * kGroup;
+      pl.bin_pitch     = pitch_t;
       pl.n_rows        = N;
       pl.row_index_in  = rows_a;
       pl.seg_in        = seg_a;
@@ -387,10 +390,10 @@ int lbk_bin_matrix(lbk_context* ctx, const void* X, int x_dtype, int64_t ldx, in
     LBK_EXPECT(bin_bytes == 2 || mb <= 256, "one-byte bins need <= 256 proposals per feature");
     if (x_dtype == LBK_F32)
       lbk::BinMatrix<float>(static_cast<const float*>(X), ldx, n_rows, n_features, static_cast<const float*>(proposals),
-                            row_ptr, bins, bin_bytes, mb, stream);
+                            row_ptr, bins, nullptr, 0, bin_bytes, mb, stream);
     else
       lbk::BinMatrix<double>(static_cast<const double*>(X), ldx, n_rows, n_features,
-                             static_cast<const double*>(proposals), row_ptr, bins, bin_bytes, mb, stream);
+                             static_cast<const double*>(proposals), row_ptr, bins, nullptr, 0, bin_bytes, mb, stream);
   });
 }
 

@@ -119,8 +119,10 @@ ProposalInfo SplitProposals(lbk_context* ctx, Scratch& s, const T* X, int64_t ld
                             int64_t n_local, int F, int S, int seed, int64_t dataset_rows, T* proposals,
                             int32_t* row_ptr, cudaStream_t stream);  // synchronises the stream
 template <typename T>
+// bins_t (optional): feature-major copy, bins_t[f * pitch_t + row], pitch_t a multiple of 32 >= n_rows
 void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposals, const int32_t* row_ptr,
-               void* bins, int bin_bytes, int max_bins_per_feature, cudaStream_t stream);
+               void* bins, void* bins_t, int64_t pitch_t, int bin_bytes, int max_bins_per_feature,
+               cudaStream_t stream);
 // quantise.cu
 void Quantise(lbk_context* ctx, Scratch& s, const double* g, const double* h, int64_t ldg, int64_t row_offset,
               int64_t n_local, int K, int seed, int2* gpair, GPairI64* root_sums, QuantParams* params,
@@ -179,9 +181,9 @@ void RootLeaf(TreeArrays tree, int K, const QuantParams* qp, double l1, double l
 void WriteHessian(const GPairI64* node_sums, const QuantParams* qp, double* hessian, int64_t n, cudaStream_t stream);
 // partition.cu
 struct PartitionLevel {
-  const void* bins;
+  const void* bins;   // feature-major copy of the bin ids: bins[f * bin_pitch + row]
   int bin_bytes;
-  int64_t bin_pitch;  // elements per row of bins (features rounded up to a multiple of kGroup)
+  int64_t bin_pitch;  // elements per feature
   int64_t n_rows;
   const int32_t* row_index_in;
   const int32_t* seg_in;  // [n_nodes+1] for the level

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kPartThreads)
   const int sb   = split_bin[node];
   const int rb   = seg[j] + (c - chunk_off[j]) * kPartTile;
   const int re   = min(seg[j + 1], rb + kPartTile);
-  const BinT* col = bins + f;  // row-major bins, `pitch` elements per row
+  const BinT* col = bins + static_cast<int64_t>(f) * pitch;  // feature-major copy: the rows of a node are neighbours
   const int tid  = threadIdx.x;
   const int r0   = rb + tid * kPartItems;
   unsigned mask  = 0;
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kPartThreads)
     const int r = r0 + i;
     if (r < re) {
       const int ridx = row_index[r];
-      const int bin  = col[static_cast<int64_t>(ridx) * pitch];
+      const int bin  = col[ridx];
       if (bin <= sb) mask |= 1u << i;
     }
   }

@@ -184,7 +184,8 @@ __device__ inline double LdsT(unsigned addr, double)
 template <typename T, typename BinT>
 __global__ void __launch_bounds__(256)
   k_bin_smem(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, const T* __restrict__ proposals,
-             const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins, int P)
+             const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins, BinT* __restrict__ bins_t, int64_t pitch_t,
+             int P)
 {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* sp          = reinterpret_cast<T*>(smem_raw);
@@ -252,6 +253,13 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int u = 0; u < U; ++u)
       if (base + u < n_rows) orow[u * pitch] = static_cast<BinT>(posb[u] / kPitch);
+    if (bins_t != nullptr && active) {
+      // feature-major copy: the U ids of this lane's feature are neighbours there (one store)
+      struct alignas(sizeof(BinT) * U) Pack { BinT v[U]; } pk;
+#pragma unroll
+      for (int u = 0; u < U; ++u) pk.v[u] = static_cast<BinT>(posb[u] / kPitch);
+      *reinterpret_cast<Pack*>(bins_t + static_cast<int64_t>(f0 + lane) * pitch_t + base) = pk;
+    }
   }
 }
 
@@ -259,7 +267,7 @@ __global__ void __launch_bounds__(256)
 template <typename T, typename BinT>
 __global__ void __launch_bounds__(256)
   k_bin_global(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, const T* __restrict__ proposals,
-               const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins)
+               const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins, BinT* __restrict__ bins_t, int64_t pitch_t)
 {
   const int g    = blockIdx.y;
   const int f0   = g * kGroup;
@@ -289,6 +297,7 @@ __global__ void __launch_bounds__(256)
       bin = base + ((p[base] < x) ? 1 : 0);
     }
     out[row * pitch + lane] = static_cast<BinT>(bin);
+    if (bins_t != nullptr && active) bins_t[static_cast<int64_t>(f) * pitch_t + row] = static_cast<BinT>(bin);
   }
 }
 
@@ -337,7 +346,7 @@ ProposalInfo SplitProposals(lbk_context* ctx, Scratch& s, const T* X, int64_t ld
 
 template <typename T>
 void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposals, const int32_t* row_ptr,
-               void* bins, int bin_bytes, int max_bins_per_feature, cudaStream_t stream)
+               void* bins, void* bins_t, int64_t pitch_t, int bin_bytes, int max_bins_per_feature, cudaStream_t stream)
 {
   if (n_rows <= 0) return;
   const int G           = (F + kGroup - 1) / kGroup;
@@ -358,10 +367,12 @@ void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposal
         LBK_CUDA(cudaFuncSetAttribute(k_bin_smem<T, BinT>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                       static_cast<int>(smem)));                                           \
       k_bin_smem<T, BinT><<<grid, 256, smem, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,            \
-                                                        static_cast<BinT*>(bins), P);                     \
+                                                        static_cast<BinT*>(bins), static_cast<BinT*>(bins_t), \
+                                                        pitch_t, P);                                      \
     } else {                                                                                              \
       k_bin_global<T, BinT><<<grid, 256, 0, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,             \
-                                                       static_cast<BinT*>(bins));                         \
+                                                       static_cast<BinT*>(bins), static_cast<BinT*>(bins_t), \
+                                                       pitch_t);                                          \
     }                                                                                                     \
   } while (0)
   if (bin_bytes == 1) {
@@ -377,9 +388,9 @@ template ProposalInfo SplitProposals<float>(lbk_context*, Scratch&, const float*
                                    int64_t, float*, int32_t*, cudaStream_t);
 template ProposalInfo SplitProposals<double>(lbk_context*, Scratch&, const double*, int64_t, int64_t, int64_t, int, int, int,
                                     int64_t, double*, int32_t*, cudaStream_t);
-template void BinMatrix<float>(const float*, int64_t, int64_t, int, const float*, const int32_t*, void*, int, int,
-                               cudaStream_t);
-template void BinMatrix<double>(const double*, int64_t, int64_t, int, const double*, const int32_t*, void*, int, int,
-                                cudaStream_t);
+template void BinMatrix<float>(const float*, int64_t, int64_t, int, const float*, const int32_t*, void*, void*, int64_t,
+                               int, int, cudaStream_t);
+template void BinMatrix<double>(const double*, int64_t, int64_t, int, const double*, const int32_t*, void*, void*,
+                                int64_t, int, int, cudaStream_t);
 
 }  // namespace lbk
