@@ -160,33 +160,69 @@ __global__ void k_write_proposals(const T* __restrict__ uniq, int S, const int32
   }
 }
 
+// Streaming global loads as volatile asm: they stay where they are written, ahead of the search
+// of the previous rows (the compiler otherwise sinks them to their first use).
+__device__ inline float LdgStream(const float* p)
+{
+  float v;
+  asm volatile("ld.global.cs.f32 %0, [%1];\n" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ inline double LdgStream(const double* p)
+{
+  double v;
+  asm volatile("ld.global.cs.f64 %0, [%1];\n" : "=d"(v) : "l"(p));
+  return v;
+}
+
+template <int kOffset>
 __device__ inline float LdsT(unsigned addr, float)
 {
   float v;
-  asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
+  asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(v) : "r"(addr), "n"(kOffset));
   return v;
 }
+template <int kOffset>
 __device__ inline double LdsT(unsigned addr, double)
 {
   double v;
-  asm volatile("ld.shared.f64 %0, [%1];\n" : "=d"(v) : "r"(addr));
+  asm volatile("ld.shared.f64 %0, [%1+%2];\n" : "=d"(v) : "r"(addr), "n"(kOffset));
   return v;
 }
+
+// One lower_bound step for U rows at once: "advance by 2^kLevel proposals if the proposal just
+// before that point is below x".  The probe offset is an immediate of the load; what remains per
+// row and step is one shared-memory load, one compare and one predicated add.
+template <typename T, int U, int kLevel, unsigned kPitch>
+struct SearchLevels {
+  __device__ static void run(unsigned (&pos)[U], const T (&x)[U])
+  {
+    constexpr int step = 1 << kLevel;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (LdsT<(step - 1) * static_cast<int>(kPitch)>(pos[u], T()) < x[u]) pos[u] += step * kPitch;
+    SearchLevels<T, U, kLevel - 1, kPitch>::run(pos, x);
+  }
+};
+template <typename T, int U, unsigned kPitch>
+struct SearchLevels<T, U, -1, kPitch> {
+  __device__ static void run(unsigned (&)[U], const T (&)[U]) {}
+};
 
 // One warp per row, one lane per feature of the group.
 //
 // Shared-memory variant: the proposals of the group are kept transposed and padded, sp[j][lane] =
-// proposal j of the lane's feature (+inf beyond the feature's last one, P = power of two rows), so
-// that every probe of lane l goes to bank l: the eight probes of a lower_bound cost eight
-// conflict-free wavefronts per warp and row instead of eight 3-4-way conflicted ones.  The search
-// is the branchless form "pos += step while sp[pos+step-1] < x", which returns the number of
-// proposals below x, i.e. the index of the first proposal >= x.
-template <typename T, typename BinT>
-__global__ void __launch_bounds__(256)
+// proposal j of the lane's feature (+inf beyond the feature's last one, P = 2^kLog2P rows), so
+// that every probe of lane l goes to bank l: the probes of a lower_bound are conflict-free
+// wavefronts whatever the values.  The search is the branchless form "pos += step while
+// sp[pos+step-1] < x" on the shared-memory address of the lane's column, fully unrolled; it
+// returns the number of proposals below x, i.e. the index of the first proposal >= x.
+template <typename T, typename BinT, int kLog2P, bool kCopyT>
+__global__ void __launch_bounds__(256, sizeof(T) == 4 ? 4 : 2)
   k_bin_smem(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, const T* __restrict__ proposals,
-             const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins, BinT* __restrict__ bins_t, int64_t pitch_t,
-             int P)
+             const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins, BinT* __restrict__ bins_t, int64_t pitch_t)
 {
+  constexpr int P = 1 << kLog2P;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* sp          = reinterpret_cast<T*>(smem_raw);
   const int g    = blockIdx.y;
@@ -202,63 +238,64 @@ __global__ void __launch_bounds__(256)
     sp[idx] = v;
   }
   __syncthreads();
-  const bool active = f0 + lane < F;
-  // The search runs on byte offsets into this lane's column of the table (pitch = one table row).
-  // The three top levels of the search (seven pivots) are held in registers: they are the same
-  // for every row a lane sees, which leaves log2(P) - 3 shared-memory probes per element.
-  constexpr unsigned kPitch = kGroup * sizeof(T);
+  // Lanes beyond the last feature read the last feature's values (in bounds) and store zeros.
+  const bool active    = f0 + lane < F;
+  const unsigned amask = active ? 0xffffffffu : 0u;
+  constexpr unsigned kPitch = kGroup * sizeof(T);  // bytes from one proposal of a feature to the next
   const unsigned col_s      = static_cast<unsigned>(__cvta_generic_to_shared(sp + lane));
-  const bool top3           = P >= 8;
-  T piv[7];
-#pragma unroll
-  for (int i = 0; i < 7; ++i) piv[i] = top3 ? sp[((i + 1) * (P >> 3) - 1) * kGroup + lane] : static_cast<T>(INFINITY);
-  const unsigned half = (P >> 1) * kPitch, quarter = (P >> 2) * kPitch, eighth = (P >> 3) * kPitch;
-  const int64_t pitch = static_cast<int64_t>(gridDim.y) * kGroup;  // bins are row-major, rows padded to groups
-  BinT* out         = bins + f0 + lane;
-  const T* xin      = X + f0 + lane;
+  // rows are counted in 32 bits (row indices are 32-bit everywhere in this library)
+  const int pitch   = static_cast<int>(gridDim.y) * kGroup;  // bins are row-major, rows padded to groups
   constexpr int U   = 8;  // rows per warp in flight
-  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-  const int64_t w0          = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5);
-  for (int64_t base = w0 * U; base < n_rows; base += warps_total * U) {
+  const int n       = static_cast<int>(n_rows);
+  const int ld      = static_cast<int>(ldx);
+  const int hop     = static_cast<int>(gridDim.x) * (blockDim.x >> 5) * U;  // rows from one turn of a warp to the next
+  int base          = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U;
+  const T* xr       = X + (active ? f0 + lane : F - 1) + static_cast<int64_t>(base) * ld;
+  BinT* orow        = bins + f0 + lane + static_cast<int64_t>(base) * pitch;
+  BinT* trow        = kCopyT ? bins_t + static_cast<int64_t>(active ? f0 + lane : F - 1) * pitch_t + base : nullptr;
+  // the values of the warp's next eight rows are loaded while the current eight are searched
+  auto load_rows = [&](const T* src, int first, T (&x)[U]) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) x[u] = first + u < n ? LdgStream(src + u * ld) : static_cast<T>(-INFINITY);
+  };
+  T xn[U];
+  if (base < n) load_rows(xr, base, xn);
+  for (; base < n; base += hop) {
     T x[U];
-    unsigned posb[U];
-    const T* xr = xin + base * ldx;
+    unsigned pos[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-      x[u] = (active && base + u < n_rows) ? __ldcs(xr + u * ldx) : static_cast<T>(-INFINITY);
-    int first_step = P >> 1;
-    if (top3) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const bool c1 = piv[3] < x[u];                       // proposal P/2 - 1
-        const T p2    = c1 ? piv[5] : piv[1];                // 3P/4 - 1 or P/4 - 1
-        const bool c2 = p2 < x[u];
-        const T p3    = c1 ? (c2 ? piv[6] : piv[4]) : (c2 ? piv[2] : piv[0]);
-        const bool c3 = p3 < x[u];
-        posb[u]       = (c1 ? half : 0u) + (c2 ? quarter : 0u) + (c3 ? eighth : 0u);
-      }
-      first_step = P >> 4;
-    } else {
-#pragma unroll
-      for (int u = 0; u < U; ++u) posb[u] = 0;
+    for (int u = 0; u < U; ++u) {
+      x[u]   = xn[u];
+      pos[u] = col_s;
     }
-    for (int step = first_step; step >= 1; step >>= 1) {
-      const unsigned probe = col_s + static_cast<unsigned>(step - 1) * kPitch;
-      const unsigned adv   = static_cast<unsigned>(step) * kPitch;
+    xr += static_cast<int64_t>(hop) * ld;
+    if (hop < n - base) load_rows(xr, base + hop, xn);
+    SearchLevels<T, U, kLog2P - 1, kPitch>::run(pos, x);
+    unsigned id[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (LdsT(probe + posb[u], T()) < x[u]) posb[u] += adv;
+    for (int u = 0; u < U; ++u) {
+      id[u] = ((pos[u] - col_s) / kPitch) & amask;
+      if (base + u < n) orow[u * pitch] = static_cast<BinT>(id[u]);
     }
-    BinT* orow = out + base * pitch;
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-      if (base + u < n_rows) orow[u * pitch] = static_cast<BinT>(posb[u] / kPitch);
-    if (bins_t != nullptr && active) {
+    orow += static_cast<int64_t>(hop) * pitch;
+    if (kCopyT) {
       // feature-major copy: the U ids of this lane's feature are neighbours there (one store)
-      struct alignas(sizeof(BinT) * U) Pack { BinT v[U]; } pk;
-#pragma unroll
-      for (int u = 0; u < U; ++u) pk.v[u] = static_cast<BinT>(posb[u] / kPitch);
-      *reinterpret_cast<Pack*>(bins_t + static_cast<int64_t>(f0 + lane) * pitch_t + base) = pk;
+      if (active) {
+        if (sizeof(BinT) == 1) {
+          uint2 pk;
+          pk.x = id[0] | (id[1] << 8) | (id[2] << 16) | (id[3] << 24);
+          pk.y = id[4] | (id[5] << 8) | (id[6] << 16) | (id[7] << 24);
+          *reinterpret_cast<uint2*>(trow) = pk;
+        } else {
+          uint4 pk;
+          pk.x = id[0] | (id[1] << 16);
+          pk.y = id[2] | (id[3] << 16);
+          pk.z = id[4] | (id[5] << 16);
+          pk.w = id[6] | (id[7] << 16);
+          *reinterpret_cast<uint4*>(trow) = pk;
+        }
+      }
+      trow += hop;
     }
   }
 }
@@ -349,28 +386,48 @@ void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposal
                void* bins, void* bins_t, int64_t pitch_t, int bin_bytes, int max_bins_per_feature, cudaStream_t stream)
 {
   if (n_rows <= 0) return;
+  LBK_EXPECT(n_rows <= 2000000000ll && ldx <= (1 << 27), "bin_matrix: at most 2e9 rows per rank and a row pitch of 2^27 elements");
   const int G           = (F + kGroup - 1) / kGroup;
-  const int P           = NextPow2(max_bins_per_feature);
-  const size_t smem     = sizeof(T) * static_cast<size_t>(kGroup) * P;
-  const bool use_smem   = smem <= 96 * 1024;
-  // a block fills its table once and then walks the rows with a grid stride: keep the grid near
-  // the number of resident blocks
-  int64_t blocks_x      = (n_rows + 63) / 64;
-  const int64_t resident = 148 * 6 / (G > 6 ? 6 : G);
-  if (blocks_x > resident) blocks_x = resident;
-  if (blocks_x < 1) blocks_x = 1;
-  dim3 grid(static_cast<unsigned>(blocks_x), G);
+  // the shared-memory table is padded to one of a few sizes (each is its own fully unrolled kernel)
+  const int need   = NextPow2(max_bins_per_feature);
+  const int log2p  = need <= 16 ? 4 : need <= 64 ? 6 : need <= 256 ? 8 : 9;
+  const size_t smem     = sizeof(T) * static_cast<size_t>(kGroup) * (size_t{1} << log2p);
+  const bool use_smem   = need <= 512 && smem <= 96 * 1024;
+  // a block fills its table once and then walks the rows with a grid stride: the grid is what is
+  // resident at once (from the occupancy calculator), spread over the feature groups
+  auto make_grid = [&](int blocks_per_sm) {
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int64_t blocks_x = (static_cast<int64_t>(sms) * (blocks_per_sm > 0 ? blocks_per_sm : 1) + G - 1) / G;
+    const int64_t most = (n_rows + 63) / 64;
+    if (blocks_x > most) blocks_x = most;
+    if (blocks_x < 1) blocks_x = 1;
+    return dim3(static_cast<unsigned>(blocks_x), G);
+  };
+#define LBK_BIN_SMEM2(BinT, L, CT)                                                                        \
+  do {                                                                                                    \
+    auto fn_ = k_bin_smem<T, BinT, L, CT>;                                                                \
+    if (smem > 48 * 1024)                                                                                 \
+      LBK_CUDA(cudaFuncSetAttribute(fn_, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))); \
+    int per_sm_ = 0;                                                                                      \
+    LBK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_, fn_, 256, smem));                    \
+    fn_<<<make_grid(per_sm_), 256, smem, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,                 \
+                                                   static_cast<BinT*>(bins), static_cast<BinT*>(bins_t), pitch_t); \
+  } while (0)
+#define LBK_BIN_SMEM(BinT, L)                                                                             \
+  do {                                                                                                    \
+    if (bins_t != nullptr) LBK_BIN_SMEM2(BinT, L, true); else LBK_BIN_SMEM2(BinT, L, false);              \
+  } while (0)
 #define LBK_BIN_LAUNCH(BinT)                                                                              \
   do {                                                                                                    \
     if (use_smem) {                                                                                       \
-      if (smem > 48 * 1024)                                                                               \
-        LBK_CUDA(cudaFuncSetAttribute(k_bin_smem<T, BinT>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                      static_cast<int>(smem)));                                           \
-      k_bin_smem<T, BinT><<<grid, 256, smem, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,            \
-                                                        static_cast<BinT*>(bins), static_cast<BinT*>(bins_t), \
-                                                        pitch_t, P);                                      \
+      if (log2p == 4) LBK_BIN_SMEM(BinT, 4);                                                              \
+      else if (log2p == 6) LBK_BIN_SMEM(BinT, 6);                                                         \
+      else if (log2p == 8) LBK_BIN_SMEM(BinT, 8);                                                         \
+      else LBK_BIN_SMEM(BinT, 9);                                                                         \
     } else {                                                                                              \
-      k_bin_global<T, BinT><<<grid, 256, 0, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,             \
+      k_bin_global<T, BinT><<<make_grid(8), 256, 0, stream>>>(X, ldx, n_rows, F, proposals, row_ptr,     \
                                                        static_cast<BinT*>(bins), static_cast<BinT*>(bins_t), \
                                                        pitch_t);                                          \
     }                                                                                                     \
@@ -380,6 +437,8 @@ void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposal
   } else {
     LBK_BIN_LAUNCH(uint16_t);
   }
+#undef LBK_BIN_SMEM
+#undef LBK_BIN_SMEM2
 #undef LBK_BIN_LAUNCH
   LBK_LAUNCH_CHECK();
 }
