@@ -248,54 +248,66 @@ __global__ void __launch_bounds__(256, sizeof(T) == 4 ? 4 : 2)
   constexpr int U   = 8;  // rows per warp in flight
   const int n       = static_cast<int>(n_rows);
   const int ld      = static_cast<int>(ldx);
-  const int hop     = static_cast<int>(gridDim.x) * (blockDim.x >> 5) * U;  // rows from one turn of a warp to the next
-  int base          = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U;
-  const T* xr       = X + (active ? f0 + lane : F - 1) + static_cast<int64_t>(base) * ld;
-  BinT* orow        = bins + f0 + lane + static_cast<int64_t>(base) * pitch;
-  BinT* trow        = kCopyT ? bins_t + static_cast<int64_t>(active ? f0 + lane : F - 1) * pitch_t + base : nullptr;
+  // A warp takes 32 consecutive rows per turn, eight at a time.  With one-byte ids a lane keeps
+  // the 32 ids of its feature in registers and writes them to the feature-major copy as one whole
+  // 32-byte sector per turn.
+  constexpr int kSubs = 4;
+  constexpr int kTurn = kSubs * U;
+  const int hop     = static_cast<int>(gridDim.x) * (blockDim.x >> 5) * kTurn;  // rows from one turn of a warp to the next
+  int turn          = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kTurn;
+  const T* xcol     = X + (active ? f0 + lane : F - 1);
+  BinT* ocol        = bins + f0 + lane;
+  BinT* tcol        = kCopyT ? bins_t + static_cast<int64_t>(active ? f0 + lane : F - 1) * pitch_t : nullptr;
   // the values of the warp's next eight rows are loaded while the current eight are searched
-  auto load_rows = [&](const T* src, int first, T (&x)[U]) {
+  auto load_rows = [&](int first, T (&x)[U]) {
+    const T* src = xcol + static_cast<int64_t>(first) * ld;
 #pragma unroll
     for (int u = 0; u < U; ++u) x[u] = first + u < n ? LdgStream(src + u * ld) : static_cast<T>(-INFINITY);
   };
   T xn[U];
-  if (base < n) load_rows(xr, base, xn);
-  for (; base < n; base += hop) {
-    T x[U];
-    unsigned pos[U];
+  if (turn < n) load_rows(turn, xn);
+  for (; turn < n; turn += hop) {
+    uint2 sector[kSubs];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      x[u]   = xn[u];
-      pos[u] = col_s;
-    }
-    xr += static_cast<int64_t>(hop) * ld;
-    if (hop < n - base) load_rows(xr, base + hop, xn);
-    SearchLevels<T, U, kLog2P - 1, kPitch>::run(pos, x);
-    unsigned id[U];
+    for (int sub = 0; sub < kSubs; ++sub) {
+      const int base = turn + sub * U;
+      T x[U];
+      unsigned pos[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      id[u] = ((pos[u] - col_s) / kPitch) & amask;
-      if (base + u < n) orow[u * pitch] = static_cast<BinT>(id[u]);
-    }
-    orow += static_cast<int64_t>(hop) * pitch;
-    if (kCopyT) {
-      // feature-major copy: the U ids of this lane's feature are neighbours there (one store)
-      if (active) {
+      for (int u = 0; u < U; ++u) {
+        x[u]   = xn[u];
+        pos[u] = col_s;
+      }
+      {
+        const int nb = sub + 1 < kSubs ? base + U : turn + hop;
+        if (nb < n) load_rows(nb, xn);
+      }
+      SearchLevels<T, U, kLog2P - 1, kPitch>::run(pos, x);
+      unsigned id[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) id[u] = ((pos[u] - col_s) / kPitch) & amask;
+      BinT* orow = ocol + static_cast<int64_t>(base) * pitch;
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (base + u < n) orow[u * pitch] = static_cast<BinT>(id[u]);
+      if (kCopyT) {
         if (sizeof(BinT) == 1) {
-          uint2 pk;
-          pk.x = id[0] | (id[1] << 8) | (id[2] << 16) | (id[3] << 24);
-          pk.y = id[4] | (id[5] << 8) | (id[6] << 16) | (id[7] << 24);
-          *reinterpret_cast<uint2*>(trow) = pk;
-        } else {
+          sector[sub].x = id[0] | (id[1] << 8) | (id[2] << 16) | (id[3] << 24);
+          sector[sub].y = id[4] | (id[5] << 8) | (id[6] << 16) | (id[7] << 24);
+        } else if (active && base < n) {
           uint4 pk;
           pk.x = id[0] | (id[1] << 16);
           pk.y = id[2] | (id[3] << 16);
           pk.z = id[4] | (id[5] << 16);
           pk.w = id[6] | (id[7] << 16);
-          *reinterpret_cast<uint4*>(trow) = pk;
+          *reinterpret_cast<uint4*>(tcol + base) = pk;
         }
       }
-      trow += hop;
+    }
+    if (kCopyT && sizeof(BinT) == 1 && active) {
+      uint4* dst = reinterpret_cast<uint4*>(tcol + turn);
+      dst[0]     = make_uint4(sector[0].x, sector[0].y, sector[1].x, sector[1].y);
+      dst[1]     = make_uint4(sector[2].x, sector[2].y, sector[3].x, sector[3].y);
     }
   }
 }
