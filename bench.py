@@ -108,12 +108,12 @@ def hist_inputs(torch, n_rows, seed, device):
     row_ptr = (torch.arange(HIST_FEATURES + 1, dtype=torch.int32, device=device) * HIST_BINS)
     g = torch.randn((n_rows, 1), dtype=torch.float64, device=device, generator=gen)
     h = torch.ones((n_rows, 1), dtype=torch.float64, device=device)
-    gpair, _, _ = stages.quantise(g, h, seed=seed)
+    gpair, _, _, max_abs = stages.quantise(g, h, seed=seed, with_max_abs=True)
     gpair_f = torch.stack([g.to(torch.float32), h.to(torch.float32)], dim=2).contiguous()
     node = torch.randint(0, HIST_NODES, (n_rows,), dtype=torch.int32, device=device, generator=gen) + (HIST_NODES - 1)
     row_index, seg = stages.group_rows(node, HIST_NODES - 1, HIST_NODES)
     del g, h
-    return bins, row_ptr, gpair, gpair_f, row_index, seg, node
+    return bins, row_ptr, gpair, gpair_f, row_index, seg, node, max_abs
 
 
 def algorithmic_bytes(n_rows):
@@ -237,7 +237,7 @@ def run_hist(args):
     lib = ctx.lib
     n_rows = args.rows
     mode = 1 if args.float_path else 0
-    bins, row_ptr, gpair, gpair_f, row_index, seg, node = hist_inputs(torch, n_rows, 1 + rank, device)
+    bins, row_ptr, gpair, gpair_f, row_index, seg, node, max_abs = hist_inputs(torch, n_rows, 1 + rank, device)
     gp = gpair_f if mode else gpair
     hist = torch.empty((HIST_NODES, 1, HIST_FEATURES * HIST_BINS, 2),
                        dtype=torch.float64 if mode else torch.int64, device=device)
@@ -247,7 +247,8 @@ def run_hist(args):
     import ctypes as C
 
     def step():
-        stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, mode=mode, hist=hist, ctx=ctx)
+        stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, mode=mode, hist=hist, ctx=ctx,
+                         max_abs=max_abs if mode == 0 else None)
         if world > 1:
             dist.all_reduce(hist)
 

@@ -172,10 +172,12 @@ size_t lbk_bin_matrix_bytes(int64_t n_rows, int n_features, int bin_bytes);
 
 /* Quantised gradient pairs (reference: GradientQuantiser, build_tree.cu:51-140, and
  * reduce_base_sums, :168-204).  gpair: int32 [n_local_rows, n_outputs, 2]; root_sums: int64
- * [n_outputs, 2] (summed over ranks); scale: double[4] = scale.g, scale.h, 1/scale.g, 1/scale.h. */
+ * [n_outputs, 2] (summed over ranks); scale: double[4] = scale.g, scale.h, 1/scale.g, 1/scale.h;
+ * max_abs (optional, may be NULL): device int32[2], the largest |grad| and |hess| among this
+ * rank's quantised pairs - what lbk_histogram_args.max_abs takes. */
 int lbk_quantise(lbk_context* ctx, const double* g, const double* h, int64_t ldg, int64_t row_offset,
                  int64_t n_local_rows, int n_outputs, int seed, int32_t* gpair, int64_t* root_sums,
-                 double* scale, void* stream);
+                 double* scale, int32_t* max_abs, void* stream);
 
 /* Histogram build over node-grouped rows (reference: fill_histogram_shared, build_tree.cu:213-577).
  * Rows are given as an index array grouped by node: rows of node (node_begin + j) are
@@ -201,6 +203,8 @@ typedef struct lbk_histogram_args {
   void* hist;
   void* stream;
   int32_t host_buffers;
+  const int32_t* max_abs;   /* mode 0, optional: device int32[2] = largest |grad|, |hess| in gpair (the
+                               call bounds its 32-bit partial sums with it); NULL = found by the call */
 } lbk_histogram_args;
 
 int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* args);

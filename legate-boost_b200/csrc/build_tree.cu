@@ -399,7 +399,7 @@ int lbk_bin_matrix(lbk_context* ctx, const void* X, int x_dtype, int64_t ldx, in
 
 int lbk_quantise(lbk_context* ctx, const double* g, const double* h, int64_t ldg, int64_t row_offset,
                  int64_t n_local_rows, int n_outputs, int seed, int32_t* gpair, int64_t* root_sums, double* scale,
-                 void* stream_)
+                 int32_t* max_abs, void* stream_)
 {
   return lbk::Guard(ctx, [&] {
     LBK_EXPECT(ctx && gpair && root_sums && scale, "null argument");
@@ -408,7 +408,7 @@ int lbk_quantise(lbk_context* ctx, const double* g, const double* h, int64_t ldg
     lbk::Scratch s(ctx, stream);
     lbk::Quantise(ctx, s, g, h, ldg, row_offset, n_local_rows, n_outputs, seed, reinterpret_cast<int2*>(gpair),
                   reinterpret_cast<lbk::GPairI64*>(root_sums), reinterpret_cast<lbk::QuantParams*>(scale),
-                  s.alloc<int>(2), stream);
+                  max_abs ? max_abs : s.alloc<int>(2), stream);
   });
 }
 
@@ -470,7 +470,7 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
     lv.row_ptr              = row_ptr;
     lv.gpair                = a->mode == 0 ? static_cast<const int2*>(gp) : nullptr;
     lv.gpair_f              = a->mode == 1 ? static_cast<const float2*>(gp) : nullptr;
-    lv.max_abs              = nullptr;
+    lv.max_abs              = a->host_buffers ? nullptr : reinterpret_cast<const int*>(a->max_abs);
     lv.row_index            = row_index;
     lv.seg                  = seg;
     lv.n_nodes              = a->n_nodes;

@@ -62,7 +62,9 @@ struct HistParams {
   int n_nodes;
   const int32_t* chunk_off;  // [n_nodes+1]
   const int32_t* part_off;   // [n_nodes+1] partial-sum slots before each node (nodes with > 1 chunk); may be null
-  const int32_t* plan;       // [0] rows per chunk, [1] total chunks, [3] rows between flushes, [6] slots usable
+  const int32_t* multi;      // [plan[5]] the nodes that were cut into several chunks; may be null
+  const int32_t* plan;       // [0] rows per chunk, [1] total chunks, [3] rows between flushes, [5] nodes in
+                             // `multi`, [6] slots usable
   unsigned int* ticket;
   void* partial;             // partial-sum slots: [slot][2][mb * 32] of the accumulator type; may be null
   void* out;
@@ -149,14 +151,15 @@ constexpr int kOverheadMulti  = 5000;  // the same for clear + partial store + i
 __global__ void __launch_bounds__(1024)
   k_hist_plan(const int32_t* __restrict__ seg, const int32_t* __restrict__ slot_of_node, int n_nodes, int GK,
               int resident, const int* __restrict__ max_abs, long long slot_capacity, int force, int32_t* __restrict__ chunk_off,
-              int32_t* __restrict__ part_off, int32_t* __restrict__ plan, unsigned int* __restrict__ ticket)
+              int32_t* __restrict__ part_off, int32_t* __restrict__ multi, int32_t* __restrict__ plan,
+              unsigned int* __restrict__ ticket)
 {
   __shared__ long long red[32];
   __shared__ int red_max[32];
   __shared__ long long wsum[32];
   __shared__ long long carry;
   __shared__ long long total_s;
-  __shared__ int ch_s, cap_s, mode_s;
+  __shared__ int ch_s, cap_s, mode_s, multi_s;
   __shared__ double cand_cost[kPlanCandidates];
   __shared__ int cand_ch[kPlanCandidates];
   __shared__ int cand_fit[kPlanCandidates];
@@ -182,6 +185,7 @@ __global__ void __launch_bounds__(1024)
     // chunks that can use partial-sum slots never need a flush in the middle
     cap_s = safe >= (1 << 30) ? (1 << 30) : (safe & ~(kTileRows - 1));
     carry = 0;
+    multi_s = 0;
     chunk_off[0] = 0;
     if (part_off) part_off[0] = 0;
   }
@@ -261,6 +265,7 @@ __global__ void __launch_bounds__(1024)
       const int r   = rows_of(j);
       const int nch = r > 0 ? (r + ch - 1) / ch : 0;
       c             = nch + (nch > 1 ? (static_cast<long long>(nch) << 32) : 0);
+      if (nch > 1 && multi) multi[atomicAdd(&multi_s, 1)] = j;
     }
     long long incl = c;
     for (int off = 1; off < 32; off <<= 1) {
@@ -291,6 +296,7 @@ __global__ void __launch_bounds__(1024)
   if (tid == 0) {
     plan[0] = ch;
     plan[1] = static_cast<int>(carry & 0xffffffffll);
+    plan[5] = multi_s;
     plan[6] = mode_s;
     *ticket = 0;
   }
@@ -610,11 +616,11 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
 }
 
 // Adds up the partial-sum slots of every node that was cut into several chunks and adds the
-// totals to the (zeroed) histogram.  grid = (nodes * tickets per chunk, kSumSplits, kSumParts): a
-// block handles one (node, group set, output), 1/kSumSplits of its histogram words and
-// 1/kSumParts of its slots; a thread reads 16 bytes of every slot of its part (four neighbouring
-// features of one bin), four slots in flight, and finishes with one pair of 64-bit atomics per
-// feature (kSumParts blocks meet in every word).
+// totals to the (zeroed) histogram.  A work item is one (node of the `multi` list, group set,
+// output), 1/kSumSplits of its histogram words and 1/kSumParts of its slots; the blocks of a
+// fixed-size grid take items in turn (no items, no work).  A thread reads 16 bytes of every slot of
+// the item's part (four neighbouring features of one bin), four slots in flight, and finishes with
+// one pair of 64-bit atomics per feature (kSumParts items meet in every word).
 constexpr int kSumSplits  = 16;
 constexpr int kSumParts   = 8;
 constexpr int kSumThreads = 256;
@@ -628,53 +634,58 @@ __global__ void __launch_bounds__(kSumThreads)
   using out_t  = typename A::out_t;
   constexpr int kCols = kGroup * W;
   if (p.plan[6] == 0) return;
-  const int GP = (p.G + W - 1) / W;
-  const int k  = blockIdx.x % p.K;
-  const int gp = (blockIdx.x / p.K) % GP;
-  const int j  = blockIdx.x / (p.K * GP);
-  const int nchunks = p.chunk_off[j + 1] - p.chunk_off[j];
-  if (nchunks <= 1) return;
-  const int per = (nchunks + kSumParts - 1) / kSumParts;
-  const int qb  = blockIdx.z * per, qe = min(nchunks, qb + per);
-  if (qb >= qe) return;
-  const int slot       = p.slot_of_node ? p.slot_of_node[j] : j;
+  const int GP         = (p.G + W - 1) / W;
+  const long long items = static_cast<long long>(p.plan[5]) * GP * p.K * kSumSplits * kSumParts;
   const int hist_words = p.mb * kCols;
   const int n4         = hist_words >> 2;
   const smem_t* part   = static_cast<const smem_t*>(p.partial);
   const size_t stride  = static_cast<size_t>(hist_words) * 2;
-  const size_t first   = (static_cast<size_t>(p.part_off[j]) * p.K + k) * GP + gp;
   const size_t step    = static_cast<size_t>(p.K) * GP;
-  out_t* onode         = static_cast<out_t*>(p.out) + (static_cast<int64_t>(slot) * p.K + k) * p.B;
-  for (int e4 = blockIdx.y * kSumThreads + threadIdx.x; e4 < n4; e4 += kSumSplits * kSumThreads) {
-    typename A::wide_t sg[4], sh[4];
+  for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+    const int zpart = static_cast<int>(item % kSumParts);
+    const int split = static_cast<int>((item / kSumParts) % kSumSplits);
+    const long long t = item / (kSumParts * kSumSplits);
+    const int k  = static_cast<int>(t % p.K);
+    const int gp = static_cast<int>((t / p.K) % GP);
+    const int j  = p.multi[t / (static_cast<long long>(p.K) * GP)];
+    const int nchunks = p.chunk_off[j + 1] - p.chunk_off[j];
+    const int per = (nchunks + kSumParts - 1) / kSumParts;
+    const int qb  = zpart * per, qe = min(nchunks, qb + per);
+    if (qb >= qe) continue;
+    const int slot     = p.slot_of_node ? p.slot_of_node[j] : j;
+    const size_t first = (static_cast<size_t>(p.part_off[j]) * p.K + k) * GP + gp;
+    out_t* onode       = static_cast<out_t*>(p.out) + (static_cast<int64_t>(slot) * p.K + k) * p.B;
+    for (int e4 = split * kSumThreads + threadIdx.x; e4 < n4; e4 += kSumSplits * kSumThreads) {
+      typename A::wide_t sg[4], sh[4];
 #pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) sg[c4] = sh[c4] = 0;
-    for (int q0 = qb; q0 < qe; q0 += 4) {
-      int4 vg[4], vh[4];
+      for (int c4 = 0; c4 < 4; ++c4) sg[c4] = sh[c4] = 0;
+      for (int q0 = qb; q0 < qe; q0 += 4) {
+        int4 vg[4], vh[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (q0 + u < qe) {
-          const smem_t* src = part + (first + (q0 + u) * step) * stride;
-          vg[u] = __ldcg(reinterpret_cast<const int4*>(src) + e4);
-          vh[u] = __ldcg(reinterpret_cast<const int4*>(src + hist_words) + e4);
-        } else {
-          vg[u] = vh[u] = make_int4(0, 0, 0, 0);
+        for (int u = 0; u < 4; ++u) {
+          if (q0 + u < qe) {
+            const smem_t* src = part + (first + (q0 + u) * step) * stride;
+            vg[u] = __ldcg(reinterpret_cast<const int4*>(src) + e4);
+            vh[u] = __ldcg(reinterpret_cast<const int4*>(src + hist_words) + e4);
+          } else {
+            vg[u] = vh[u] = make_int4(0, 0, 0, 0);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          sg[0] += A::widen(vg[u].x); sg[1] += A::widen(vg[u].y); sg[2] += A::widen(vg[u].z); sg[3] += A::widen(vg[u].w);
+          sh[0] += A::widen(vh[u].x); sh[1] += A::widen(vh[u].y); sh[2] += A::widen(vh[u].z); sh[3] += A::widen(vh[u].w);
         }
       }
+      const int bin = (e4 * 4) / kCols, w0 = (e4 * 4) % kCols;
+      const int f0  = (gp * W) * kGroup + (W == 1 ? w0 : 16 * ((w0 >> 3) & 3) + 8 * (w0 >> 5) + (w0 & 7));
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        sg[0] += A::widen(vg[u].x); sg[1] += A::widen(vg[u].y); sg[2] += A::widen(vg[u].z); sg[3] += A::widen(vg[u].w);
-        sh[0] += A::widen(vh[u].x); sh[1] += A::widen(vh[u].y); sh[2] += A::widen(vh[u].z); sh[3] += A::widen(vh[u].w);
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const int f = f0 + c4;
+        if (f >= p.F) continue;
+        const int fbeg = p.row_ptr[f];
+        if (bin < p.row_ptr[f + 1] - fbeg && (sg[c4] != 0 || sh[c4] != 0)) A::add_wide(onode + fbeg + bin, sg[c4], sh[c4]);
       }
-    }
-    const int bin = (e4 * 4) / kCols, w0 = (e4 * 4) % kCols;
-    const int f0  = (gp * W) * kGroup + (W == 1 ? w0 : 16 * ((w0 >> 3) & 3) + 8 * (w0 >> 5) + (w0 & 7));
-#pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) {
-      const int f = f0 + c4;
-      if (f >= p.F) continue;
-      const int fbeg = p.row_ptr[f];
-      if (bin < p.row_ptr[f + 1] - fbeg && (sg[c4] != 0 || sh[c4] != 0)) A::add_wide(onode + fbeg + bin, sg[c4], sh[c4]);
     }
   }
 }
@@ -842,6 +853,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   // partial-sum slots for nodes that are cut into several chunks: ten per resident block
   long long slot_capacity = 0;
   p.part_off = nullptr;
+  p.multi    = nullptr;
   p.partial  = nullptr;
   int force = -1;
   if (const char* e = getenv("LBK_HIST_FORCE")) force = atoi(e);
@@ -850,20 +862,24 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
     slot_capacity           = 10ll * hl.grid;
     const size_t slot_bytes = static_cast<size_t>(p.mb) * kGroup * hl.width * 8;
     int32_t* part_off       = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes) + 1);
+    int32_t* multi          = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes));
     p.part_off              = part_off;
+    p.multi                 = multi;
     p.partial               = s.alloc<unsigned char>(slot_bytes * slot_capacity);
     k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, tickets_per_chunk, hl.grid,
-                                        lv.float_mode ? nullptr : max_abs, slot_capacity, force, chunk_off, part_off, plan, p.ticket);
+                                        lv.float_mode ? nullptr : max_abs, slot_capacity, force, chunk_off, part_off,
+                                        multi, plan, p.ticket);
   } else {
     k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, tickets_per_chunk, hl.grid,
-                                        lv.float_mode ? nullptr : max_abs, 0, -1, chunk_off, nullptr, plan, p.ticket);
+                                        lv.float_mode ? nullptr : max_abs, 0, -1, chunk_off, nullptr, nullptr, plan,
+                                        p.ticket);
   }
   LBK_LAUNCH_CHECK();
   if (ctx->profile) LBK_CUDA(cudaEventRecord(ctx->ev_start, stream));
   hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
   LBK_LAUNCH_CHECK();
   if (p.partial) {
-    hl.sum<<<dim3(static_cast<unsigned>(lv.n_nodes) * tickets_per_chunk, kSumSplits, kSumParts), kSumThreads, 0, stream>>>(p);
+    hl.sum<<<ctx->sm_count * 8, kSumThreads, 0, stream>>>(p);
     LBK_LAUNCH_CHECK();
   }
   if (ctx->profile) {
@@ -931,8 +947,8 @@ namespace {
 
 constexpr int kNoAllocMaxNodes    = LBK_NOALLOC_MAX_NODES;
 constexpr int kNoAllocMaxFeatures = LBK_NOALLOC_MAX_FEATURES;
-constexpr int kNoAllocPlanOffset  = kNoAllocMaxNodes + 4;   // chunk offsets first, then plan[4], max_abs[2]
-constexpr int kNoAllocInts        = kNoAllocPlanOffset + 8;
+constexpr int kNoAllocPlanOffset  = kNoAllocMaxNodes + 4;   // chunk offsets first, then plan[8], max_abs[2]
+constexpr int kNoAllocInts        = kNoAllocPlanOffset + 12;
 
 static __device__ __align__(256) int32_t g_hist_scratch[kNoAllocInts];
 
@@ -976,7 +992,7 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     int32_t* scratch    = HistScratchAddress(device);
     int32_t* chunk_off  = scratch;
     int32_t* plan       = scratch + kNoAllocPlanOffset;
-    int* max_abs        = reinterpret_cast<int*>(plan + 4);
+    int* max_abs        = reinterpret_cast<int*>(plan + 8);
 
     const int F = a->n_features, K = a->n_outputs, B = a->total_bins;
     int32_t rp[kNoAllocMaxFeatures + 1];
@@ -1013,9 +1029,11 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     const HistLaunch hl  = PickHistKernel(smem_path, a->bin_bytes, float_mode, p.G, sm_count);
 
     // the array keeps what the previous call left: clear the words that accumulate
-    LBK_CUDA(cudaMemsetAsync(plan, 0, sizeof(int32_t) * 8, stream));
+    LBK_CUDA(cudaMemsetAsync(plan, 0, sizeof(int32_t) * 12, stream));
     LBK_CUDA(cudaMemsetAsync(a->hist, 0, sizeof(GPairI64) * a->n_nodes * K * B, stream));
-    if (!float_mode) {
+    if (!float_mode && a->max_abs != nullptr) {
+      max_abs = const_cast<int*>(reinterpret_cast<const int*>(a->max_abs));
+    } else if (!float_mode) {
       const int64_t n = a->n_rows * K;
       if (n > 0) {
         k_max_abs<<<sm_count * 8, 256, 0, stream>>>(static_cast<const int2*>(p.gpair), n, max_abs);
@@ -1024,10 +1042,11 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     }
     // no partial-sum slots here (they would have to be allocated): nodes cut into chunks flush with atomics
     p.part_off = nullptr;
+    p.multi    = nullptr;
     p.partial  = nullptr;
       k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, (p.G + hl.width - 1) / hl.width * p.K, hl.grid,
                                         float_mode ? nullptr : max_abs, 0,
-                                        -1, chunk_off, nullptr, plan, p.ticket);
+                                        -1, chunk_off, nullptr, nullptr, plan, p.ticket);
     LBK_LAUNCH_CHECK();
     hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
     LBK_LAUNCH_CHECK();

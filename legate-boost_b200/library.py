@@ -66,7 +66,7 @@ class HistogramArgs(C.Structure):
         ("gpair", C.c_void_p), ("gpair_f32", C.c_void_p), ("n_outputs", C.c_int32),
         ("row_index", C.c_void_p), ("seg", C.c_void_p), ("n_nodes", C.c_int32),
         ("mode", C.c_int32), ("hist", C.c_void_p), ("stream", C.c_void_p),
-        ("host_buffers", C.c_int32),
+        ("host_buffers", C.c_int32), ("max_abs", C.c_void_p),
     ]
 
 
@@ -112,7 +112,7 @@ def load():
             lib.lbk_bin_matrix_bytes.restype = C.c_size_t
             lib.lbk_quantise.argtypes = [
                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int,
-                C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+                C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
             lib.lbk_group_rows.argtypes = [
                 C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
             _lib = lib

@@ -49,8 +49,9 @@ def to_padded_rows(bins_row_major):
     return out
 
 
-def quantise(g, h, seed, row_offset=0, ctx=None):
-    """int32 pairs (N,K,2), root sums int64 (K,2), scale float64 (4,)."""
+def quantise(g, h, seed, row_offset=0, ctx=None, with_max_abs=False):
+    """int32 pairs (N,K,2), root sums int64 (K,2), scale float64 (4,); with ``with_max_abs`` also the
+    largest |grad| and |hess| of the pairs, int32 (2,), which ``histogram`` accepts."""
     ctx = ctx or L.context(g.device.index)
     g = g.contiguous()
     h = h.contiguous()
@@ -58,9 +59,13 @@ def quantise(g, h, seed, row_offset=0, ctx=None):
     gpair = torch.empty((N, K, 2), dtype=torch.int32, device=g.device)
     root = torch.empty((K, 2), dtype=torch.int64, device=g.device)
     scale = torch.empty(4, dtype=torch.float64, device=g.device)
+    max_abs = torch.empty(2, dtype=torch.int32, device=g.device) if with_max_abs else None
     with torch.cuda.device(g.device):
         ctx.check(ctx.lib.lbk_quantise(ctx.handle, g.data_ptr(), h.data_ptr(), K, row_offset, N, K, int(seed),
-                                       gpair.data_ptr(), root.data_ptr(), scale.data_ptr(), _stream_ptr()))
+                                       gpair.data_ptr(), root.data_ptr(), scale.data_ptr(),
+                                       max_abs.data_ptr() if with_max_abs else None, _stream_ptr()))
+    if with_max_abs:
+        return gpair, root, scale, max_abs
     return gpair, root, scale
 
 
@@ -76,7 +81,8 @@ def group_rows(node_of_row, node_begin, n_nodes, ctx=None):
     return row_index, seg
 
 
-def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=None, ctx=None, host=False):
+def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=None, ctx=None, host=False,
+              max_abs=None):
     """Histogram [n_nodes, K, B, 2] (int64 for mode 0, float64 for mode 1) of node-grouped rows.
 
     ``host=True`` takes CPU tensors and lets the library do the copies (the end-to-end path)."""
@@ -101,5 +107,6 @@ def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=Non
     a.hist = hist.data_ptr()
     a.stream = _stream_ptr()
     a.host_buffers = 1 if host else 0
+    a.max_abs = max_abs.data_ptr() if max_abs is not None else None
     ctx.check(ctx.lib.lbk_histogram(ctx.handle, C.byref(a)))
     return hist
