@@ -313,8 +313,8 @@ def run_hist(args):
         kms = ksum / args.steps
         achieved = algorithmic_bytes(n_rows) / (kms * 1e-3) / 1e9
         # DRAM traffic of one launch, from the ncu capture of the 2 M-row case summarised in
-        # profiles/k_hist_config2_ncu_full.md (363.1 B read per row, 55.5 MB written), scaled by rows
-        traffic = n_rows * 363.1 + 55.5e6 if mode == 0 else None
+        # profiles/k_hist_config2_ncu_full.md (140.2 B read per row, 15.3 MB written), scaled by rows
+        traffic = n_rows * 140.2 + 15.3e6 if mode == 0 else None
         line = {
             "metric": "histogram rows*features/s", "value": value, "unit": "row-features/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
@@ -326,7 +326,7 @@ def run_hist(args):
                                                             ", NCCL all-reduce of the level's histograms" if world > 1 else ""),
                        "l2": "160 MB flush buffer written between timed steps; inputs (1.4 GB) exceed L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": which, "kernel": "k_hist", "kernel_ms": kms},
+                         "traffic": traffic, "peak_source": which, "kernel": "k_hist_smem", "kernel_ms": kms},
             "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * args.steps,
         }
         if not args.no_cpu and world >= 1:
