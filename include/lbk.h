@@ -115,6 +115,12 @@ typedef struct lbk_build_tree_args {
                                its split was evaluated */
   int32_t trace_nodes;
   int32_t* out_total_bins;  /* host pointer: B */
+  /* Optional (NULL to skip): the node in which each local row of X ends, int32 [n_local_rows],
+   * device (host if host_buffers).  It is the node lbk_predict's walk of this tree reaches for the
+   * row (read off the binned matrix while it still exists), so leaf_value[out_leaf[i]] is the
+   * tree's prediction for training row i without a second pass over X.  No counterpart in the
+   * reference, whose callers run PREDICT on the training matrix after every BUILD_TREE. */
+  int32_t* out_leaf;
 } lbk_build_tree_args;
 
 int lbk_build_tree(lbk_context* ctx, const lbk_build_tree_args* args);

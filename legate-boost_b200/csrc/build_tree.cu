@@ -17,6 +17,27 @@
 namespace lbk {
 namespace {
 
+// The node each row ends in, read off the binned matrix: "x <= split value" is "bin <= split bin"
+// because a split value is one of the feature's proposals (the repartition relies on the same
+// fact), so this is the walk the predict kernel does on X, on a quarter of the bytes (float32 X).
+// One thread per row; the row's bin bytes (one or two lines) stay in L1 between the levels.
+template <typename BinT>
+__global__ void __launch_bounds__(256)
+  k_leaf_of_row(const BinT* __restrict__ bins, int64_t pitch, int64_t n_rows, const int32_t* __restrict__ feature,
+                const int32_t* __restrict__ split_bin, int max_depth, int32_t* __restrict__ leaf)
+{
+  const int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (row >= n_rows) return;
+  const BinT* b = bins + row * pitch;
+  int node      = 0;
+  for (int d = 0; d < max_depth; ++d) {
+    const int f = __ldg(feature + node);
+    if (f < 0) break;
+    node = 2 * node + 1 + (static_cast<int>(b[f]) > __ldg(split_bin + node) ? 1 : 0);
+  }
+  leaf[row] = node;
+}
+
 template <typename T>
 void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t stream)
 {
@@ -245,6 +266,20 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
   }
 
   WriteHessian(tree.node_sums, qp, hessian, static_cast<int64_t>(M) * K, stream);
+  if (a.out_leaf != nullptr && N > 0) {
+    int32_t* d_leaf = a.host_buffers ? s.alloc<int32_t>(static_cast<size_t>(N)) : a.out_leaf;
+    const int64_t pitch = static_cast<int64_t>((F + kGroup - 1) / kGroup) * kGroup;
+    const unsigned blocks = static_cast<unsigned>((N + 255) / 256);
+    if (bin_bytes == 1)
+      k_leaf_of_row<uint8_t><<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(bins), pitch, N, tree.feature,
+                                                         tree.split_bin, D, d_leaf);
+    else
+      k_leaf_of_row<uint16_t><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(bins), pitch, N, tree.feature,
+                                                          tree.split_bin, D, d_leaf);
+    LBK_LAUNCH_CHECK();
+    if (a.host_buffers)
+      LBK_CUDA(cudaMemcpyAsync(a.out_leaf, d_leaf, sizeof(int32_t) * N, cudaMemcpyDeviceToHost, stream));
+  }
   if (a.trace_node_sums)
     LBK_CUDA(cudaMemcpyAsync(a.trace_node_sums, tree.node_sums, sizeof(GPairI64) * M * K, cudaMemcpyDeviceToDevice, stream));
   if (a.host_buffers) {

@@ -44,7 +44,7 @@ class BuildTreeArgs(C.Structure):
         ("gain", C.c_void_p), ("hessian", C.c_void_p),
         ("stream", C.c_void_p), ("host_buffers", C.c_int32),
         ("trace_node_sums", C.c_void_p), ("trace_hist", C.c_void_p), ("trace_nodes", C.c_int32),
-        ("out_total_bins", C.POINTER(C.c_int32)),
+        ("out_total_bins", C.POINTER(C.c_int32)), ("out_leaf", C.c_void_p),
     ]
 
 

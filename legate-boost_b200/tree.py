@@ -41,10 +41,17 @@ def _row_layout(n_local: int):
     return int(sum(sizes[: dist.get_rank()])), int(sum(sizes))
 
 
+def _tensor_key(t: torch.Tensor):
+    """Identity of a tensor's contents as far as torch can tell: storage, view and version counter
+    (every in-place change bumps the counter)."""
+    return (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, t.device, t._version)
+
+
 def build_tree_arrays(X, g, h, *, max_depth, split_samples, seed, l1=0.0, l2=1.0, min_split_gain=0.0,
-                      feature_set=None, row_offset=None, dataset_rows=None, trace_nodes=0, ctx=None):
+                      feature_set=None, row_offset=None, dataset_rows=None, trace_nodes=0, ctx=None,
+                      want_leaf=False):
     """Run ``lbk_build_tree`` on device tensors.  Returns a dict with the five tree arrays (and the
-    optional traces)."""
+    optional traces; with ``want_leaf`` also ``leaf``: the node every local row ends in)."""
     assert X.is_cuda and g.is_cuda and h.is_cuda, "inputs must be CUDA tensors (no CPU fallback)"
     if g.dim() == 1:
         g, h = g[:, None], h[:, None]
@@ -90,6 +97,9 @@ def build_tree_arrays(X, g, h, *, max_depth, split_samples, seed, l1=0.0, l2=1.0
     if trace_nodes > 0:
         trace = torch.zeros((trace_nodes, K, F * split_samples, 2), dtype=torch.int64, device=dev)
         a.trace_hist, a.trace_nodes = trace.data_ptr(), trace_nodes
+    if want_leaf:
+        out["leaf"] = torch.empty((N,), dtype=torch.int32, device=dev)
+        a.out_leaf = out["leaf"].data_ptr()
     with torch.cuda.device(dev):
         ctx.check(ctx.lib.lbk_build_tree(ctx.handle, C.byref(a)))
     out["B"] = B.value
@@ -227,12 +237,17 @@ class Tree(BaseModel):
         out = build_tree_arrays(
             X, g, h, max_depth=self.max_depth, split_samples=self.split_samples, seed=seed,
             l1=self.l1_regularization, l2=self.l2_regularization, min_split_gain=self.min_split_gain,
-            feature_set=feature_set)
+            feature_set=feature_set, want_leaf=True)
         self.leaf_value = out["leaf_value"]
         self.feature = out["feature"]
         self.split_value = out["split_value"]
         self.gain = out["gain"]
         self.hessian = out["hessian"]
+        # The builder also says where every training row ended.  A boosting driver asks for the
+        # predictions on the training matrix right after fit: the first predict() on the very same,
+        # unmodified tensor is then a gather of leaf values instead of a second pass over X.  The
+        # record is used once and dropped (it is one int32 per row).
+        self._fit_rows = (_tensor_key(X), out["leaf"])
         return self
 
     def clear(self) -> None:
@@ -243,6 +258,9 @@ class Tree(BaseModel):
         raise NotImplementedError("the UPDATE_TREE task is outside the tree-building hot path")
 
     def predict(self, X: torch.Tensor) -> torch.Tensor:
+        fit_rows, self._fit_rows = getattr(self, "_fit_rows", None), None
+        if fit_rows is not None and fit_rows[0] == _tensor_key(X):
+            return self.leaf_value.index_select(0, fit_rows[1])
         return Tree.batch_predict([self], X)
 
     @staticmethod
@@ -277,6 +295,7 @@ class Tree(BaseModel):
         return recurse_print(0, 0)
 
     def __mul__(self, scalar: Any) -> "Tree":
+        self._fit_rows = None  # the record of the training rows is not worth copying
         new = copy.deepcopy(self)
         new.leaf_value = new.leaf_value * scalar
         return new

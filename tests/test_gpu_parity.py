@@ -384,3 +384,27 @@ def test_bad_arguments_are_errors(lb):
         build_tree_arrays(X, g, g, max_depth=2, split_samples=5000, seed=0, row_offset=0, dataset_rows=10)
     with pytest.raises(lb.library.LbkError):
         build_tree_arrays(X, g, g, max_depth=2, split_samples=16, seed=0, row_offset=5, dataset_rows=10)
+
+
+def test_first_predict_on_the_training_matrix_uses_the_leaf_record(lb):
+    """fit() keeps the node every training row ended in; the first predict() on the same, unmodified
+    tensor gathers leaf values from it.  It must equal the walk over X bit for bit, must be used
+    once, and must not be used after the tensor changed."""
+    rs = np.random.RandomState(3)
+    for dtype, K, F, S in ((np.float32, 1, 40, 256), (np.float64, 3, 7, 500)):
+        X = dev(rs.random((3000, F)).astype(dtype))
+        g = dev(rs.normal(size=(3000, K)))
+        h = dev(rs.random((3000, K)) + 0.1)
+        t = lb.Tree(max_depth=6, split_samples=S).set_random_state(np.random.RandomState(1)).fit(X, g, h)
+        assert t._fit_rows is not None
+        want = lb.Tree.batch_predict([t], X)
+        got = t.predict(X)
+        assert t._fit_rows is None
+        assert torch.equal(got, want)
+        assert torch.equal(t.predict(X), want)           # the walk over X this time
+        t.fit(X, g, h)
+        X[0, 0] += 1.0                                   # in-place change: the record is stale
+        want = lb.Tree.batch_predict([t], X)
+        assert torch.equal(t.predict(X), want)
+    stump = lb.Tree(max_depth=0).set_random_state(np.random.RandomState(1)).fit(X, g, h)
+    assert torch.equal(stump.predict(X), lb.Tree.batch_predict([stump], X))
