@@ -15,7 +15,7 @@ from typing import List, Optional
 import numpy as np
 import torch
 
-from .tree import Tree
+from .tree import Tree, _row_layout
 
 
 def _all_sum(t: torch.Tensor) -> torch.Tensor:
@@ -127,11 +127,14 @@ class _LBBase:
         self.model_init_ = self._obj.init(y, self.init == "average")
         self.train_metric_: List[float] = []
         train_pred = self.model_init_.repeat(X.shape[0], 1)
+        layout = _row_layout(X.shape[0])  # this rank's block of rows: the same for every tree
         for i in range(self.n_estimators):
             g, h = self._obj.gradient(y, self._obj.transform(train_pred))
             g = g * self.learning_rate
             h = torch.clamp(h, min=1e-8)
-            tree = deepcopy(self.base_models[i % len(self.base_models)]).set_random_state(self.random_state_).fit(X, g, h)
+            tree = deepcopy(self.base_models[i % len(self.base_models)]).set_random_state(self.random_state_)
+            tree.row_layout = layout
+            tree.fit(X, g, h)
             self.models_.append(tree)
             train_pred += tree.predict(X)
             if self.verbose:

@@ -62,7 +62,7 @@ def build_tree_arrays(X, g, h, *, max_depth, split_samples, seed, l1=0.0, l2=1.0
     h = h.contiguous()
     N, F = X.shape
     K = g.shape[1]
-    ctx = ctx or (L.init_distributed(X.device.index) if row_offset is None else L.context(X.device.index))
+    ctx = ctx or L.init_distributed(X.device.index)
     if row_offset is None:
         row_offset, dataset_rows = _row_layout(N)
     M = 2 ** (max_depth + 1) - 1
@@ -234,10 +234,13 @@ class Tree(BaseModel):
             n_sampled = max(1, int(X.shape[1] * self.feature_fraction))
             mask[self.random_state.choice(X.shape[1], n_sampled, False)] = True
             feature_set = torch.from_numpy(mask)
+        # A driver that fits many trees on the same row blocks can set `row_layout` = (row_offset,
+        # dataset_rows) once; otherwise every fit asks the other ranks for their row counts.
+        row_offset, dataset_rows = getattr(self, "row_layout", None) or (None, None)
         out = build_tree_arrays(
             X, g, h, max_depth=self.max_depth, split_samples=self.split_samples, seed=seed,
             l1=self.l1_regularization, l2=self.l2_regularization, min_split_gain=self.min_split_gain,
-            feature_set=feature_set, want_leaf=True)
+            feature_set=feature_set, want_leaf=True, row_offset=row_offset, dataset_rows=dataset_rows)
         self.leaf_value = out["leaf_value"]
         self.feature = out["feature"]
         self.split_value = out["split_value"]
