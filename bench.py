@@ -248,9 +248,7 @@ def run_hist(args):
 
     def step():
         stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, mode=mode, hist=hist, ctx=ctx,
-                         max_abs=max_abs if mode == 0 else None)
-        if world > 1:
-            dist.all_reduce(hist)
+                         max_abs=max_abs if mode == 0 else None, all_reduce=world > 1)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -292,13 +290,15 @@ def run_hist(args):
         hh = torch.empty(hist.shape, dtype=hist.dtype).pin_memory()
         n_e2e = max(2, min(args.steps, 5))
         for _ in range(2):
-            stages.histogram(hb, hrp, hgp, hidx, hseg, HIST_FEATURES, mode=mode, hist=hh, ctx=ctx, host=True)
+            stages.histogram(hb, hrp, hgp, hidx, hseg, HIST_FEATURES, mode=mode, hist=hh, ctx=ctx, host=True,
+                             all_reduce=world > 1)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         t0 = time.perf_counter()
         for _ in range(n_e2e):
-            stages.histogram(hb, hrp, hgp, hidx, hseg, HIST_FEATURES, mode=mode, hist=hh, ctx=ctx, host=True)
+            stages.histogram(hb, hrp, hgp, hidx, hseg, HIST_FEATURES, mode=mode, hist=hh, ctx=ctx, host=True,
+                             all_reduce=world > 1)
         torch.cuda.synchronize()
         dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
         if world > 1:

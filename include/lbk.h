@@ -211,6 +211,9 @@ typedef struct lbk_histogram_args {
   int32_t host_buffers;
   const int32_t* max_abs;   /* mode 0, optional: device int32[2] = largest |grad|, |hess| in gpair (the
                                call bounds its 32-bit partial sums with it); NULL = found by the call */
+  int32_t all_reduce;       /* 1: hist is summed over the ranks of the context's communicator before
+                               the call returns (the nodes are cut into parts so that the sum of
+                               one part travels while the next part is built) */
 } lbk_histogram_args;
 
 int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* args);

@@ -224,10 +224,8 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
       lv.slot_of_node         = slot_of_node;
       lv.out                  = target;
       lv.float_mode           = false;
-      if (N > 0) BuildHistogram(ctx, s, lv, stream);
-
-      // sum over ranks (reference: :1107-1113 reduces the whole batch; only built nodes here)
-      AllReduce(ctx, target, static_cast<size_t>(n_slots) * node_elems * 2, LBK_I64, LBK_SUM, stream);
+      // build + sum over ranks (reference: :1107-1113 reduces the whole batch; only built nodes here)
+      BuildHistogramAllReduce(ctx, s, lv, n_slots, n_slots != n_nodes, stream);
 
       const GPairI64* parent_hist = nullptr;
       int parent_begin            = 0;
@@ -513,7 +511,8 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
     lv.slot_of_node         = nullptr;
     lv.out                  = hist;
     lv.float_mode           = a->mode == 1;
-    lbk::BuildHistogram(ctx, s, lv, stream);
+    if (a->all_reduce) lbk::BuildHistogramAllReduce(ctx, s, lv, a->n_nodes, false, stream);
+    else lbk::BuildHistogram(ctx, s, lv, stream);
     if (a->host_buffers)
       LBK_CUDA(cudaMemcpyAsync(a->hist, hist, hist_bytes, cudaMemcpyDeviceToHost, stream));
     lbk::CheckDeviceStatus(ctx, stream);

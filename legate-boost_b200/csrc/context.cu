@@ -195,6 +195,10 @@ void lbk_context_destroy(lbk_context* ctx)
   if (ctx->owns_nccl && ctx->nccl_comm && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
+  if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);
+  for (cudaEvent_t e : ctx->ev_part)
+    if (e) cudaEventDestroy(e);
+  if (ctx->ev_comm_done) cudaEventDestroy(ctx->ev_comm_done);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   delete ctx;

@@ -835,7 +835,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
-  const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, p.G, ctx->sm_count);
+  const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, p.G, ctx->sm_count - (lv.reserve_sms < ctx->sm_count ? lv.reserve_sms : 0));
 
   const int* max_abs = lv.max_abs;
   if (!lv.float_mode && max_abs == nullptr) {
@@ -894,6 +894,74 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
     LBK_CUDA(cudaStreamSynchronize(stream));
     fprintf(stderr, "hist plan: ch %d chunks %d safe %d mode %d cand %d grid %d\n", hp[0], hp[1], hp[3], hp[6], hp[7], hl.grid);
   }
+}
+
+void BuildHistogramAllReduce(lbk_context* ctx, Scratch& s, const HistLevel& lv, int n_slots, bool pairs,
+                             cudaStream_t stream)
+{
+  const size_t slot_words = static_cast<size_t>(lv.K) * lv.B * 2;  // 64-bit words per slot
+  const lbk_dtype dtype   = lv.float_mode ? LBK_F64 : LBK_I64;
+  if (ctx->n_ranks <= 1) {
+    if (lv.n_rows > 0) BuildHistogram(ctx, s, lv, stream);
+    return;
+  }
+  // Parts: only with NCCL (a callback communicator is not known to be stream-safe), only when every
+  // part still has a ticket for every resident block, and only when there is something to hide.
+  constexpr int kReserve = 20;  // SMs left to the all-reduce kernel
+  const int G            = (lv.F + kGroup - 1) / kGroup;
+  const bool smem_path   = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
+  const int width        = smem_path && G >= 2 ? 2 : 1;
+  const long long tickets = static_cast<long long>(lv.n_nodes) / (pairs ? 2 : 1) * ((G + width - 1) / width) * lv.K;
+  const int resident     = (ctx->sm_count - kReserve) * (width == 2 ? 1 : 2);
+  int parts              = static_cast<int>(tickets / (resident > 0 ? resident : 1));
+  if (parts > 4) parts = 4;
+  if (ctx->cb != nullptr || ctx->nccl_comm == nullptr || !smem_path || lv.n_rows <= 0 ||
+      static_cast<size_t>(n_slots) * slot_words * 8 < (size_t{8} << 20))
+    parts = 1;
+  if (parts <= 1) {
+    if (lv.n_rows > 0) BuildHistogram(ctx, s, lv, stream);
+    AllReduce(ctx, lv.out, static_cast<size_t>(n_slots) * slot_words, dtype, LBK_SUM, stream);
+    return;
+  }
+  if (ctx->comm_stream == nullptr) {
+    int lo = 0, hi = 0;
+    LBK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    LBK_CUDA(cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, hi));
+    for (cudaEvent_t& e : ctx->ev_part) LBK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    LBK_CUDA(cudaEventCreateWithFlags(&ctx->ev_comm_done, cudaEventDisableTiming));
+  }
+  const int unit = pairs ? 2 : 1;  // nodes per slot
+  // the optional timing covers the histogram kernels of all parts (they run back to back)
+  const bool timed = ctx->profile;
+  ctx->profile     = false;
+  if (timed) LBK_CUDA(cudaEventRecord(ctx->ev_start, stream));
+  for (int i = 0; i < parts; ++i) {
+    // node range of the part, on slot boundaries
+    const int s0 = static_cast<int>(static_cast<long long>(n_slots) * i / parts);
+    const int s1 = static_cast<int>(static_cast<long long>(n_slots) * (i + 1) / parts);
+    if (s1 <= s0) continue;
+    HistLevel sub       = lv;
+    sub.seg_node_offset = lv.seg_node_offset + s0 * unit;
+    sub.n_nodes         = (s1 - s0) * unit;
+    sub.reserve_sms     = kReserve;
+    if (lv.slot_of_node != nullptr) {
+      sub.slot_of_node = lv.slot_of_node + s0 * unit;  // absolute slots: `out` stays the base
+    } else {
+      sub.out = static_cast<unsigned char*>(lv.out) + static_cast<size_t>(s0) * slot_words * 8;
+    }
+    BuildHistogram(ctx, s, sub, stream);
+    if (timed && i == parts - 1) {
+      LBK_CUDA(cudaEventRecord(ctx->ev_stop, stream));
+      ctx->profile_recorded = true;
+    }
+    LBK_CUDA(cudaEventRecord(ctx->ev_part[i], stream));
+    LBK_CUDA(cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_part[i], 0));
+    AllReduce(ctx, static_cast<unsigned char*>(lv.out) + static_cast<size_t>(s0) * slot_words * 8,
+              static_cast<size_t>(s1 - s0) * slot_words, dtype, LBK_SUM, ctx->comm_stream);
+  }
+  ctx->profile = timed;
+  LBK_CUDA(cudaEventRecord(ctx->ev_comm_done, ctx->comm_stream));
+  LBK_CUDA(cudaStreamWaitEvent(stream, ctx->ev_comm_done, 0));
 }
 
 void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t n_rows, int node_begin,

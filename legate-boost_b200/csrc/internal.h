@@ -71,6 +71,10 @@ struct lbk_context {
   bool owns_nccl      = false;
   lbk_allreduce_fn cb = nullptr;
   void* cb_user       = nullptr;
+  // second stream for all-reduces that run beside the next histogram kernel (made on first use)
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t ev_part[4]   = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t ev_comm_done = nullptr;
   // optional timing of the histogram kernel alone (events on the caller's stream)
   bool profile            = false;
   cudaEvent_t ev_start    = nullptr, ev_stop = nullptr;
@@ -146,8 +150,15 @@ struct HistLevel {
   const int32_t* slot_of_node;
   void* out;               // [n_slots, K, B] pairs (int64 or double), already zeroed
   bool float_mode;
+  int reserve_sms = 0;     // SMs the persistent grid leaves free (for a collective that runs beside it)
 };
 void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStream_t stream);
+// BuildHistogram followed by the sum over ranks of the n_slots histograms of `out`.  With an NCCL
+// communicator and enough tickets the nodes are cut into parts: the all-reduce of one part runs
+// on a second stream beside the histogram kernel of the next.  `pairs` says that slot s holds
+// the built child of nodes 2s, 2s+1 of the batch (else slot = node).
+void BuildHistogramAllReduce(lbk_context* ctx, Scratch& s, const HistLevel& lv, int n_slots, bool pairs,
+                             cudaStream_t stream);
 void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t n_rows, int node_begin,
                int n_nodes, int32_t* row_index, int32_t* seg, cudaStream_t stream);
 // split.cu

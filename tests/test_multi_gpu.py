@@ -75,3 +75,55 @@ def test_two_gpus_match_oracle_with_two_ranks(case):
         assert p.exitcode == 0
     assert all(ok for _, ok, _ in res), res
     assert res[0][2] > 3
+
+
+def _hist_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import legateboost_b200 as lb
+    from legateboost_b200 import stages
+
+    ctx = lb.library.init_distributed(rank)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(100 + rank)
+    N, F, nb, n_nodes = 150000 + 1000 * rank, 128, 256, 128
+    bins = torch.randint(0, nb, (N, F), dtype=torch.uint8, device=dev, generator=gen)
+    row_ptr = torch.arange(F + 1, dtype=torch.int32, device=dev) * nb
+    q_pairs = torch.randint(-5000, 5000, (N, 1, 2), dtype=torch.int32, device=dev, generator=gen)
+    node = torch.randint(0, n_nodes, (N,), dtype=torch.int32, device=dev, generator=gen) + (n_nodes - 1)
+    row_index, seg = stages.group_rows(node, n_nodes - 1, n_nodes)
+    local = stages.histogram(bins, row_ptr, q_pairs, row_index, seg, F, mode=0, ctx=ctx)
+    want = local.clone()
+    dist.all_reduce(want)
+    # large enough (67 MB, 256 tickets) for the all-reduce to travel in parts beside the next part's kernel
+    got = stages.histogram(bins, row_ptr, q_pairs, row_index, seg, F, mode=0, ctx=ctx, all_reduce=True)
+    ok = bool(torch.equal(got, want)) and bool((want != local).any())
+    q.put((rank, ok))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_histogram_all_reduce_in_parts_matches_a_plain_all_reduce():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_hist_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(ok for _, ok in res), res
