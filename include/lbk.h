@@ -125,6 +125,13 @@ typedef struct lbk_build_tree_args {
 
 int lbk_build_tree(lbk_context* ctx, const lbk_build_tree_args* args);
 
+/* out[i, :] = leaf_value[leaf[i], :] for the rows of lbk_build_tree_args.out_leaf: the tree's
+ * predictions for its training rows (what the reference gets from a PREDICT task on the training
+ * matrix, legateboost.py `train_pred += model.predict(X)`).  Device pointers; leaf_value
+ * [max_nodes, n_outputs], leaf [n_rows], out [n_rows, n_outputs]; asynchronous on `stream`. */
+int lbk_leaf_values(lbk_context* ctx, const double* leaf_value, const int32_t* leaf, int64_t n_rows,
+                    int n_outputs, double* out, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * PREDICT.  Inputs X then (leaf_value, feature, split_value) per tree, output pred
  * (legateboost/models/tree.py:252-277, predict.cu:26-84).  pred is overwritten (zero + sum of

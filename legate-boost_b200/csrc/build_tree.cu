@@ -38,6 +38,18 @@ __global__ void __launch_bounds__(256)
   leaf[row] = node;
 }
 
+// out[i, :] = table[index[i], :]: the leaf values of the nodes a set of rows ended in.
+__global__ void __launch_bounds__(256)
+  k_gather_rows(const double* __restrict__ table, const int32_t* __restrict__ index, int64_t n, int K,
+                double* __restrict__ out)
+{
+  const int64_t e = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (e >= n * K) return;
+  const int64_t i = e / K;
+  const int k     = static_cast<int>(e - i * K);
+  out[e]          = __ldg(table + static_cast<int64_t>(__ldg(index + i)) * K + k);
+}
+
 template <typename T>
 void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t stream)
 {
@@ -529,6 +541,24 @@ int lbk_group_rows(lbk_context* ctx, const int32_t* node_of_row, int64_t n_rows,
     lbk::Scratch s(ctx, stream);
     lbk::GroupRows(ctx, s, node_of_row, n_rows, node_begin, n_nodes, row_index, seg, stream);
     LBK_CUDA(cudaStreamSynchronize(stream));
+  });
+}
+
+int lbk_leaf_values(lbk_context* ctx, const double* leaf_value, const int32_t* leaf, int64_t n_rows, int n_outputs,
+                    double* out, void* stream_)
+{
+  return lbk::Guard(ctx, [&] {
+    LBK_EXPECT(ctx != nullptr, "context is null");
+    LBK_EXPECT(n_rows >= 0 && n_outputs >= 1, "bad shape");
+    if (n_rows == 0) return;
+    LBK_EXPECT(leaf_value && leaf && out, "null argument");
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t stream  = static_cast<cudaStream_t>(stream_);
+    const int64_t total  = n_rows * n_outputs;
+    const int64_t blocks = (total + 255) / 256;
+    LBK_EXPECT(blocks <= 2147483647ll, "too many elements for one launch");
+    lbk::k_gather_rows<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(leaf_value, leaf, n_rows, n_outputs, out);
+    LBK_LAUNCH_CHECK();
   });
 }
 

@@ -85,22 +85,28 @@ __global__ void k_make_scale(const double* __restrict__ sums /* g,h */, QuantPar
   *qp       = p;
 }
 
-// One thread per row, looping over outputs; per-output block sums go to node_sums[0,k] with one
-// 64-bit atomic pair per block and output.  Blocks walk the rows with a grid stride so that
-// the number of atomics stays small.
+// Per-output block sums go to node_sums[0,k] with one 64-bit atomic pair per block and output;
+// blocks walk the elements with a grid stride so that the number of atomics stays small.
+// Element (row, k) = flat index row * K + k; a thread keeps one k (the grid's stride is a multiple
+// of K), so the loads and stores of a warp are contiguous whatever K is.
 __global__ void __launch_bounds__(256)
   k_quantise(const double* __restrict__ g, const double* __restrict__ h, int64_t ldg, int64_t row_offset,
              int64_t n_local, int K, long long seed, const QuantParams* __restrict__ qp_ptr,
              int2* __restrict__ gpair, GPairI64* __restrict__ root_sums, int* __restrict__ max_abs)
 {
-  __shared__ long long red[2][8];
+  extern __shared__ unsigned long long s_sum[];  // [K][2]
   const QuantParams qp = *qp_ptr;
   const int tid        = threadIdx.x;
+  for (int i = tid; i < 2 * K; i += blockDim.x) s_sum[i] = 0ull;
+  __syncthreads();
+  const int64_t threads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t rows_per_turn = threads / K;  // >= 1: the launcher gives at least K threads
+  const int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + tid;
   int mg = 0, mh = 0;
-  for (int k = 0; k < K; ++k) {
+  if (t < rows_per_turn * K) {
+    const int k = static_cast<int>(t % K);
     long long sg = 0, sh = 0;
-    for (int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.x) + tid; row < n_local;
-         row += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    for (int64_t row = t / K; row < n_local; row += rows_per_turn) {
       const double gv = g[row * ldg + k];
       const double hv = h[row * ldg + k];
       const int2 q    = QuantisePair(gv, hv, qp, HashCombine(seed, row_offset + row, k));
@@ -110,26 +116,13 @@ __global__ void __launch_bounds__(256)
       mg = max(mg, q.x == INT32_MIN ? INT32_MAX : abs(q.x));
       mh = max(mh, q.y == INT32_MIN ? INT32_MAX : abs(q.y));
     }
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-      sg += __shfl_down_sync(0xffffffffu, sg, off);
-      sh += __shfl_down_sync(0xffffffffu, sh, off);
-    }
-    if ((tid & 31) == 0) {
-      red[0][tid >> 5] = sg;
-      red[1][tid >> 5] = sh;
-    }
-    __syncthreads();
-    if (tid == 0) {
-      long long tg = 0, th = 0;
-      for (int w = 0; w < 8; ++w) {
-        tg += red[0][w];
-        th += red[1][w];
-      }
-      atomicAdd(reinterpret_cast<unsigned long long*>(&root_sums[k].grad), static_cast<unsigned long long>(tg));
-      atomicAdd(reinterpret_cast<unsigned long long*>(&root_sums[k].hess), static_cast<unsigned long long>(th));
-    }
-    __syncthreads();
+    atomicAdd(&s_sum[2 * k], static_cast<unsigned long long>(sg));
+    atomicAdd(&s_sum[2 * k + 1], static_cast<unsigned long long>(sh));
+  }
+  __syncthreads();
+  for (int i = tid; i < 2 * K; i += blockDim.x) {
+    unsigned long long* dst = reinterpret_cast<unsigned long long*>(root_sums) + i;  // grad, hess of k = i / 2
+    if (s_sum[i] != 0ull) atomicAdd(dst, s_sum[i]);
   }
   for (int off = 16; off >= 1; off >>= 1) {
     mg = max(mg, __shfl_down_sync(0xffffffffu, mg, off));
@@ -185,10 +178,13 @@ void Quantise(lbk_context* ctx, Scratch& s, const double* g, const double* h, in
   LBK_CUDA(cudaMemsetAsync(root_sums, 0, sizeof(GPairI64) * K, stream));
   LBK_CUDA(cudaMemsetAsync(max_abs, 0, 2 * sizeof(int), stream));
   if (n_local > 0) {
-    int64_t blocks = (n_local + 255) / 256;
+    int64_t blocks = (n_local * K + 255) / 256;
     const int64_t cap = static_cast<int64_t>(ctx->sm_count) * 8;
     if (blocks > cap) blocks = cap;
-    k_quantise<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(g, h, ldg, row_offset, n_local, K,
+    if (blocks * 256 < K) blocks = (K + 255) / 256;  // a thread keeps one output: at least K threads
+    const size_t smem = sizeof(unsigned long long) * 2 * K;
+    LBK_EXPECT(smem <= 48 * 1024, "too many outputs for the quantiser's block sums");
+    k_quantise<<<static_cast<unsigned>(blocks), 256, smem, stream>>>(g, h, ldg, row_offset, n_local, K,
                                                                   static_cast<long long>(seed), params, gpair, root_sums, max_abs);
     LBK_LAUNCH_CHECK();
   }

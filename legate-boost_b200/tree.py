@@ -263,7 +263,13 @@ class Tree(BaseModel):
     def predict(self, X: torch.Tensor) -> torch.Tensor:
         fit_rows, self._fit_rows = getattr(self, "_fit_rows", None), None
         if fit_rows is not None and fit_rows[0] == _tensor_key(X):
-            return self.leaf_value.index_select(0, fit_rows[1])
+            leaf = fit_rows[1]
+            out = torch.empty((leaf.shape[0], self.leaf_value.shape[1]), dtype=torch.float64, device=leaf.device)
+            ctx = L.context(leaf.device.index)
+            with torch.cuda.device(leaf.device):
+                ctx.check(ctx.lib.lbk_leaf_values(ctx.handle, self.leaf_value.data_ptr(), leaf.data_ptr(),
+                                                  leaf.shape[0], self.leaf_value.shape[1], out.data_ptr(), _stream_ptr()))
+            return out
         return Tree.batch_predict([self], X)
 
     @staticmethod
