@@ -17,7 +17,7 @@
 //     the nodes become pass-through nodes (split = +inf) and the leaf's value is copied to the
 //     bottom level.  A walk is then exactly S steps of "load node, load x, compare, descend" with
 //     no leaf test, and only the bottom level of leaf values is kept.
-//   * Trees are brought into shared memory in groups of up to eight (cp.async, double buffered)
+//   * Trees are brought into shared memory in groups of up to eight (bulk async copies, double buffered)
 //     together with their bottom-level leaf values; a thread walks the trees of a group as
 //     independent chains, which hides the shared-memory latency that one dependent chain exposes.
 //   * Predictions are accumulated in float64 in tree order (bit-identical to the reference's
@@ -87,12 +87,44 @@ __global__ void k_pack_trees(const TreePtrs* __restrict__ trees, int K, int F, i
     leaves[static_cast<int64_t>(t.node_off) * K + i] = t.leaf[i];
 }
 
-__device__ inline void CpAsync16(unsigned smem_dst, const void* gsrc)
+// Bulk asynchronous copy global -> shared (the copy engine moves whole lines; nothing passes
+// through the load/store pipe), completion counted in bytes on an mbarrier.  No multicast.
+__device__ inline void MbarInit(unsigned bar, unsigned count)
 {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gsrc) : "memory");
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ inline void CpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-__device__ inline void CpAsyncWaitAll() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+__device__ inline void MbarExpectTx(unsigned bar, unsigned bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ inline void BulkCopy(unsigned smem_dst, const void* gsrc, unsigned bytes, unsigned bar)
+{
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_dst),
+               "l"(gsrc), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ inline bool MbarTryWait(unsigned bar, unsigned parity)
+{
+  unsigned ok;
+  asm volatile(
+    "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+    : "=r"(ok)
+    : "r"(bar), "r"(parity)
+    : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after about a second, reports through the context's status word and lets
+// the block finish (with wrong sums, which the host then refuses) instead of spinning for ever.
+constexpr int kFaultPredictStaging = 21;
+__device__ inline bool MbarWait(unsigned bar, unsigned parity, int* status)
+{
+  for (unsigned spin = 0; spin < (1u << 22); ++spin) {
+    if (MbarTryWait(bar, parity)) return true;
+    if (spin > 64) __nanosleep(256);
+  }
+  atomicExch(status, kFaultPredictStaging);
+  return false;
+}
 
 __device__ inline void LdsNode(unsigned addr, float& split, int& foff)
 {
@@ -168,40 +200,46 @@ template <typename T, int RB, int TG>
 __global__ void __launch_bounds__(RB)
   k_predict_tiled(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
                   const typename NodeOf<T>::type* __restrict__ nodes_c, const double* __restrict__ leaves_c,
-                  double* __restrict__ pred, int64_t ldp, int S, int NI, int NL)
+                  double* __restrict__ pred, int64_t ldp, int S, int NI, int NL, int* __restrict__ status)
 {
   using NodeT = typename NodeOf<T>::type;
   constexpr int RBP = RB + 1;
+  __shared__ __align__(8) unsigned long long s_bar[2];
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* xs = reinterpret_cast<T*>(smem_raw);
   size_t off = (sizeof(T) * static_cast<size_t>(F) * RBP + 15) / 16 * 16;
   double* accs = reinterpret_cast<double*>(smem_raw + off);
   off += K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
+  // a group buffer: the nodes of its TG trees, then (K == 1) their bottom-level values
   const unsigned node_bytes = static_cast<unsigned>(NI * sizeof(NodeT));
-  const unsigned slot_bytes = node_bytes + (K == 1 ? static_cast<unsigned>(NL * sizeof(double)) : 0u);
+  const unsigned leaf_bytes = K == 1 ? static_cast<unsigned>(NL * sizeof(double)) : 0u;
+  const unsigned buf_bytes  = TG * (node_bytes + leaf_bytes);
   unsigned char* tree_s     = smem_raw + off;
 
   const int tid       = threadIdx.x;
   const int64_t row0  = static_cast<int64_t>(blockIdx.x) * RB;
   const int rows_here = static_cast<int>((n_rows - row0) < RB ? (n_rows - row0) : RB);
   const unsigned tree0 = static_cast<unsigned>(__cvta_generic_to_shared(tree_s));
+  const unsigned bar0  = static_cast<unsigned>(__cvta_generic_to_shared(&s_bar[0]));
   const int n_groups   = (n_trees + TG - 1) / TG;
+  if (tid == 0) {
+    MbarInit(bar0, 1);
+    MbarInit(bar0 + 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
 
-  // group of trees -> shared memory, 16 bytes per copy (nodes, then leaves when K == 1)
+  // group of trees -> shared memory: two bulk copies (the trees of a group are neighbours in the
+  // packed arrays), issued by one thread
   auto stage_group = [&](int group, int buf) {
-    for (int j = 0; j < TG; ++j) {
-      const int t = group * TG + j;
-      if (t >= n_trees) break;
-      const unsigned d_s       = tree0 + static_cast<unsigned>(buf * TG + j) * slot_bytes;
-      const unsigned char* src = reinterpret_cast<const unsigned char*>(nodes_c + static_cast<int64_t>(t) * NI);
-      for (unsigned i = tid; i < node_bytes / 16; i += RB) CpAsync16(d_s + i * 16, src + static_cast<size_t>(i) * 16);
-      if (K == 1) {
-        const unsigned char* lsrc = reinterpret_cast<const unsigned char*>(leaves_c + static_cast<int64_t>(t) * NL);
-        for (unsigned i = tid; i < static_cast<unsigned>(NL) / 2; i += RB)
-          CpAsync16(d_s + node_bytes + i * 16, lsrc + static_cast<size_t>(i) * 16);
-      }
-    }
-    CpAsyncCommit();
+    if (tid != 0) return;
+    const int t0       = group * TG;
+    const unsigned nt  = static_cast<unsigned>(min(TG, n_trees - t0));
+    const unsigned bar = bar0 + 8u * buf;
+    const unsigned dst = tree0 + static_cast<unsigned>(buf) * buf_bytes;
+    MbarExpectTx(bar, nt * (node_bytes + leaf_bytes));
+    BulkCopy(dst, nodes_c + static_cast<int64_t>(t0) * NI, nt * node_bytes, bar);
+    if (K == 1) BulkCopy(dst + TG * node_bytes, leaves_c + static_cast<int64_t>(t0) * NL, nt * leaf_bytes, bar);
   };
   stage_group(0, 0);
 
@@ -233,15 +271,18 @@ __global__ void __launch_bounds__(RB)
   // level, whose values start at heap index 2^S - 1.
   constexpr unsigned kNodeShift = sizeof(NodeT) == 16 ? 1 : 0;
   const unsigned xcol_s   = static_cast<unsigned>(__cvta_generic_to_shared(xs + tid));
-  const unsigned leaf_adj = node_bytes - 8u * ((1u << S) - 1u);
+  const unsigned leaf_adj = TG * node_bytes - 8u * ((1u << S) - 1u);  // from a bottom-level p8 to the value, tree 0
   const bool one_buffer   = n_groups == 1;
   double acc0             = 0.0;
+  __syncthreads();  // the X tile is in place
   for (int g = 0; g < n_groups; ++g) {
     const int buf = one_buffer ? 0 : (g & 1);
-    CpAsyncWaitAll();
-    __syncthreads();  // group g has landed (and the X tile, on the first pass)
-    if (g + 1 < n_groups) stage_group(g + 1, buf ^ 1);
-    const unsigned gbase = tree0 + static_cast<unsigned>(buf * TG) * slot_bytes;
+    // buffer `buf` is filled for the (g / 2)-th time (every time when there is one buffer)
+    const unsigned parity = one_buffer ? (g & 1) : ((g >> 1) & 1);
+    // group g has landed - or every thread of the block gives up together
+    if (!__syncthreads_and(MbarWait(bar0 + 8u * buf, parity, status) ? 1 : 0)) break;
+    if (g + 1 < n_groups && !one_buffer) stage_group(g + 1, buf ^ 1);
+    const unsigned gbase = tree0 + static_cast<unsigned>(buf) * buf_bytes;
     const int nt         = min(TG, n_trees - g * TG);
     if (tid < rows_here) {
       unsigned p8[TG];
@@ -253,7 +294,7 @@ __global__ void __launch_bounds__(RB)
           for (int j = 0; j < TG; ++j) {
             T split;
             int foff;
-            LdsNode(gbase + j * slot_bytes + (p8[j] << kNodeShift), split, foff);
+            LdsNode(gbase + j * node_bytes + (p8[j] << kNodeShift), split, foff);
             const T x = LdsX(xcol_s + foff, T());
             p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
           }
@@ -263,7 +304,7 @@ __global__ void __launch_bounds__(RB)
           for (int j = 0; j < nt; ++j) {
             T split;
             int foff;
-            LdsNode(gbase + j * slot_bytes + (p8[j] << kNodeShift), split, foff);
+            LdsNode(gbase + j * node_bytes + (p8[j] << kNodeShift), split, foff);
             const T x = LdsX(xcol_s + foff, T());
             p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
           }
@@ -273,7 +314,7 @@ __global__ void __launch_bounds__(RB)
       for (int j = 0; j < TG; ++j) {
         if (j < nt) {
           if (K == 1) {
-            acc0 += LdsF64(gbase + j * slot_bytes + leaf_adj + p8[j]);
+            acc0 += LdsF64(gbase + j * leaf_bytes + leaf_adj + p8[j]);
           } else {
             const int64_t lj = static_cast<int64_t>(g * TG + j) * NL + ((p8[j] >> 3) - ((1u << S) - 1u));
             const double* lf = leaves_c + lj * K;
@@ -283,6 +324,7 @@ __global__ void __launch_bounds__(RB)
       }
     }
     __syncthreads();  // everyone is done with buffer `buf` before it is refilled
+    if (g + 1 < n_groups && one_buffer) stage_group(g + 1, 0);
   }
   if (tid < rows_here) {
     const int64_t row = row0 + tid;
@@ -332,14 +374,14 @@ size_t TiledSmem(int rb, int tg, int nbuf, int F, int K, int NI, int NL)
 template <typename T, int RB, int TG>
 void LaunchTiled(const T* X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
                  const typename NodeOf<T>::type* nodes_c, const double* leaves_c, double* pred, int64_t ldp, int S,
-                 int NI, int NL, size_t smem, cudaStream_t stream)
+                 int NI, int NL, size_t smem, int* status, cudaStream_t stream)
 {
   if (smem > 48 * 1024)
     LBK_CUDA(cudaFuncSetAttribute(k_predict_tiled<T, RB, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
   const unsigned grid = static_cast<unsigned>((n_rows + RB - 1) / RB);
   k_predict_tiled<T, RB, TG><<<grid, RB, smem, stream>>>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S,
-                                                          NI, NL);
+                                                          NI, NL, status);
   LBK_LAUNCH_CHECK();
 }
 
@@ -420,7 +462,8 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
   LBK_LAUNCH_CHECK();
 #define LBK_PREDICT_CASE(RB_, TG_)                                                                                  \
   if (rb == RB_ && tg == TG_) {                                                                                     \
-    LaunchTiled<T, RB_, TG_>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S, NI, NL, smem, stream); \
+    LaunchTiled<T, RB_, TG_>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S, NI, NL, smem,          \
+                             ctx->d_status, stream);                                                                \
     return;                                                                                                         \
   }
 #define LBK_PREDICT_ROW(RB_) LBK_PREDICT_CASE(RB_, 8) LBK_PREDICT_CASE(RB_, 4) LBK_PREDICT_CASE(RB_, 2) LBK_PREDICT_CASE(RB_, 1)
