@@ -6,9 +6,10 @@
 //
 // Design for B200: ONE launch for the whole ensemble, everything a step of the walk touches lives
 // in shared memory.
-//   * A block owns a tile of rows (one thread per row) and stages it once, feature-major with a
-//     pitch of rows+1, so the thread of row r reads bank (f+r)%32: every row of X is read from HBM
-//     exactly once, coalesced.
+//   * A block owns a tile of rows (one thread per row); every thread stages its own row,
+//     feature-major with a pitch of one element per thread, so thread t only ever touches bank
+//     t mod 32 whatever feature a tree asks for: the x lookups of a walk never conflict.  Every row
+//     of X is read from HBM exactly once (16-byte loads, the rest of a sector comes from L1).
 //   * The trees are first packed into one array of small nodes: for float32 X a node is 8 bytes
 //     (float split, int feature) - "x <= split" with x a float is the same test as
 //     "x <= the largest float not above split", so the split is rounded down once at packing time
@@ -194,7 +195,7 @@ __global__ void k_pack_complete(const TreePtrs* __restrict__ trees, int K, int F
   }
 }
 
-// Tiled kernel.  Shared memory: X tile [F][RB+1] | accumulators [K][RB] (K > 1) |
+// Tiled kernel.  Shared memory: X tile [F][RB] | accumulators [K][RB] (K > 1) |
 // NBUF x TG x slot, slot = NI nodes (+ NL leaf values when K == 1).
 template <typename T, int RB, int TG>
 __global__ void __launch_bounds__(RB)
@@ -203,11 +204,10 @@ __global__ void __launch_bounds__(RB)
                   double* __restrict__ pred, int64_t ldp, int S, int NI, int NL, int* __restrict__ status)
 {
   using NodeT = typename NodeOf<T>::type;
-  constexpr int RBP = RB + 1;
   __shared__ __align__(8) unsigned long long s_bar[2];
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* xs = reinterpret_cast<T*>(smem_raw);
-  size_t off = (sizeof(T) * static_cast<size_t>(F) * RBP + 15) / 16 * 16;
+  size_t off = (sizeof(T) * static_cast<size_t>(F) * RB + 15) / 16 * 16;
   double* accs = reinterpret_cast<double*>(smem_raw + off);
   off += K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
   // a group buffer: the nodes of its TG trees, then (K == 1) their bottom-level values
@@ -243,25 +243,23 @@ __global__ void __launch_bounds__(RB)
   };
   stage_group(0, 0);
 
-  // stage the X tile: a warp reads whole rows (coalesced), eight rows in flight per lane
-  {
-    const int lane = tid & 31, warp = tid >> 5;
-    constexpr int NW = RB / 32, U = 8;
-    for (int rb = warp; rb < rows_here; rb += NW * U) {
-      for (int f = lane; f < F; f += 32) {
-        T v[U];
+  // Stage the X tile: every thread copies its own row, feature-major with a pitch of RB elements,
+  // so that thread t only ever touches bank t mod 32 (x 2 for float64) - on the way in and in every
+  // step of every walk, whatever features the trees ask for.  16-byte loads when the rows allow it;
+  // the sectors of a row are reused from L1 by the following loads of the same thread.
+  if (tid < rows_here) {
+    const T* xr     = X + (row0 + tid) * ldx;
+    constexpr int V = 16 / sizeof(T);
+    int f           = 0;
+    if ((reinterpret_cast<uintptr_t>(X) & 15) == 0 && ldx % V == 0) {
+#pragma unroll 4
+      for (; f + V <= F; f += V) {
+        const int4 v = *reinterpret_cast<const int4*>(xr + f);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int r = rb + u * NW;
-          if (r < rows_here) v[u] = __ldcs(X + (row0 + r) * ldx + f);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int r = rb + u * NW;
-          if (r < rows_here) xs[f * RBP + r] = v[u];
-        }
+        for (int i = 0; i < V; ++i) xs[(f + i) * RB + tid] = reinterpret_cast<const T*>(&v)[i];
       }
     }
+    for (; f < F; ++f) xs[f * RB + tid] = xr[f];
   }
   if (K > 1)
     for (int k = 0; k < K; ++k) accs[k * RB + tid] = 0.0;
@@ -365,7 +363,7 @@ template <typename T>
 size_t TiledSmem(int rb, int tg, int nbuf, int F, int K, int NI, int NL)
 {
   using NodeT = typename NodeOf<T>::type;
-  const size_t x_bytes    = (sizeof(T) * static_cast<size_t>(F) * (rb + 1) + 15) / 16 * 16;
+  const size_t x_bytes    = (sizeof(T) * static_cast<size_t>(F) * rb + 15) / 16 * 16;
   const size_t a_bytes    = K > 1 ? sizeof(double) * static_cast<size_t>(K) * rb : 0;
   const size_t slot_bytes = static_cast<size_t>(NI) * sizeof(NodeT) + (K == 1 ? static_cast<size_t>(NL) * sizeof(double) : 0);
   return x_bytes + a_bytes + static_cast<size_t>(nbuf) * tg * slot_bytes;
@@ -426,7 +424,7 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
     const int rbs[4] = {256, 128, 64, 32};
     const int tgs[4] = {8, 4, 2, 1};
     for (int ri = 0; ri < 4 && rb == 0; ++ri) {
-      if (static_cast<int64_t>(F) * (rbs[ri] + 1) * static_cast<int64_t>(sizeof(T)) >= (int64_t{1} << 30)) continue;
+      if (static_cast<int64_t>(F) * rbs[ri] * static_cast<int64_t>(sizeof(T)) >= (int64_t{1} << 30)) continue;
       for (int ti = 0; ti < 4; ++ti) {
         if (tgs[ti] > n_trees && tgs[ti] > 1) continue;  // no wider than the ensemble
         const int nbuf = n_trees > tgs[ti] ? 2 : 1;
@@ -457,7 +455,7 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
   }
   NodeT* nodes_c   = s.alloc<NodeT>(static_cast<size_t>(n_trees) * NI);
   double* leaves_c = s.alloc<double>(static_cast<size_t>(n_trees) * NL * K);
-  k_pack_complete<NodeT><<<n_trees, 256, 0, stream>>>(d_trees, K, F, (rb + 1) * static_cast<int>(sizeof(T)), S, NI, NL,
+  k_pack_complete<NodeT><<<n_trees, 256, 0, stream>>>(d_trees, K, F, rb * static_cast<int>(sizeof(T)), S, NI, NL,
                                                       nodes_c, leaves_c);
   LBK_LAUNCH_CHECK();
 #define LBK_PREDICT_CASE(RB_, TG_)                                                                                  \
