@@ -408,3 +408,43 @@ def test_first_predict_on_the_training_matrix_uses_the_leaf_record(lb):
         assert torch.equal(t.predict(X), want)
     stump = lb.Tree(max_depth=0).set_random_state(np.random.RandomState(1)).fit(X, g, h)
     assert torch.equal(stump.predict(X), lb.Tree.batch_predict([stump], X))
+
+
+def test_full_size_histogram_checksums(lb):
+    """Size-independent properties at the benchmark's own size (10 M x 128, 128 nodes): within
+    every node the bins of every feature add up to the node's total pair, and the grand total is the
+    total of all pairs (integer arithmetic: exact)."""
+    import bench
+    from legateboost_b200 import stages
+
+    n = 10_000_000
+    bins, row_ptr, gpair, _, row_index, seg, node, max_abs = bench.hist_inputs(torch, n, 7, torch.device("cuda"))
+    hist = stages.histogram(bins, row_ptr, gpair, row_index, seg, bench.HIST_FEATURES, mode=0, max_abs=max_abs)
+    n_nodes = seg.shape[0] - 1
+    per_feature = hist.view(n_nodes, bench.HIST_FEATURES, bench.HIST_BINS, 2).sum(dim=2)      # [node, feature, 2]
+    want = torch.zeros((n_nodes, 2), dtype=torch.int64, device=hist.device)
+    want.index_add_(0, (node - (n_nodes - 1)).long(), gpair[:, 0, :].long())
+    assert torch.equal(per_feature, want[:, None, :].expand_as(per_feature))
+    assert torch.equal(per_feature[:, 0, :].sum(dim=0), gpair[:, 0, :].long().sum(dim=0))
+    # the same call without the magnitudes handed in (the library finds them) gives the same bits
+    assert torch.equal(stages.histogram(bins, row_ptr, gpair, row_index, seg, bench.HIST_FEATURES, mode=0), hist)
+
+
+def test_full_size_tree_properties(lb):
+    """10 M x 64 rows, depth 8: the node of every training row from the builder equals the walk over
+    X; the hessians of the children add up to the parent's (h = 1: the root holds the row count)."""
+    n, F = 10_000_000, 64
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5)
+    X = torch.rand((n, F), dtype=torch.float32, device="cuda", generator=gen)
+    g = torch.randn((n, 1), dtype=torch.float64, device="cuda", generator=gen)
+    h = torch.ones((n, 1), dtype=torch.float64, device="cuda")
+    t = lb.Tree(max_depth=8).set_random_state(np.random.RandomState(2)).fit(X, g, h)
+    walk = lb.Tree.batch_predict([t], X)
+    assert torch.equal(t.predict(X), walk)
+    feature = t.feature.cpu().numpy()
+    hess = t.hessian.cpu().numpy()[:, 0]
+    assert abs(hess[0] - n) <= 1e-6 * n
+    split = np.nonzero(feature >= 0)[0]
+    assert len(split) > 100
+    assert np.allclose(hess[2 * split + 1] + hess[2 * split + 2], hess[split], rtol=1e-12, atol=0)
