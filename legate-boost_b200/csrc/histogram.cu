@@ -8,31 +8,26 @@
 // Design for B200:
 //   * rows arrive grouped by node (an index array plus per-node offsets), so a thread block only
 //     ever accumulates one node at a time and its private histogram lives in shared memory;
-//   * bins are one byte per element in groups of 32 features (see proposals.cu); a warp handles
-//     one row at a time with ONE LANE PER FEATURE, and the private histogram is laid out
-//     [bin][lane]: lane l always hits shared-memory bank l, so the two atomics a warp issues per
-//     row are conflict free whatever the bins are, and no two lanes of a warp share an address;
-//   * the kernel is bound by the load/store pipe of the SM, not by HBM: the two reductions a warp
-//     issues per row are unavoidable (64-bit shared atomics are compare-and-swap loops on this
-//     part), so everything else is kept small: per row one byte load (the lane's bin) and half a
-//     broadcast 16-byte load (the pairs of two rows);
-//   * every warp runs its own pipeline over 32-row batches (no block barrier in the main loop):
-//     the rows of a node are scattered, so each 32-byte row of a group is its own gather; the bins
-//     of the warp's next batch travel global -> shared asynchronously (cp.async.cg, 16 bytes per
-//     lane, one instruction moves 16 rows and bypasses the small L1 left beside the histograms)
-//     into a two-deep per-warp ring, the pairs of that batch wait in one register pair per lane,
-//     and the row ids of the batch after that are being loaded; with 32 warps per SM that keeps
-//     64 KB per SM in flight;
+//   * bins are one byte per element, row-major with rows padded to whole 32-feature groups (see
+//     proposals.cu): the pieces of a row that different tickets need share DRAM bursts and L2 lines;
+//   * the kernel is bound by the load/store data pipe of the SM, not by HBM: the two shared-memory
+//     reductions a warp issues per 32 updates are unavoidable (64-bit shared atomics are
+//     compare-and-swap loops on this part), and a gather costs the pipe one pass per distinct
+//     128-byte line.  So a ticket covers two feature groups (one pass per row for 64 bin bytes),
+//     the rows of a batch go straight from global memory into registers with one 16-byte load per
+//     lane, and the lanes of a row walk their bytes in an xor-skewed order that keeps the 32
+//     reductions of a warp on 32 different banks whatever the bins are (k_hist_smem);
+//   * every warp runs its own pipeline over batches of rows (no block barrier in the main loop, no
+//     staging in shared memory): the rows of the next two batches and the row ids of the two after
+//     are in flight in registers;
 //   * accumulation is in int32 like the reference, but guarded: with m = the largest |q| of the
 //     call, at most floor((2^31-1)/m) rows are accumulated between flushes, so no partial sum can
 //     wrap whatever the bins are;
-//   * work is cut into (node, row chunk, feature group, output) tickets sized on the device:
-//     one chunk per node when the level has at least as many (node, group, output) triples as
-//     resident blocks, else chunks that give every resident block about one ticket; blocks draw
-//     tickets from an atomic counter (persistent grid, two 512-thread blocks per SM);
-//   * a node whose rows fit one chunk owns its output region and flushes with plain stores;
-//     otherwise the flush uses 64-bit global atomics; chunks of <= 128 rows skip shared memory.
-#include <cstdlib>
+//   * work is cut into (node chunk, feature groups, output) tickets by a planner on the device
+//     (k_hist_plan); blocks draw tickets from an atomic counter (persistent grid);
+//   * a node in one chunk owns its output region and flushes with plain stores; a node cut into
+//     several chunks leaves int32 partial sums in slots and k_hist_sum adds them up afterwards
+//     (without slot memory: 64-bit global atomics); chunks of <= 128 rows skip shared memory.
 #include <mutex>
 #include <string>
 
@@ -70,39 +65,7 @@ struct HistParams {
   void* out;
 };
 
-__device__ inline void CpAsync16(unsigned smem_dst, const void* gsrc)
-{
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gsrc) : "memory");
-}
-__device__ inline void CpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ inline void CpAsyncWait()
-{
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-__device__ inline unsigned LdsU8(unsigned addr)
-{
-  unsigned v;
-  asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(addr) : "memory");
-  return v;
-}
-__device__ inline int2 LdsV2(unsigned addr)
-{
-  int2 v;
-  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
-  return v;
-}
-__device__ inline void StsV2(unsigned addr, int2 v)
-{
-  asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
-}
 __device__ inline unsigned SmemAddr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
-__device__ inline int4 LdsV4(unsigned addr)
-{
-  int4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-  return v;
-}
 __device__ inline void RedShared(unsigned addr, int v)
 {
   asm volatile("red.shared.add.s32 [%0], %1;\n" ::"r"(addr), "r"(v) : "memory");
@@ -150,12 +113,11 @@ constexpr int kOverheadMulti  = 5000;  // the same for clear + partial store + i
 
 __global__ void __launch_bounds__(1024)
   k_hist_plan(const int32_t* __restrict__ seg, const int32_t* __restrict__ slot_of_node, int n_nodes, int GK,
-              int resident, const int* __restrict__ max_abs, long long slot_capacity, int force, int32_t* __restrict__ chunk_off,
+              int resident, const int* __restrict__ max_abs, long long slot_capacity, int32_t* __restrict__ chunk_off,
               int32_t* __restrict__ part_off, int32_t* __restrict__ multi, int32_t* __restrict__ plan,
               unsigned int* __restrict__ ticket)
 {
   __shared__ long long red[32];
-  __shared__ int red_max[32];
   __shared__ long long wsum[32];
   __shared__ long long carry;
   __shared__ long long total_s;
@@ -236,8 +198,6 @@ __global__ void __launch_bounds__(1024)
     int best = -1;
     for (int c = 0; c < kPlanCandidates; ++c)
       if (slot_capacity > 0 && cap >= kTileRows && cand_fit[c] && (best < 0 || cand_cost[c] < cand_cost[best] * 0.98)) best = c;
-    if (force >= 0 && force < kPlanCandidates && slot_capacity > 0 && cap >= kTileRows && cand_fit[force]) best = force;
-    plan[7] = best;
     if (best >= 0) {
       ch_s   = cand_ch[best];
       mode_s = 1;
@@ -707,7 +667,7 @@ struct HistLaunch {
 HistLaunch PickHistKernel(bool smem_path, int bin_bytes, bool float_mode, int n_groups, int sm_count)
 {
   HistLaunch h;
-  h.width   = smem_path && n_groups >= 2 && getenv("LBK_HIST_NARROW") == nullptr ? 2 : 1;
+  h.width   = smem_path && n_groups >= 2 ? 2 : 1;
   h.threads = kHistThreads * h.width;
   h.smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * h.width * 8 + 256 : 0;
   h.sum = nullptr;
@@ -855,10 +815,7 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   p.part_off = nullptr;
   p.multi    = nullptr;
   p.partial  = nullptr;
-  int force = -1;
-  if (const char* e = getenv("LBK_HIST_FORCE")) force = atoi(e);
-  const bool want_slots = getenv("LBK_HIST_SLOTS") == nullptr || atoi(getenv("LBK_HIST_SLOTS")) != 0;
-  if (smem_path && want_slots) {
+  if (smem_path) {
     slot_capacity           = 10ll * hl.grid;
     const size_t slot_bytes = static_cast<size_t>(p.mb) * kGroup * hl.width * 8;
     int32_t* part_off       = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes) + 1);
@@ -867,11 +824,11 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
     p.multi                 = multi;
     p.partial               = s.alloc<unsigned char>(slot_bytes * slot_capacity);
     k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, tickets_per_chunk, hl.grid,
-                                        lv.float_mode ? nullptr : max_abs, slot_capacity, force, chunk_off, part_off,
+                                        lv.float_mode ? nullptr : max_abs, slot_capacity, chunk_off, part_off,
                                         multi, plan, p.ticket);
   } else {
     k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, tickets_per_chunk, hl.grid,
-                                        lv.float_mode ? nullptr : max_abs, 0, -1, chunk_off, nullptr, nullptr, plan,
+                                        lv.float_mode ? nullptr : max_abs, 0, chunk_off, nullptr, nullptr, plan,
                                         p.ticket);
   }
   LBK_LAUNCH_CHECK();
@@ -888,12 +845,6 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   }
   // stream ordered: the slots go back to the pool once the kernel has run
   if (p.partial) s.free_one(p.partial);
-  if (getenv("LBK_HIST_DEBUG")) {
-    int hp[8];
-    LBK_CUDA(cudaMemcpyAsync(hp, plan, sizeof(hp), cudaMemcpyDeviceToHost, stream));
-    LBK_CUDA(cudaStreamSynchronize(stream));
-    fprintf(stderr, "hist plan: ch %d chunks %d safe %d mode %d cand %d grid %d\n", hp[0], hp[1], hp[3], hp[6], hp[7], hl.grid);
-  }
 }
 
 void BuildHistogramAllReduce(lbk_context* ctx, Scratch& s, const HistLevel& lv, int n_slots, bool pairs,
@@ -1113,8 +1064,7 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     p.multi    = nullptr;
     p.partial  = nullptr;
       k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, (p.G + hl.width - 1) / hl.width * p.K, hl.grid,
-                                        float_mode ? nullptr : max_abs, 0,
-                                        -1, chunk_off, nullptr, nullptr, plan, p.ticket);
+                                        float_mode ? nullptr : max_abs, 0, chunk_off, nullptr, nullptr, plan, p.ticket);
     LBK_LAUNCH_CHECK();
     hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
     LBK_LAUNCH_CHECK();
