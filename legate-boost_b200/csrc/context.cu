@@ -6,6 +6,7 @@
 // needs no NCCL at all and a multi-GPU user shares the copy already loaded in the process.
 #include <dlfcn.h>
 
+#include <climits>
 #include <cstring>
 #include <mutex>
 
@@ -23,7 +24,26 @@ struct NcclApi {
   int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t)            = nullptr;
   const char* (*GetErrorString)(int)                                                     = nullptr;
   void* CommInitRankRaw                                                                  = nullptr;
+  void* CommInitRankConfigRaw                                                            = nullptr;
 };
+
+// The leading fields of ncclConfig_t as they have been since NCCL 2.18; the library reads `size`
+// and `version` and takes its defaults for the fields a shorter structure does not have.
+struct NcclConfigPrefix {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  int blocking;
+  int cgaClusterSize;
+  int minCTAs;
+  int maxCTAs;
+  const char* netName;
+  int splitShare;
+};
+// CTAs the library's own communicator may use per collective: the histogram kernel leaves 20 SMs
+// free while an all-reduce runs beside it (see BuildHistogramAllReduce); a collective that took
+// more would push histogram blocks into a second round.
+constexpr int kCommMaxCtas = 16;
 
 struct UniqueId {
   char bytes[LBK_UNIQUE_ID_BYTES];
@@ -42,6 +62,7 @@ NcclApi& nccl()
     if (!api.handle) return;
     api.GetUniqueId     = reinterpret_cast<int (*)(void*)>(dlsym(api.handle, "ncclGetUniqueId"));
     api.CommInitRankRaw = dlsym(api.handle, "ncclCommInitRank");
+    api.CommInitRankConfigRaw = dlsym(api.handle, "ncclCommInitRankConfig");
     api.CommDestroy     = reinterpret_cast<int (*)(void*)>(dlsym(api.handle, "ncclCommDestroy"));
     api.AllReduce       = reinterpret_cast<int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t)>(
       dlsym(api.handle, "ncclAllReduce"));
@@ -240,7 +261,23 @@ int lbk_comm_init(lbk_context* ctx, const void* id, int rank, int n_ranks)
     using InitFn = int (*)(void**, int, UniqueId, int);  // ncclCommInitRank(comm*, nranks, id, rank)
     auto init    = reinterpret_cast<InitFn>(nccl().CommInitRankRaw);
     void* comm   = nullptr;
-    nccl_check(init(&comm, n_ranks, uid, rank), "ncclCommInitRank");
+    int rc       = -1;
+    if (nccl().CommInitRankConfigRaw != nullptr) {
+      using InitCfgFn = int (*)(void**, int, UniqueId, int, void*);  // ncclCommInitRankConfig(comm*, nranks, id, rank, config*)
+      NcclConfigPrefix cfg;
+      cfg.size           = sizeof(cfg);
+      cfg.magic          = 0xcafebeefu;
+      cfg.version        = 21800;       // NCCL_VERSION(2, 18, 0): the release this layout is from
+      cfg.blocking       = INT_MIN;     // NCCL_CONFIG_UNDEF_INT: the library's default
+      cfg.cgaClusterSize = INT_MIN;
+      cfg.minCTAs        = INT_MIN;
+      cfg.maxCTAs        = kCommMaxCtas;
+      cfg.netName        = nullptr;
+      cfg.splitShare     = INT_MIN;
+      rc = reinterpret_cast<InitCfgFn>(nccl().CommInitRankConfigRaw)(&comm, n_ranks, uid, rank, &cfg);
+      if (rc != 0) comm = nullptr;  // an NCCL that refuses the structure: every rank falls back alike
+    }
+    if (rc != 0) nccl_check(init(&comm, n_ranks, uid, rank), "ncclCommInitRank");
     ctx->nccl_comm = comm;
     ctx->owns_nccl = true;
     ctx->rank      = rank;
