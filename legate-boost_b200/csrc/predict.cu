@@ -89,7 +89,7 @@ __global__ void k_pack_trees(const TreePtrs* __restrict__ trees, int K, int F, i
 }
 
 // Bulk asynchronous copy global -> shared (the copy engine moves whole lines; nothing passes
-// through the load/store pipe), completion counted in bytes on an mbarrier.  No multicast.
+// through the load/store pipe), completion counted in bytes on an mbarrier; a plain copy into this block only.
 __device__ inline void MbarInit(unsigned bar, unsigned count)
 {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
