@@ -24,7 +24,7 @@ struct NcclApi {
   int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t)            = nullptr;
   const char* (*GetErrorString)(int)                                                     = nullptr;
   void* CommInitRankRaw                                                                  = nullptr;
-  void* CommInitRankConfigRaw                                                            = nullptr;
+  void* CommSplitRaw                                                                     = nullptr;
 };
 
 // The leading fields of ncclConfig_t as they have been since NCCL 2.18; the library reads `size`
@@ -40,10 +40,11 @@ struct NcclConfigPrefix {
   const char* netName;
   int splitShare;
 };
-// CTAs the library's own communicator may use per collective: the histogram kernel leaves 20 SMs
-// free while an all-reduce runs beside it (see BuildHistogramAllReduce); a collective that took
-// more would push histogram blocks into a second round.
-constexpr int kCommMaxCtas = 16;
+// CTAs the side communicator may use per collective: the histogram kernel leaves 20 SMs free while
+// an all-reduce runs beside it (see BuildHistogramAllReduce); a collective that took more would
+// push histogram blocks into a second round.  Collectives that run alone use the main
+// communicator with the library's own choice of CTAs.
+constexpr int kSideCommMaxCtas = 16;
 
 struct UniqueId {
   char bytes[LBK_UNIQUE_ID_BYTES];
@@ -62,7 +63,7 @@ NcclApi& nccl()
     if (!api.handle) return;
     api.GetUniqueId     = reinterpret_cast<int (*)(void*)>(dlsym(api.handle, "ncclGetUniqueId"));
     api.CommInitRankRaw = dlsym(api.handle, "ncclCommInitRank");
-    api.CommInitRankConfigRaw = dlsym(api.handle, "ncclCommInitRankConfig");
+    api.CommSplitRaw    = dlsym(api.handle, "ncclCommSplit");
     api.CommDestroy     = reinterpret_cast<int (*)(void*)>(dlsym(api.handle, "ncclCommDestroy"));
     api.AllReduce       = reinterpret_cast<int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t)>(
       dlsym(api.handle, "ncclAllReduce"));
@@ -131,7 +132,8 @@ void Scratch::free_one(void* p)
     }
 }
 
-void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream)
+void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream,
+               bool beside_kernel)
 {
   if (ctx->n_ranks <= 1 || count == 0) return;
   if (ctx->cb) {
@@ -141,7 +143,8 @@ void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_r
   }
   if (!ctx->nccl_comm) throw Error(LBK_ERR_COMM, "Expected a communicator for a multi-rank call.");
   require_nccl();
-  nccl_check(nccl().AllReduce(buf, buf, count, nccl_dtype(dtype), nccl_op(op), ctx->nccl_comm, stream), "ncclAllReduce");
+  void* comm = beside_kernel && ctx->nccl_comm_side ? ctx->nccl_comm_side : ctx->nccl_comm;
+  nccl_check(nccl().AllReduce(buf, buf, count, nccl_dtype(dtype), nccl_op(op), comm, stream), "ncclAllReduce");
 }
 
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream)
@@ -213,6 +216,7 @@ void lbk_context_destroy(lbk_context* ctx)
   if (!ctx) return;
   cudaSetDevice(ctx->device);
   cudaDeviceSynchronize();
+  if (ctx->nccl_comm_side && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm_side);
   if (ctx->owns_nccl && ctx->nccl_comm && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
@@ -261,9 +265,10 @@ int lbk_comm_init(lbk_context* ctx, const void* id, int rank, int n_ranks)
     using InitFn = int (*)(void**, int, UniqueId, int);  // ncclCommInitRank(comm*, nranks, id, rank)
     auto init    = reinterpret_cast<InitFn>(nccl().CommInitRankRaw);
     void* comm   = nullptr;
-    int rc       = -1;
-    if (nccl().CommInitRankConfigRaw != nullptr) {
-      using InitCfgFn = int (*)(void**, int, UniqueId, int, void*);  // ncclCommInitRankConfig(comm*, nranks, id, rank, config*)
+    nccl_check(init(&comm, n_ranks, uid, rank), "ncclCommInitRank");
+    void* side = nullptr;
+    if (n_ranks > 1 && nccl().CommSplitRaw != nullptr) {
+      using SplitFn = int (*)(void*, int, int, void**, void*);  // ncclCommSplit(comm, color, key, newcomm*, config*)
       NcclConfigPrefix cfg;
       cfg.size           = sizeof(cfg);
       cfg.magic          = 0xcafebeefu;
@@ -271,13 +276,13 @@ int lbk_comm_init(lbk_context* ctx, const void* id, int rank, int n_ranks)
       cfg.blocking       = INT_MIN;     // NCCL_CONFIG_UNDEF_INT: the library's default
       cfg.cgaClusterSize = INT_MIN;
       cfg.minCTAs        = INT_MIN;
-      cfg.maxCTAs        = kCommMaxCtas;
+      cfg.maxCTAs        = kSideCommMaxCtas;
       cfg.netName        = nullptr;
       cfg.splitShare     = INT_MIN;
-      rc = reinterpret_cast<InitCfgFn>(nccl().CommInitRankConfigRaw)(&comm, n_ranks, uid, rank, &cfg);
-      if (rc != 0) comm = nullptr;  // an NCCL that refuses the structure: every rank falls back alike
+      // every rank calls alike; an NCCL that refuses leaves every rank without a side communicator
+      if (reinterpret_cast<SplitFn>(nccl().CommSplitRaw)(comm, 0, rank, &side, &cfg) != 0) side = nullptr;
     }
-    if (rc != 0) nccl_check(init(&comm, n_ranks, uid, rank), "ncclCommInitRank");
+    ctx->nccl_comm_side = side;
     ctx->nccl_comm = comm;
     ctx->owns_nccl = true;
     ctx->rank      = rank;

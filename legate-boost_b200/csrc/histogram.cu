@@ -910,8 +910,9 @@ void BuildHistogramAllReduce(lbk_context* ctx, Scratch& s, const HistLevel& lv, 
     }
     LBK_CUDA(cudaEventRecord(ctx->ev_part[i], stream));
     LBK_CUDA(cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_part[i], 0));
+    // every part but the last has the next part's kernel beside it
     AllReduce(ctx, static_cast<unsigned char*>(lv.out) + static_cast<size_t>(s0) * slot_words * 8,
-              static_cast<size_t>(s1 - s0) * slot_words, dtype, LBK_SUM, ctx->comm_stream);
+              static_cast<size_t>(s1 - s0) * slot_words, dtype, LBK_SUM, ctx->comm_stream, i + 1 < parts);
   }
   ctx->profile = timed;
   LBK_CUDA(cudaEventRecord(ctx->ev_comm_done, ctx->comm_stream));

@@ -68,6 +68,7 @@ struct lbk_context {
   // communicator
   int rank = 0, n_ranks = 1;
   void* nccl_comm     = nullptr;
+  void* nccl_comm_side = nullptr;  // same ranks, few CTAs per collective: for all-reduces that run beside a kernel
   bool owns_nccl      = false;
   lbk_allreduce_fn cb = nullptr;
   void* cb_user       = nullptr;
@@ -105,7 +106,10 @@ class Scratch {
 };
 
 // In-place all-reduce over the context's communicator; no-op for a single rank.
-void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream);
+// `beside_kernel`: the collective shares the GPU with a kernel of ours; use the communicator that
+// is limited to a few CTAs, if there is one.
+void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream,
+               bool beside_kernel = false);
 // Reads the device status word (synchronises the stream) and throws LBK_ERR_DEVICE if set.
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream);
 
