@@ -243,10 +243,6 @@ __global__ void __launch_bounds__(256, sizeof(T) == 4 ? 4 : 2)
   const unsigned amask = active ? 0xffffffffu : 0u;
   constexpr unsigned kPitch = kGroup * sizeof(T);  // bytes from one proposal of a feature to the next
   const unsigned col_s      = static_cast<unsigned>(__cvta_generic_to_shared(sp + lane));
-  // proposals P/4 - 1, P/2 - 1, 3P/4 - 1 of the lane's feature: what the two top search levels probe
-  const T piv_lo  = kLog2P >= 2 ? sp[(P / 4 - 1) * kGroup + lane] : T(0);
-  const T piv_mid = kLog2P >= 2 ? sp[(P / 2 - 1) * kGroup + lane] : T(0);
-  const T piv_hi  = kLog2P >= 2 ? sp[(3 * P / 4 - 1) * kGroup + lane] : T(0);
   // rows are counted in 32 bits (row indices are 32-bit everywhere in this library)
   const int pitch   = static_cast<int>(gridDim.y) * kGroup;  // bins are row-major, rows padded to groups
   constexpr int U   = 8;  // rows per warp in flight
@@ -278,26 +274,15 @@ __global__ void __launch_bounds__(256, sizeof(T) == 4 ? 4 : 2)
       T x[U];
       unsigned pos[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) x[u] = xn[u];
+      for (int u = 0; u < U; ++u) {
+        x[u]   = xn[u];
+        pos[u] = col_s;
+      }
       {
         const int nb = sub + 1 < kSubs ? base + U : turn + hop;
         if (nb < n) load_rows(nb, xn);
       }
-      if (kLog2P >= 2) {
-        // the two top levels of the search against the lane's three pivots, which sit in registers
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const bool c1 = piv_mid < x[u];
-          const T p2    = c1 ? piv_hi : piv_lo;
-          pos[u]        = c1 ? col_s + (P / 2) * kPitch : col_s;
-          if (p2 < x[u]) pos[u] += (P / 4) * kPitch;
-        }
-        SearchLevels<T, U, kLog2P - 3, kPitch>::run(pos, x);
-      } else {
-#pragma unroll
-        for (int u = 0; u < U; ++u) pos[u] = col_s;
-        SearchLevels<T, U, kLog2P - 1, kPitch>::run(pos, x);
-      }
+      SearchLevels<T, U, kLog2P - 1, kPitch>::run(pos, x);
       unsigned id[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) id[u] = ((pos[u] - col_s) / kPitch) & amask;
