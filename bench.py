@@ -248,7 +248,8 @@ def run_hist(args):
 
     def step():
         stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, mode=mode, hist=hist, ctx=ctx,
-                         max_abs=max_abs if mode == 0 else None, all_reduce=world > 1)
+                         max_abs=max_abs if mode == 0 else None, all_reduce=world > 1, max_bins=HIST_BINS,
+                         total_bins=HIST_FEATURES * HIST_BINS)
 
     for _ in range(max(args.warmup, 3)):
         step()

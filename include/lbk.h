@@ -218,6 +218,10 @@ typedef struct lbk_histogram_args {
   int32_t host_buffers;
   const int32_t* max_abs;   /* mode 0, optional: device int32[2] = largest |grad|, |hess| in gpair (the
                                call bounds its 32-bit partial sums with it); NULL = found by the call */
+  int32_t max_bins;         /* optional, device buffers only: an upper bound of the bins of any one
+                               feature (max of row_ptr[f+1] - row_ptr[f]); with it the call does not
+                               read row_ptr back and nothing waits before the kernels are queued.
+                               0 = found by the call.  A bound that is too small gives wrong sums. */
   int32_t all_reduce;       /* 1: hist is summed over the ranks of the context's communicator before
                                the call returns (the nodes are cut into parts so that the sum of
                                one part travels while the next part is built) */

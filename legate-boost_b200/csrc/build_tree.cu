@@ -495,13 +495,17 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
       LBK_CUDA(cudaMemcpyAsync(d_idx, row_index, sizeof(int32_t) * n_idx, cudaMemcpyHostToDevice, stream));
       LBK_CUDA(cudaMemcpyAsync(d_seg, seg, sizeof(int32_t) * (a->n_nodes + 1), cudaMemcpyHostToDevice, stream));
       bins = d_bins; row_ptr = d_rp; gp = d_gp; row_index = d_idx; seg = d_seg; hist = d_hist;
-    } else {
+    } else if (a->max_bins <= 0) {
       LBK_CUDA(cudaMemcpyAsync(rp.data(), row_ptr, sizeof(int32_t) * (F + 1), cudaMemcpyDeviceToHost, stream));
       LBK_CUDA(cudaStreamSynchronize(stream));
     }
-    LBK_EXPECT(rp[F] == B, "total_bins does not match row_ptr");
     int mb = 1;
-    for (int f = 0; f < F; ++f) mb = std::max(mb, rp[f + 1] - rp[f]);
+    if (!a->host_buffers && a->max_bins > 0) {
+      mb = a->max_bins;  // the caller vouches for it: row_ptr stays on the device, no wait before the launch
+    } else {
+      LBK_EXPECT(rp[F] == B, "total_bins does not match row_ptr");
+      for (int f = 0; f < F; ++f) mb = std::max(mb, rp[f + 1] - rp[f]);
+    }
     LBK_EXPECT(a->bin_bytes == 2 || mb <= 256, "one-byte bins need <= 256 proposals per feature");
     LBK_CUDA(cudaMemsetAsync(hist, 0, hist_bytes, stream));
     lbk::HistLevel lv;

@@ -66,7 +66,7 @@ class HistogramArgs(C.Structure):
         ("gpair", C.c_void_p), ("gpair_f32", C.c_void_p), ("n_outputs", C.c_int32),
         ("row_index", C.c_void_p), ("seg", C.c_void_p), ("n_nodes", C.c_int32),
         ("mode", C.c_int32), ("hist", C.c_void_p), ("stream", C.c_void_p),
-        ("host_buffers", C.c_int32), ("max_abs", C.c_void_p), ("all_reduce", C.c_int32),
+        ("host_buffers", C.c_int32), ("max_abs", C.c_void_p), ("max_bins", C.c_int32), ("all_reduce", C.c_int32),
     ]
 
 

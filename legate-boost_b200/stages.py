@@ -82,7 +82,7 @@ def group_rows(node_of_row, node_begin, n_nodes, ctx=None):
 
 
 def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=None, ctx=None, host=False,
-              max_abs=None, all_reduce=False):
+              max_abs=None, all_reduce=False, max_bins=0, total_bins=None):
     """Histogram [n_nodes, K, B, 2] (int64 for mode 0, float64 for mode 1) of node-grouped rows.
 
     ``host=True`` takes CPU tensors and lets the library do the copies (the end-to-end path)."""
@@ -91,7 +91,7 @@ def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=Non
     N = bins.shape[0]
     K = gpair.shape[1]
     n_nodes = seg.shape[0] - 1
-    B = int(row_ptr[-1])
+    B = int(row_ptr[-1]) if total_bins is None else int(total_bins)
     if hist is None:
         hist = torch.empty((n_nodes, K, B, 2), dtype=torch.int64 if mode == 0 else torch.float64, device=dev,
                            pin_memory=host)
@@ -109,5 +109,6 @@ def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=Non
     a.host_buffers = 1 if host else 0
     a.max_abs = max_abs.data_ptr() if max_abs is not None else None
     a.all_reduce = 1 if all_reduce else 0
+    a.max_bins = int(max_bins)
     ctx.check(ctx.lib.lbk_histogram(ctx.handle, C.byref(a)))
     return hist
