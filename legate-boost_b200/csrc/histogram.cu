@@ -109,6 +109,7 @@ __global__ void k_max_abs(const int2* __restrict__ gpair, int64_t n, int* __rest
 // group, output); candidates that need more slots than `slot_capacity` are not considered, and
 // plan[6] says whether the chosen cut can use the slots (1) or has to flush with atomics (0).
 constexpr int kPlanCandidates = 64;
+constexpr int kPlanCachedNodes = 4096;
 constexpr int kOverheadSingle = 2000;  // rows a block could have processed while it clears and flushes with stores
 constexpr int kOverheadMulti  = 5000;  // the same for clear + partial store + its share of the final sum (measured)
 
@@ -126,14 +127,21 @@ __global__ void __launch_bounds__(1024)
   __shared__ double cand_cost[kPlanCandidates];
   __shared__ int cand_ch[kPlanCandidates];
   __shared__ int cand_fit[kPlanCandidates];
+  __shared__ int rows_s[kPlanCachedNodes];  // rows of the first nodes (0 for nodes that are not built)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
-  auto rows_of = [&](int j) -> int {
+  auto rows_global = [&](int j) -> int {
     const bool built = slot_of_node == nullptr || slot_of_node[j] >= 0;
     const int r      = seg[j + 1] - seg[j];
     return built ? r : 0;
   };
+  // every later pass reads the node sizes many times: from shared memory where they fit
+  auto rows_of = [&](int j) -> int { return j < kPlanCachedNodes ? rows_s[j] : rows_global(j); };
   long long rows = 0;
-  for (int j = tid; j < n_nodes; j += blockDim.x) rows += rows_of(j);
+  for (int j = tid; j < n_nodes; j += blockDim.x) {
+    const int r = rows_global(j);
+    if (j < kPlanCachedNodes) rows_s[j] = r;
+    rows += r;
+  }
   for (int off = 16; off >= 1; off >>= 1) rows += __shfl_down_sync(0xffffffffu, rows, off);
   if (lane == 0) red[warp] = rows;
   __syncthreads();
