@@ -158,6 +158,37 @@ typedef struct lbk_predict_args {
 int lbk_predict(lbk_context* ctx, const lbk_predict_args* args);
 
 /* ------------------------------------------------------------------------------------------
+ * UPDATE_TREE: a tree keeps its structure (feature, split_value) and gets new leaf values and
+ * hessians from new gradients (reference: update_tree_fn, src/models/tree/update_tree.cc:36-134,
+ * launched by Tree.update, legateboost/models/tree.py:197-240; the reference has a CPU variant
+ * only).  Every row adds its (g, h) to every node on its path; the sums are added over the ranks of
+ * the context's communicator; leaf = H > 0 ? -softthreshold(G, l1) / (H + l2) : 0, hessian = H.
+ * Device pointers.  Float64 sums in another order than the reference's row loop: equal within
+ * rounding, not bit for bit.
+ */
+typedef struct lbk_update_tree_args {
+  const void* X;       /* [n_local_rows, n_features], row stride ldx elements */
+  int32_t x_dtype;
+  int64_t ldx;
+  const double* g;     /* [n_local_rows, n_outputs], row stride ldg */
+  const double* h;
+  int64_t ldg;
+  int64_t n_local_rows;
+  int32_t n_features;
+  int32_t n_outputs;
+  int32_t max_nodes;
+  const int32_t* feature;     /* [max_nodes], -1 = leaf */
+  const double* split_value;  /* [max_nodes] */
+  double l1_regularization;
+  double l2_regularization;
+  double* leaf_value;  /* out [max_nodes, n_outputs] */
+  double* hessian;     /* out [max_nodes, n_outputs] */
+  void* stream;        /* the call returns after the stream has drained */
+} lbk_update_tree_args;
+
+int lbk_update_tree(lbk_context* ctx, const lbk_update_tree_args* args);
+
+/* ------------------------------------------------------------------------------------------
  * Stage-level entry points.  They expose the steps of BUILD_TREE separately so each can be
  * checked and timed on its own; lbk_build_tree runs the same kernels.
  */

@@ -19,7 +19,7 @@ UNIQUE_ID_BYTES = 128
 EXPORTS = [
     "lbk_version", "lbk_context_create", "lbk_context_destroy", "lbk_last_error", "lbk_context_trim",
     "lbk_comm_unique_id", "lbk_comm_init", "lbk_comm_attach_nccl", "lbk_comm_set_callback",
-    "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_leaf_values", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
+    "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_leaf_values", "lbk_update_tree", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
     "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_histogram_noalloc", "lbk_group_rows",
 ]
 
@@ -45,6 +45,17 @@ class BuildTreeArgs(C.Structure):
         ("stream", C.c_void_p), ("host_buffers", C.c_int32),
         ("trace_node_sums", C.c_void_p), ("trace_hist", C.c_void_p), ("trace_nodes", C.c_int32),
         ("out_total_bins", C.POINTER(C.c_int32)), ("out_leaf", C.c_void_p),
+    ]
+
+
+class UpdateTreeArgs(C.Structure):
+    _fields_ = [
+        ("X", C.c_void_p), ("x_dtype", C.c_int32), ("ldx", C.c_int64),
+        ("g", C.c_void_p), ("h", C.c_void_p), ("ldg", C.c_int64),
+        ("n_local_rows", C.c_int64), ("n_features", C.c_int32), ("n_outputs", C.c_int32),
+        ("max_nodes", C.c_int32), ("feature", C.c_void_p), ("split_value", C.c_void_p),
+        ("l1_regularization", C.c_double), ("l2_regularization", C.c_double),
+        ("leaf_value", C.c_void_p), ("hessian", C.c_void_p), ("stream", C.c_void_p),
     ]
 
 

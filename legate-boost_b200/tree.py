@@ -257,8 +257,35 @@ class Tree(BaseModel):
         self.leaf_value.fill_(0)
         self.hessian.fill_(0)
 
-    def update(self, X, g, h) -> "Tree":
-        raise NotImplementedError("the UPDATE_TREE task is outside the tree-building hot path")
+    def update(self, X: torch.Tensor, g: torch.Tensor, h: torch.Tensor) -> "Tree":
+        """New leaf values and hessians from new gradients, the structure stays (reference:
+        Tree.update, legateboost/models/tree.py:197-240 -> UPDATE_TREE)."""
+        assert X.is_cuda and g.is_cuda and h.is_cuda, "inputs must be CUDA tensors (no CPU fallback)"
+        if g.dim() == 1:
+            g, h = g[:, None], h[:, None]
+        assert g.dtype == torch.float64 and h.dtype == torch.float64
+        if X.stride(1) != 1 and X.shape[0] > 0:
+            X = X.contiguous()
+        g, h = g.contiguous(), h.contiguous()
+        N, F = X.shape
+        K = g.shape[1]
+        ctx = L.init_distributed(X.device.index)
+        leaf_value = torch.empty_like(self.leaf_value)
+        hessian = torch.empty_like(self.hessian)
+        a = L.UpdateTreeArgs()
+        a.X, a.x_dtype, a.ldx = X.data_ptr(), _dtype_code(X), X.stride(0) if N > 0 else F
+        a.g, a.h, a.ldg = g.data_ptr(), h.data_ptr(), K
+        a.n_local_rows, a.n_features, a.n_outputs = N, F, K
+        a.max_nodes = self.feature.shape[0]
+        a.feature, a.split_value = self.feature.data_ptr(), self.split_value.data_ptr()
+        a.l1_regularization, a.l2_regularization = self.l1_regularization, self.l2_regularization
+        a.leaf_value, a.hessian = leaf_value.data_ptr(), hessian.data_ptr()
+        a.stream = _stream_ptr()
+        with torch.cuda.device(X.device):
+            ctx.check(ctx.lib.lbk_update_tree(ctx.handle, C.byref(a)))
+        self.leaf_value, self.hessian = leaf_value, hessian
+        self._fit_rows = None
+        return self
 
     def predict(self, X: torch.Tensor) -> torch.Tensor:
         fit_rows, self._fit_rows = getattr(self, "_fit_rows", None), None

@@ -856,6 +856,43 @@ void Predict(const T* X,
 
 }  // namespace
 
+// UPDATE_TREE (reference: update_tree_fn, src/models/tree/update_tree.cc:36-134): the structure of
+// a tree stays, its statistics are recomputed from new gradients.  Every row walks from the root
+// (at most 100 levels) and adds its (g, h) to every node it visits, the leaf included; per rank the
+// rows are taken in order and the sums are float64; the ranks' sums are added in rank order (the
+// reference's two all-reduces); then leaf = H > 0 ? CalculateLeafValue(G, H) : 0, hessian = H.
+template <typename T>
+void UpdateTree(const T* X, int64_t n_rows, int F, int K, const double* g, const double* h, int max_nodes,
+                const int32_t* feature, const double* split_value, double l1, double l2, int n_ranks,
+                const int64_t* rank_off, double* leaf_value, double* hessian)
+{
+  const size_t MK = static_cast<size_t>(max_nodes) * K;
+  std::vector<double> G(MK, 0.0), H(MK, 0.0);
+  for (int r = 0; r < n_ranks; ++r) {
+    std::vector<double> lg(MK, 0.0), lh(MK, 0.0);
+    for (int64_t i = rank_off[r]; i < rank_off[r + 1]; ++i) {
+      int pos = 0;
+      for (int depth = 0; depth < 100; ++depth) {
+        for (int k = 0; k < K; ++k) {
+          lg[static_cast<size_t>(pos) * K + k] += g[i * K + k];
+          lh[static_cast<size_t>(pos) * K + k] += h[i * K + k];
+        }
+        if (feature[pos] == -1) break;
+        const T x = X[i * F + feature[pos]];
+        pos       = x <= split_value[pos] ? pos * 2 + 1 : pos * 2 + 2;
+      }
+    }
+    for (size_t e = 0; e < MK; ++e) {
+      G[e] += lg[e];
+      H[e] += lh[e];
+    }
+  }
+  for (size_t e = 0; e < MK; ++e) {
+    leaf_value[e] = H[e] > 0.0 ? CalculateLeafValue(G[e], H[e], l1, l2) : 0.0;
+    hessian[e]    = H[e];
+  }
+}
+
 extern "C" {
 
 int lbo_build_tree(const lbo_tree_args* a)
@@ -879,6 +916,23 @@ void lbo_predict(const void* X,
     Predict(static_cast<const double*>(X), n_rows, F, K, n_trees, leaf, feat, split, pred);
   else
     Predict(static_cast<const float*>(X), n_rows, F, K, n_trees, leaf, feat, split, pred);
+}
+
+void lbo_update_tree(const void* X, int x_is_f64, int64_t n_rows, int F, int K, const double* g, const double* h,
+                     int max_nodes, const int32_t* feature, const double* split_value, double l1, double l2,
+                     int n_ranks, const int64_t* rank_off, double* leaf_value, double* hessian)
+{
+  std::vector<int64_t> one = {0, n_rows};
+  if (n_ranks <= 0) {
+    n_ranks  = 1;
+    rank_off = one.data();
+  }
+  if (x_is_f64)
+    UpdateTree(static_cast<const double*>(X), n_rows, F, K, g, h, max_nodes, feature, split_value, l1, l2, n_ranks,
+               rank_off, leaf_value, hessian);
+  else
+    UpdateTree(static_cast<const float*>(X), n_rows, F, K, g, h, max_nodes, feature, split_value, l1, l2, n_ranks,
+               rank_off, leaf_value, hessian);
 }
 
 // Stage-level entry points ----------------------------------------------------------------

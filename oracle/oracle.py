@@ -184,6 +184,51 @@ def predict(X, trees):
     return pred
 
 
+_REF_UPDATE = None
+
+
+def ref_update_lib():
+    """The reference's own UPDATE_TREE task body (stub-compiled), or None when it has not been built."""
+    global _REF_UPDATE
+    if _REF_UPDATE is None:
+        path = os.path.join(_HERE, "_ref", "libref_update.so")
+        if not os.path.exists(path):
+            return None
+        _REF_UPDATE = C.CDLL(path)
+    return _REF_UPDATE
+
+
+def update_tree(X, g, h, feature, split_value, l1=0.0, l2=1.0, n_ranks=1, use_reference=False):
+    """New (leaf_value, hessian), both (M, K) float64, of a tree whose structure stays
+    (reference: update_tree.cc:36-134).  ``use_reference`` runs the stub-compiled reference task."""
+    X = np.ascontiguousarray(X)
+    g = np.ascontiguousarray(g, dtype=np.float64)
+    h = np.ascontiguousarray(h, dtype=np.float64)
+    if g.ndim == 1:
+        g, h = g[:, None], h[:, None]
+    N, F = X.shape
+    K = g.shape[1]
+    feature = np.ascontiguousarray(feature, dtype=np.int32)
+    split_value = np.ascontiguousarray(split_value, dtype=np.float64)
+    M = feature.shape[0]
+    leaf = np.zeros((M, K))
+    hess = np.zeros((M, K))
+    if use_reference:
+        rl = ref_update_lib()
+        assert rl is not None, "build it with make -C oracle ref"
+        assert n_ranks == 1
+        rc = rl.ref_update_tree_cpu(C.c_int(int(X.dtype == np.float64)), _ptr(X), _ptr(g), _ptr(h), C.c_int64(N),
+                                    C.c_int(F), C.c_int(K), C.c_int(M), _ptr(feature), _ptr(split_value),
+                                    C.c_double(l1), C.c_double(l2), _ptr(leaf), _ptr(hess))
+        assert rc == 0
+        return leaf, hess
+    off = _rank_off(N, n_ranks)
+    lib().lbo_update_tree(_ptr(X), C.c_int(int(X.dtype == np.float64)), C.c_int64(N), C.c_int(F), C.c_int(K),
+                          _ptr(g), _ptr(h), C.c_int(M), _ptr(feature), _ptr(split_value), C.c_double(l1),
+                          C.c_double(l2), C.c_int(n_ranks), _ptr(off), _ptr(leaf), _ptr(hess))
+    return leaf, hess
+
+
 def split_proposals(X, split_samples, seed, mode="Q", n_ranks=1):
     X = np.ascontiguousarray(X)
     N, F = X.shape

@@ -73,6 +73,38 @@ struct Rect {
     return v;
   }
 };
+// Row-major walk over the points of a rectangle (the last dimension moves fastest).
+template <int N, typename T = coord_t>
+class PointInRectIterator {
+ public:
+  explicit PointInRectIterator(const Rect<N, T>& r) : rect_(r), p_(r.lo), valid_(!r.empty()) {}
+  bool valid() const { return valid_; }
+  const Point<N, T>& operator*() const { return p_; }
+  PointInRectIterator& operator++()
+  {
+    for (int d = N - 1; d >= 0; --d) {
+      if (p_[d] < rect_.hi[d]) {
+        ++p_[d];
+        return *this;
+      }
+      p_[d] = rect_.lo[d];
+    }
+    valid_ = false;
+    return *this;
+  }
+  PointInRectIterator operator++(int)
+  {
+    PointInRectIterator t = *this;
+    ++(*this);
+    return t;
+  }
+
+ private:
+  Rect<N, T> rect_;
+  Point<N, T> p_;
+  bool valid_;
+};
+
 template <int N, typename T>
 std::ostream& operator<<(std::ostream& os, const Rect<N, T>& r)
 {

@@ -1,10 +1,10 @@
-"""Generates tests/golden/tree_*.npz: seeded inputs together with the tree arrays and predictions
-that the REFERENCE's own CPU code produces for them.
+"""Generates tests/golden/tree_*.npz: seeded inputs together with the tree arrays, the predictions and
+the result of an update with new gradients that the REFERENCE's own CPU code produces for them.
 
 The reference's Python package cannot be imported without its runtime, so the vectors come from its
-unmodified build_tree.cc / predict.cc compiled against a host-only stand-in of the runtime headers
-(``make -C oracle ref`` -> oracle/_ref/libref_cpu.so, only possible where the reference source tree
-is present).  Run from the repository root:  python tests/golden/make_golden.py
+unmodified build_tree.cc / predict.cc / update_tree.cc compiled against a host-only stand-in of the
+runtime headers (``make -C oracle ref`` -> oracle/_ref/libref_cpu.so, libref_update.so, only possible
+where the reference source tree is present).  Run from the repository root:  python tests/golden/make_golden.py
 """
 import ctypes as C
 import os
@@ -50,10 +50,15 @@ def main():
                 C.c_int(K), C.c_int(T), mn, PP(t.leaf_value.ctypes.data), PP(t.feature.ctypes.data),
                 PP(t.split_value.ctypes.data), pred.ctypes.data_as(C.c_void_p))
         assert rc == 0
+        # the same tree updated with new gradients by the reference's update_tree.cc
+        g2 = rs.normal(size=(N, K))
+        h2 = rs.random((N, K)) + 0.1
+        upd_leaf, upd_hess = O.update_tree(X, g2, h2, t.feature, t.split_value, l1=l1, l2=l2, use_reference=True)
         np.savez_compressed(os.path.join(out_dir, "tree_%s.npz" % name), X=X, g=g, h=h, max_depth=D,
                             split_samples=S, seed=seed, l1=l1, l2=l2, min_split_gain=msg,
                             leaf_value=t.leaf_value, feature=t.feature, split_value=t.split_value,
-                            gain=t.gain, hessian=t.hessian, pred=pred)
+                            gain=t.gain, hessian=t.hessian, pred=pred, g2=g2, h2=h2,
+                            upd_leaf_value=upd_leaf, upd_hessian=upd_hess)
         print("wrote", name, "split nodes:", int((t.feature >= 0).sum()))
 
 

@@ -448,3 +448,37 @@ def test_full_size_tree_properties(lb):
     split = np.nonzero(feature >= 0)[0]
     assert len(split) > 100
     assert np.allclose(hess[2 * split + 1] + hess[2 * split + 2], hess[split], rtol=1e-12, atol=0)
+
+
+@pytest.mark.parametrize("dtype,K,D,l1,l2", [(np.float32, 1, 6, 0.0, 1.0), (np.float64, 3, 5, 0.3, 0.5),
+                                               (np.float32, 12, 8, 0.0, 1.0)])
+def test_update_tree_matches_oracle(lb, oracle, dtype, K, D, l1, l2):
+    """Tree.update (UPDATE_TREE): new leaf values and hessians for an unchanged structure.  Float64
+    sums in another order than the reference's row loop: 1e-10 relative, hessians included; nodes
+    no row reaches get 0."""
+    rs = np.random.RandomState(17)
+    N, F = 20000, 15
+    X = rs.random((N, F)).astype(dtype)
+    g = rs.normal(size=(N, K))
+    h = rs.random((N, K)) + 0.1
+    t = lb.Tree(max_depth=D, split_samples=64, l1_regularization=l1, l2_regularization=l2)
+    t.set_random_state(np.random.RandomState(4)).fit(dev(X), dev(g), dev(h))
+    feature, split = t.feature.cpu().numpy(), t.split_value.cpu().numpy()
+    old_leaf = t.leaf_value.clone()
+    g2 = rs.normal(size=(N, K))
+    h2 = (rs.random((N, K)) + 0.05) * (rs.random((N, K)) > 0.2)   # some zero hessians
+    sub = slice(0, N // 3)                                         # fewer rows: some nodes stay empty
+    want_leaf, want_hess = oracle.update_tree(X[sub], g2[sub], h2[sub], feature, split, l1=l1, l2=l2)
+    t.update(dev(X[sub]), dev(g2[sub]), dev(h2[sub]))
+    assert torch.equal(t.feature.cpu(), torch.from_numpy(feature))
+    got_leaf, got_hess = t.leaf_value.cpu().numpy(), t.hessian.cpu().numpy()
+    assert np.allclose(got_hess, want_hess, rtol=1e-10, atol=1e-12)
+    assert np.allclose(got_leaf, want_leaf, rtol=1e-9, atol=1e-12)
+    assert not np.array_equal(got_leaf, old_leaf.cpu().numpy())
+    assert np.array_equal(got_leaf == 0.0, want_leaf == 0.0)
+    # the updated tree predicts with the new values
+    pred = t.predict(dev(X[:100]))
+    assert np.allclose(pred.cpu().numpy(), oracle.predict(X[:100], [(got_leaf, feature, split)]), rtol=0, atol=0)
+    # an empty shard keeps every node at zero
+    t.update(dev(X[:0]), dev(g2[:0]), dev(h2[:0]))
+    assert not t.leaf_value.any() and not t.hessian.any()

@@ -170,6 +170,26 @@ def test_mode_d_matches_reference_build(oracle, case):
         assert np.array_equal(getattr(a, f), getattr(b, f)), f
 
 
+def test_update_tree_matches_reference_build(oracle):
+    """Bit-for-bit against the reference's own update_tree.cc (stub-compiled); two simulated ranks
+    agree with one within rounding."""
+    if oracle.ref_update_lib() is None:
+        pytest.skip("oracle/_ref/libref_update.so not built here")
+    rs = np.random.RandomState(5)
+    for dt, K in ((np.float32, 1), (np.float64, 4)):
+        X = rs.random((2500, 12)).astype(dt)
+        g = rs.normal(size=(2500, K))
+        h = rs.random((2500, K)) + 0.1
+        t = oracle.build_tree(X, g, h, max_depth=6, split_samples=64, seed=9, mode="D")
+        g2 = rs.normal(size=(2500, K))
+        h2 = rs.random((2500, K)) * (rs.random((2500, K)) > 0.3)  # some zero hessians
+        a = oracle.update_tree(X, g2, h2, t.feature, t.split_value, l1=0.2, l2=0.7)
+        b = oracle.update_tree(X, g2, h2, t.feature, t.split_value, l1=0.2, l2=0.7, use_reference=True)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+        c = oracle.update_tree(X, g2, h2, t.feature, t.split_value, l1=0.2, l2=0.7, n_ranks=2)
+        assert np.allclose(c[0], a[0], rtol=1e-10, atol=1e-12) and np.allclose(c[1], a[1], rtol=1e-12)
+
+
 def test_golden_vectors(oracle):
     """Committed outputs of the reference CPU build (tests/golden/make_golden.py)."""
     files = sorted(glob.glob(os.path.join(HERE, "golden", "tree_*.npz")))
@@ -184,3 +204,8 @@ def test_golden_vectors(oracle):
             assert np.array_equal(getattr(t, f), z[f]), (path, f)
         p = oracle.predict(z["X"], [tree_tuple(t)])
         assert np.array_equal(p, z["pred"]), path
+        # UPDATE_TREE with new gradients: same row order, same sums, bit for bit
+        leaf, hess = oracle.update_tree(z["X"], z["g2"], z["h2"], t.feature, t.split_value, l1=float(z["l1"]),
+                                        l2=float(z["l2"]))
+        assert np.array_equal(leaf, z["upd_leaf_value"]), path
+        assert np.array_equal(hess, z["upd_hessian"]), path
