@@ -426,13 +426,50 @@ def run_predict(args):
                                    "peak_source": which}}), flush=True)
 
 
+def run_update(args):
+    """UPDATE_TREE rows per second: one tree of depth args.depth grown on the data, then updated
+    with new gradients (the structure stays).  Algorithmic bytes per row: F * 4 (X) + 16 (g, h)."""
+    import numpy as np
+    import torch
+
+    import legateboost_b200 as lb
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(6)
+    n, F, D = args.rows, args.features, args.depth
+    X = torch.rand((n, F), dtype=torch.float32, device=device, generator=gen)
+    g = torch.randn((n, 1), dtype=torch.float64, device=device, generator=gen)
+    h = torch.ones((n, 1), dtype=torch.float64, device=device)
+    t = lb.Tree(max_depth=D).set_random_state(np.random.RandomState(0)).fit(X, g, h)
+    g2 = torch.randn((n, 1), dtype=torch.float64, device=device, generator=gen)
+    for _ in range(max(args.warmup, 1)):
+        t.update(X, g2, h)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        t.update(X, g2, h)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    peak, which = measured_peaks()
+    gbs = n * (F * 4 + 16) / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "update_tree rows/s", "value": n / (ms * 1e-3), "unit": "rows/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+                      "dtype": "f64", "data": "synthetic",
+                      "config": {"workload": "update of one tree of depth %d, %d rows x %d features" % (D, n, F)},
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                   "peak_source": which}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="hist", choices=["hist", "train", "predict"])
+    ap.add_argument("--workload", default="hist", choices=["hist", "train", "predict", "update"])
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--features", type=int, default=64)
     ap.add_argument("--depth", type=int, default=8)
@@ -449,6 +486,9 @@ def main():
     if args.workload == "train":
         args.rows = args.rows or 10_000_000
         return run_train(args)
+    if args.workload == "update":
+        args.rows = args.rows or 10_000_000
+        return run_update(args)
     args.rows = args.rows or 5_000_000
     return run_predict(args)
 
