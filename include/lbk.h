@@ -158,6 +158,19 @@ typedef struct lbk_predict_args {
 int lbk_predict(lbk_context* ctx, const lbk_predict_args* args);
 
 /* ------------------------------------------------------------------------------------------
+ * Weighted gradients of a boosting round in one pass (reference: LBBase._get_weighted_gradient,
+ * legateboost/legateboost.py:189-224, with unit sample weights and no subsampling, over
+ * SquaredErrorObjective / LogLossObjective transform + gradient, legateboost/objectives.py:131-135,
+ * 489-512): g = d loss / d raw prediction * learning_rate, h = max(second derivative, 1e-8).
+ * raw_pred, g, h: float64 [n_rows, n_outputs]; y: float64 [n_rows, n_outputs] for squared error,
+ * class index [n_rows] for log loss (0/1 when n_outputs == 1).  Device pointers, asynchronous on
+ * `stream`.
+ */
+enum { LBK_SQUARED_ERROR = 0, LBK_LOG_LOSS = 1 };
+int lbk_gradient(lbk_context* ctx, int objective, const double* raw_pred, const double* y, int64_t n_rows,
+                 int n_outputs, double learning_rate, double* g, double* h, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * UPDATE_TREE: a tree keeps its structure (feature, split_value) and gets new leaf values and
  * hessians from new gradients (reference: update_tree_fn, src/models/tree/update_tree.cc:36-134,
  * launched by Tree.update, legateboost/models/tree.py:197-240; the reference has a CPU variant

@@ -15,6 +15,7 @@ from typing import List, Optional
 import numpy as np
 import torch
 
+from . import library as L
 from .tree import Tree, _row_layout
 
 
@@ -27,6 +28,8 @@ def _all_sum(t: torch.Tensor) -> torch.Tensor:
 
 
 class _SquaredError:
+    code = 0  # LBK_SQUARED_ERROR
+
     def gradient(self, y, pred):
         return pred - y, torch.ones_like(pred)
 
@@ -45,6 +48,8 @@ class _SquaredError:
 
 
 class _LogLoss:
+    code = 1  # LBK_LOG_LOSS
+
     def gradient(self, y, pred):
         if pred.shape[1] == 1:
             return pred - y, pred * (1.0 - pred)
@@ -115,6 +120,24 @@ class _LBBase:
             raise ValueError("Number of labels does not match number of samples.")
         return X, y
 
+    def _weighted_gradient(self, y, raw_pred):
+        """g * learning_rate and h floored at 1e-8 at the current raw prediction, in one pass over the
+        rows (`lbk_gradient`; reference: `_get_weighted_gradient`, legateboost.py:189-224)."""
+        code = getattr(self._obj, "code", None)
+        if code is None:  # an objective the library has no kernel for
+            g, h = self._obj.gradient(y, self._obj.transform(raw_pred))
+            return g * self.learning_rate, torch.clamp(h, min=1e-8)
+        raw_pred = raw_pred.contiguous()
+        y = y.contiguous()
+        g = torch.empty_like(raw_pred)
+        h = torch.empty_like(raw_pred)
+        ctx = L.context(raw_pred.device.index)
+        with torch.cuda.device(raw_pred.device):
+            ctx.check(ctx.lib.lbk_gradient(ctx.handle, code, raw_pred.data_ptr(), y.data_ptr(), raw_pred.shape[0],
+                                           raw_pred.shape[1], float(self.learning_rate), g.data_ptr(), h.data_ptr(),
+                                           torch.cuda.current_stream().cuda_stream))
+        return g, h
+
     def fit(self, X, y):
         X, y = self._check(X, y)
         if not isinstance(self.base_models, tuple) or len(self.base_models) == 0:
@@ -129,9 +152,7 @@ class _LBBase:
         train_pred = self.model_init_.repeat(X.shape[0], 1)
         layout = _row_layout(X.shape[0])  # this rank's block of rows: the same for every tree
         for i in range(self.n_estimators):
-            g, h = self._obj.gradient(y, self._obj.transform(train_pred))
-            g = g * self.learning_rate
-            h = torch.clamp(h, min=1e-8)
+            g, h = self._weighted_gradient(y, train_pred)
             tree = deepcopy(self.base_models[i % len(self.base_models)]).set_random_state(self.random_state_)
             tree.row_layout = layout
             tree.fit(X, g, h)

@@ -19,7 +19,7 @@ UNIQUE_ID_BYTES = 128
 EXPORTS = [
     "lbk_version", "lbk_context_create", "lbk_context_destroy", "lbk_last_error", "lbk_context_trim",
     "lbk_comm_unique_id", "lbk_comm_init", "lbk_comm_attach_nccl", "lbk_comm_set_callback",
-    "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_leaf_values", "lbk_update_tree", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
+    "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
     "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_histogram_noalloc", "lbk_group_rows",
 ]
 
@@ -126,6 +126,9 @@ def load():
                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
             lib.lbk_leaf_values.argtypes = [
                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]
+            lib.lbk_gradient.argtypes = [
+                C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_double, C.c_void_p, C.c_void_p,
+                C.c_void_p]
             lib.lbk_group_rows.argtypes = [
                 C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
             _lib = lib

@@ -482,3 +482,35 @@ def test_update_tree_matches_oracle(lb, oracle, dtype, K, D, l1, l2):
     # an empty shard keeps every node at zero
     t.update(dev(X[:0]), dev(g2[:0]), dev(h2[:0]))
     assert not t.leaf_value.any() and not t.hessian.any()
+
+
+def test_weighted_gradient_kernels_match_the_array_formulas(lb):
+    """lbk_gradient against the reference's chain of array operations (objectives.py:131-135, 489-512,
+    legateboost.py:189-224), evaluated with numpy: squared error bit for bit, log loss within the last
+    bits of exp / division."""
+    from legateboost_b200 import estimator as E
+
+    rs = np.random.RandomState(8)
+    N = 5000
+    est = lb.LBRegressor(learning_rate=0.3)
+    est._obj = E._SquaredError()
+    raw, y = rs.normal(size=(N, 3)), rs.normal(size=(N, 3))
+    g, h = est._weighted_gradient(dev(y), dev(raw))
+    assert np.array_equal(g.cpu().numpy(), (raw - y) * 0.3) and np.array_equal(h.cpu().numpy(), np.ones((N, 3)))
+    est._obj = E._LogLoss()
+    raw, y = rs.normal(size=(N, 1)) * 4, rs.randint(0, 2, size=(N, 1)).astype(np.float64)
+    g, h = est._weighted_gradient(dev(y), dev(raw))
+    p = 1.0 / (1.0 + np.exp(-raw))
+    assert np.allclose(g.cpu().numpy(), (p - y) * 0.3, rtol=1e-13, atol=1e-16)
+    assert np.allclose(h.cpu().numpy(), np.maximum(p * (1 - p), 1e-8), rtol=1e-13)
+    for K in (3, 10, 40):
+        raw, y = rs.normal(size=(N, K)) * 5, rs.randint(0, K, size=(N, 1)).astype(np.float64)
+        raw[0] = 800.0 * np.arange(K)  # far apart: hessians hit the floor
+        g, h = est._weighted_gradient(dev(y), dev(raw))
+        e = np.exp(raw - raw.max(axis=1, keepdims=True))
+        p = e / e.sum(axis=1, keepdims=True)
+        want_g = p.copy()
+        want_g[np.arange(N), y[:, 0].astype(int)] -= 1.0
+        assert np.allclose(g.cpu().numpy(), want_g * 0.3, rtol=1e-12, atol=1e-15)
+        assert np.allclose(h.cpu().numpy(), np.maximum(p * (1 - p), 1e-8), rtol=1e-12)
+        assert h.min().item() == 1e-8
