@@ -51,6 +51,13 @@ def _worker(rank, world, port, case, q):
              for n in ("feature", "split_value", "gain", "leaf_value", "hessian"))
     wp = O.predict(X[b:e], [(want.leaf_value, want.feature, want.split_value)])
     ok = ok and np.array_equal(pred, wp)
+    # UPDATE_TREE with new gradients: every rank ends with the sums over both row blocks
+    g2 = rs.normal(size=(N, K))
+    h2 = rs.random((N, K)) + 0.1
+    ul, uh = O.update_tree(X, g2, h2, want.feature, want.split_value, n_ranks=world)
+    t.update(torch.from_numpy(X[b:e]).to(dev), torch.from_numpy(g2[b:e]).to(dev), torch.from_numpy(h2[b:e]).to(dev))
+    ok = ok and np.allclose(t.leaf_value.cpu().numpy(), ul, rtol=1e-9, atol=1e-12)
+    ok = ok and np.allclose(t.hessian.cpu().numpy(), uh, rtol=1e-10, atol=1e-12)
     q.put((rank, bool(ok), int((want.feature >= 0).sum())))
     dist.barrier()
     dist.destroy_process_group()
