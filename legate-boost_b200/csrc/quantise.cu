@@ -116,8 +116,20 @@ __global__ void __launch_bounds__(256)
       mg = max(mg, q.x == INT32_MIN ? INT32_MAX : abs(q.x));
       mh = max(mh, q.y == INT32_MIN ? INT32_MAX : abs(q.y));
     }
-    atomicAdd(&s_sum[2 * k], static_cast<unsigned long long>(sg));
-    atomicAdd(&s_sum[2 * k + 1], static_cast<unsigned long long>(sh));
+    if (K == 1) {
+      // every lane holds the same output: one pair of shared-memory atomics per warp
+      for (int off = 16; off >= 1; off >>= 1) {
+        sg += __shfl_down_sync(0xffffffffu, sg, off);
+        sh += __shfl_down_sync(0xffffffffu, sh, off);
+      }
+      if ((tid & 31) == 0) {
+        atomicAdd(&s_sum[0], static_cast<unsigned long long>(sg));
+        atomicAdd(&s_sum[1], static_cast<unsigned long long>(sh));
+      }
+    } else {
+      atomicAdd(&s_sum[2 * k], static_cast<unsigned long long>(sg));
+      atomicAdd(&s_sum[2 * k + 1], static_cast<unsigned long long>(sh));
+    }
   }
   __syncthreads();
   for (int i = tid; i < 2 * K; i += blockDim.x) {
