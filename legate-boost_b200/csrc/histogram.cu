@@ -28,7 +28,6 @@
 //   * a node in one chunk owns its output region and flushes with plain stores; a node cut into
 //     several chunks leaves int32 partial sums in slots and k_hist_sum adds them up afterwards
 //     (without slot memory: 64-bit global atomics); chunks of <= 128 rows skip shared memory.
-#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -867,8 +866,7 @@ void BuildHistogramAllReduce(lbk_context* ctx, Scratch& s, const HistLevel& lv, 
   }
   // Parts: only with NCCL (a callback communicator is not known to be stream-safe), only when every
   // part still has a ticket for every resident block, and only when there is something to hide.
-  int kReserve = 20;  // SMs left to the all-reduce kernel
-  if (const char* e = getenv("LBK_AR_RESERVE")) kReserve = atoi(e);
+  constexpr int kReserve = 20;  // SMs left to the all-reduce kernel
   const int G            = (lv.F + kGroup - 1) / kGroup;
   const bool smem_path   = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   const int width        = smem_path && G >= 2 ? 2 : 1;
@@ -876,7 +874,6 @@ void BuildHistogramAllReduce(lbk_context* ctx, Scratch& s, const HistLevel& lv, 
   const int resident     = (ctx->sm_count - kReserve) * (width == 2 ? 1 : 2);
   int parts              = static_cast<int>(tickets / (resident > 0 ? resident : 1));
   if (parts > 4) parts = 4;
-  if (const char* e = getenv("LBK_AR_PARTS")) parts = atoi(e) < parts ? atoi(e) : parts;
   if (ctx->cb != nullptr || ctx->nccl_comm == nullptr || !smem_path || lv.n_rows <= 0 ||
       static_cast<size_t>(n_slots) * slot_words * 8 < (size_t{8} << 20))
     parts = 1;
