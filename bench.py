@@ -133,19 +133,26 @@ def _ref_hist_lib():
     return lib
 
 
-def cpu_hist_sample(n_rows_sample, seed, threads):
-    """CPU histogram of one row sample of the level-7 batch on `threads` host threads, one rank
-    per thread on a row shard, partial histograms summed in process (the stand-in for the CPU
-    all-reduce).  Uses the reference's own ComputeHistogram (src/models/tree/build_tree.cc:258-289,
-    stub-compiled) when that build is present, else the oracle's restatement of the same loop.
-    Returns (rows*features/s, seconds, kind)."""
-    import ctypes as C
-
+def cpu_hist_data(n_rows_sample, seed):
+    """Host copy of the benchmark's inputs for `n_rows_sample` rows: bins, g, h, node of every row."""
     rs = np.random.default_rng(seed)
     bins = rs.integers(0, HIST_BINS, size=(n_rows_sample, HIST_FEATURES), dtype=np.uint8)
     g = rs.normal(size=(n_rows_sample, 1))
     h = np.ones((n_rows_sample, 1))
     node = rs.integers(0, HIST_NODES, size=n_rows_sample).astype(np.int32) + (HIST_NODES - 1)
+    return bins, g, h, node
+
+
+def cpu_hist_sample(n_rows_sample, seed, threads, data=None):
+    """CPU histogram of one row sample of the level-7 batch on `threads` host threads, one rank
+    per thread on a row shard, partial histograms summed in process (the stand-in for the CPU
+    all-reduce).  Uses the reference's own ComputeHistogram (src/models/tree/build_tree.cc:258-289,
+    stub-compiled) when that build is present, else the oracle's restatement of the same loop.
+    `data` = a sample made by cpu_hist_data (made here when absent).
+    Returns (rows*features/s, seconds, kind)."""
+    import ctypes as C
+
+    bins, g, h, node = data if data is not None else cpu_hist_data(n_rows_sample, seed)
     ref = _ref_hist_lib()
     parts = [None] * threads
     inner = [0.0] * threads
@@ -200,8 +207,9 @@ def run_reference(args):
         cpu_hist_sample(200_000, 1, threads)
     t_all = 0.0
     kind = "port"
+    data = cpu_hist_data(sample, 1)  # made once, outside the timed steps
     for i in range(args.steps):
-        v, dt, kind = cpu_hist_sample(sample, 1 + i, threads)
+        v, dt, kind = cpu_hist_sample(sample, 1, threads, data)
         t_all += dt
     value = sample * HIST_FEATURES * args.steps / t_all
     line = {
@@ -330,11 +338,12 @@ def run_hist(args):
                          "traffic": traffic, "peak_source": which, "kernel": "k_hist_smem", "kernel_ms": kms},
             "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * args.steps,
         }
-        if not args.no_cpu and world >= 1:
+        if not args.no_cpu and world == 1:
             threads = os.cpu_count() or 1
-            v, dt, kind = cpu_hist_sample(2_000_000, 7, threads)
+            v, dt, kind = cpu_hist_sample(5_000_000, 7, threads)
             line["cpu_baseline"] = {"value": v, "unit": "row-features/s", "cores": threads, "kind": kind,
-                                    "sample": "one 2M-row sample of the batch, %d ranks (threads) on row shards (%.2f s)" % (threads, dt)}
+                                    "sample": "one 5M-row sample of the batch, %d ranks (threads) on row shards "
+                                              "(%.2f s, %.0f core-seconds)" % (threads, dt, dt * threads)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
