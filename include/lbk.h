@@ -242,7 +242,8 @@ int lbk_quantise(lbk_context* ctx, const double* g, const double* h, int64_t ldg
  *   hist[j][k][row_ptr[f] + bin(row,f)] += value(row,k)
  * mode 0: value = int32 pair from gpair, hist = int64 pairs  [n_nodes, n_outputs, B, 2]
  * mode 1: value = float32 pair from gpair_f32, hist = float64 pairs of the same shape.
- * hist is zeroed by the call. */
+ * hist is zeroed by the call.  With device buffers the call is asynchronous on `stream` (unless it
+ * has to read row_ptr back, see max_bins); with host buffers it returns when hist is filled. */
 typedef struct lbk_histogram_args {
   const void* bins;   /* layout of lbk_bin_matrix */
   int32_t bin_bytes;

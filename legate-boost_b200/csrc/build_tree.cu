@@ -529,9 +529,12 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
     lv.float_mode           = a->mode == 1;
     if (a->all_reduce) lbk::BuildHistogramAllReduce(ctx, s, lv, a->n_nodes, false, stream);
     else lbk::BuildHistogram(ctx, s, lv, stream);
-    if (a->host_buffers)
+    // host buffers: the histogram has to be back before the call returns; device buffers: the call
+    // is one more piece of work on the caller's stream
+    if (a->host_buffers) {
       LBK_CUDA(cudaMemcpyAsync(a->hist, hist, hist_bytes, cudaMemcpyDeviceToHost, stream));
-    lbk::CheckDeviceStatus(ctx, stream);
+      lbk::CheckDeviceStatus(ctx, stream);
+    }
   });
 }
 
