@@ -101,7 +101,8 @@ def _hist_case(rs, N, F, K, n_nodes, nb):
 
 
 @pytest.mark.parametrize("N,F,K,n_nodes,nb", [(200000, 128, 1, 128, 256), (50000, 50, 3, 8, 256),
-                                              (3000, 100, 1, 64, 7), (100, 5, 2, 4, 256), (70000, 64, 1, 1, 256)])
+                                              (3000, 100, 1, 64, 7), (100, 5, 2, 4, 256), (70000, 64, 1, 1, 256),
+                                              (60000, 70, 2, 5, 200), (90000, 161, 1, 3, 256)])
 def test_histogram_int_exact(lb, oracle, N, F, K, n_nodes, nb):
     from legateboost_b200 import stages
 
