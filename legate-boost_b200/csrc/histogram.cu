@@ -61,6 +61,8 @@ struct HistParams {
   const int32_t* plan;       // [0] rows per chunk, [1] total chunks, [3] rows between flushes, [5] nodes in
                              // `multi`, [6] slots usable
   unsigned int* ticket;
+  cudaTextureObject_t tex_bins;   // the bin matrix as 16-byte texels, the pairs as 8-byte texels: the row
+  cudaTextureObject_t tex_pairs;  // gathers then go through the texture data pipe; 0 = plain loads
   void* partial;             // partial-sum slots: [slot][2][mb * 32] of the accumulator type; may be null
   void* out;
 };
@@ -514,8 +516,18 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
       // rows beyond the end carry zero pairs and bin 0: they add nothing
       auto load_row = [&](int rid, int4& w, int2& v) {
         if (rid >= 0) {
-          w = __ldcs(reinterpret_cast<const int4*>(gb + static_cast<int64_t>(rid) * pitch));
-          v = __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid) * p.K + k));
+          // through the texture pipe where the buffers have texture objects: the load/store pipe,
+          // which the reductions saturate, is spared the gathers
+          if (p.tex_bins != 0) {
+            w = tex1Dfetch<int4>(p.tex_bins, static_cast<int>((static_cast<int64_t>(rid) * pitch + g0 * kGroup + q * 16) >> 4));
+          } else {
+            w = __ldcs(reinterpret_cast<const int4*>(gb + static_cast<int64_t>(rid) * pitch));
+          }
+          if (p.tex_pairs != 0) {
+            v = tex1Dfetch<int2>(p.tex_pairs, static_cast<int>(static_cast<int64_t>(rid) * p.K + k));
+          } else {
+            v = __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid) * p.K + k));
+          }
         } else {
           w = make_int4(0, 0, 0, 0);
           v = make_int2(0, 0);
@@ -803,6 +815,13 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
+  p.tex_bins           = 0;
+  p.tex_pairs          = 0;
+  // (measured: the float path, bound by its float reductions, is slower with the texture fetches)
+  if (smem_path && lv.n_rows > 0 && !lv.float_mode) {
+    p.tex_bins  = LinearTexture(ctx, lv.bins, static_cast<size_t>(lv.n_rows) * p.G * kGroup, 16);
+    p.tex_pairs = LinearTexture(ctx, p.gpair, static_cast<size_t>(lv.n_rows) * lv.K * 8, 8);
+  }
   const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, p.G, ctx->sm_count - (lv.reserve_sms < ctx->sm_count ? lv.reserve_sms : 0));
 
   const int* max_abs = lv.max_abs;
@@ -1069,10 +1088,12 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
       }
     }
     // no partial-sum slots here (they would have to be allocated): nodes cut into chunks flush with atomics
-    p.part_off = nullptr;
-    p.multi    = nullptr;
-    p.partial  = nullptr;
-      k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, (p.G + hl.width - 1) / hl.width * p.K, hl.grid,
+    p.part_off  = nullptr;
+    p.multi     = nullptr;
+    p.partial   = nullptr;
+    p.tex_bins  = 0;  // texture objects belong to a context; this entry point has none
+    p.tex_pairs = 0;
+    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, (p.G + hl.width - 1) / hl.width * p.K, hl.grid,
                                         float_mode ? nullptr : max_abs, 0, chunk_off, nullptr, nullptr, plan, p.ticket);
     LBK_LAUNCH_CHECK();
     hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);

@@ -76,6 +76,17 @@ struct lbk_context {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ev_part[4]   = {nullptr, nullptr, nullptr, nullptr};
   cudaEvent_t ev_comm_done = nullptr;
+  // linear textures over buffers the histogram kernel gathers from (see LinearTexture)
+  struct TexEntry {
+    const void* ptr;
+    size_t bytes;
+    int texel_bytes;
+    cudaTextureObject_t obj;
+    unsigned long long last_use;
+  };
+  std::vector<TexEntry> tex_cache;
+  unsigned long long tex_clock = 0;
+  int tex_alignment = 0, tex_max_texels = 0;
   // optional timing of the histogram kernel alone (events on the caller's stream)
   bool profile            = false;
   cudaEvent_t ev_start    = nullptr, ev_stop = nullptr;
@@ -110,6 +121,11 @@ class Scratch {
 // is limited to a few CTAs, if there is one.
 void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream,
                bool beside_kernel = false);
+// A texture object that presents `bytes` of device memory at `ptr` as a 1-D array of 8- or 16-byte
+// texels, or 0 when the buffer cannot be one (alignment, more texels than a linear texture holds).
+// Objects are kept in a small per-context cache keyed by (pointer, size, texel); the least recently
+// used one is destroyed, after a device synchronisation, when the cache is full.
+cudaTextureObject_t LinearTexture(lbk_context* ctx, const void* ptr, size_t bytes, int texel_bytes);
 // Reads the device status word (synchronises the stream) and throws LBK_ERR_DEVICE if set.
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream);
 
