@@ -122,6 +122,28 @@ def test_histogram_int_exact(lb, oracle, N, F, K, n_nodes, nb):
     assert np.array_equal(got.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("F,K", [(32, 2), (64, 1)])
+def test_histogram_many_large_nodes(lb, oracle, F, K):
+    """More large, unequal nodes than resident blocks, some of them empty: the planner cuts the
+    larger nodes into chunks that leave partial sums; the sums stay exact."""
+    from legateboost_b200 import stages
+
+    N, n_nodes = 6_000_000, 200
+    rng = np.random.default_rng(F + K)
+    weight = rng.uniform(0.5, 1.5, size=n_nodes)
+    weight[[0, 17, 18, 199]] = 0.0  # empty nodes, at both ends and in a row
+    edges = np.cumsum(weight / weight.sum())
+    node = np.minimum(np.searchsorted(edges, rng.random(N), side="right"), n_nodes - 2).astype(np.int32) + (n_nodes - 1)
+    bins = rng.integers(0, 256, size=(N, F), dtype=np.uint8)
+    row_ptr = (np.arange(F + 1) * 256).astype(np.int32)
+    q = rng.integers(-200, 200, size=(N, K, 2), dtype=np.int32)
+    q[:, :, 1] = np.abs(q[:, :, 1])
+    want = oracle.histogram_q(bins, row_ptr, q, node, n_nodes - 1, 2 * n_nodes - 1)
+    row_index, seg = stages.group_rows(dev(node), n_nodes - 1, n_nodes)
+    got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
 def test_histogram_int_no_wraparound(lb, oracle):
     """Partial sums that exceed int32 in one chunk must still come out exact."""
     from legateboost_b200 import stages
