@@ -1101,16 +1101,3 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     LBK_CUDA(cudaStreamSynchronize(stream));
   });
 }
-
-#ifdef LBK_HIST_TIMING
-extern "C" int lbk_debug_hist_timing(unsigned long long* out8, int reset)
-{
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out8, lbk::g_hist_timing, 64);
-  if (reset) {
-    unsigned long long z[8] = {};
-    cudaMemcpyToSymbol(lbk::g_hist_timing, z, 64);
-  }
-  return 0;
-}
-#endif
