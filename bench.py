@@ -371,12 +371,14 @@ def run_train(args):
     w = torch.randn(F, dtype=torch.float32, device=device, generator=torch.Generator(device=device).manual_seed(3))
     y = X @ w + 0.1 * torch.randn(n, dtype=torch.float32, device=device, generator=gen)
     rounds = args.steps
-    m = lb.LBRegressor(n_estimators=max(args.warmup, 1), base_models=(lb.Tree(max_depth=args.depth),), random_state=0)
+    m = lb.LBRegressor(n_estimators=max(args.warmup, 1), base_models=(lb.Tree(max_depth=args.depth),), random_state=0,
+                       fixed_sketch=args.fixed_sketch)
     m.fit(X, y)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    m = lb.LBRegressor(n_estimators=rounds, base_models=(lb.Tree(max_depth=args.depth),), random_state=0)
+    m = lb.LBRegressor(n_estimators=rounds, base_models=(lb.Tree(max_depth=args.depth),), random_state=0,
+                       fixed_sketch=args.fixed_sketch)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     m.fit(X, y)
@@ -391,8 +393,10 @@ def run_train(args):
                           "n_gpus": world, "steps": rounds, "warmup": max(args.warmup, 1), "ms_per_step": ms / rounds,
                           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
                           "data": "synthetic",
-                          "config": {"workload": "squared-error boosting, depth %d, 256 bins, %d rows x %d features per GPU"
-                                                 % (args.depth, n, F)}}), flush=True)
+                          "config": {"workload": "squared-error boosting, depth %d, 256 bins, %d rows x %d features per GPU%s"
+                                                 % (args.depth, n, F, ", proposals and bins of the first tree reused "
+                                                    "(not the reference's per-tree sketch)" if args.fixed_sketch else "")}}),
+              flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -484,6 +488,9 @@ def main():
     ap.add_argument("--depth", type=int, default=8)
     ap.add_argument("--trees", type=int, default=500)
     ap.add_argument("--float-path", action="store_true")
+    ap.add_argument("--fixed-sketch", action="store_true",
+                    help="train workload: reuse the first tree's proposals and bins (an extension; results differ "
+                         "from the reference's)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -121,9 +121,25 @@ typedef struct lbk_build_tree_args {
    * tree's prediction for training row i without a second pass over X.  No counterpart in the
    * reference, whose callers run PREDICT on the training matrix after every BUILD_TREE. */
   int32_t* out_leaf;
+  /* Optional fixed sketch.  The reference draws new split proposals and bins X again for every tree,
+   * because every tree has its own seed (models/tree.py:125, build_tree.cu:882-956); `sketch` is a
+   * device buffer of lbk_sketch_bytes() bytes that keeps the proposals and the binned matrix of one
+   * call for later ones.  LBK_SKETCH_OFF ignores it.  LBK_SKETCH_SAVE builds the tree as usual (the
+   * same tree as OFF) and leaves its proposals and bins in the buffer.  LBK_SKETCH_REUSE takes them
+   * from the buffer instead of sampling and binning X (X is not read and may be NULL): the tree then
+   * differs from the reference's, since its proposals are those of the saving call's seed; `seed`
+   * still drives the rounding of the gradients.  n_local_rows, n_features, split_samples and x_dtype
+   * must be those of the saving call (checked), and X unchanged (the caller's promise). */
+  void* sketch;
+  int32_t sketch_mode;
 } lbk_build_tree_args;
 
+enum { LBK_SKETCH_OFF = 0, LBK_SKETCH_SAVE = 1, LBK_SKETCH_REUSE = 2 };
+
 int lbk_build_tree(lbk_context* ctx, const lbk_build_tree_args* args);
+
+/* Bytes of the sketch buffer for a matrix of this shape (0 for a bad shape). */
+size_t lbk_sketch_bytes(int64_t n_local_rows, int n_features, int split_samples, int x_dtype);
 
 /* out[i, :] = leaf_value[leaf[i], :] for the rows of lbk_build_tree_args.out_leaf: the tree's
  * predictions for its training rows (what the reference gets from a PREDICT task on the training

@@ -6,7 +6,7 @@
 compute call needs the built library and a CUDA device.
 """
 from . import library  # noqa: F401
-from .tree import BaseModel, Tree  # noqa: F401
+from .tree import BaseModel, Sketch, Tree  # noqa: F401
 from .estimator import LBClassifier, LBRegressor  # noqa: F401
 
-__all__ = ["Tree", "BaseModel", "LBRegressor", "LBClassifier", "library"]
+__all__ = ["Tree", "BaseModel", "Sketch", "LBRegressor", "LBClassifier", "library"]

@@ -50,6 +50,31 @@ __global__ void __launch_bounds__(256)
   out[e]          = __ldg(table + static_cast<int64_t>(__ldg(index + i)) * K + k);
 }
 
+// The caller's sketch buffer: a header, then the split proposals, their row pointers, the binned
+// matrix and its feature-major copy, each on a 512-byte boundary and sized for the widest case
+// (two-byte bins when a feature can have more than 256 proposals).
+constexpr int32_t kSketchMagic = 0x4c424b53;
+struct SketchHeader {
+  int32_t magic, total_bins, max_bins_per_feature, n_features, split_samples, elem_bytes, has_feature_major, pad;
+  int64_t n_rows;
+};
+struct SketchLayout {
+  size_t proposals, row_ptr, bins, bins_t, bytes;
+};
+SketchLayout SketchLayoutOf(int64_t N, int F, int S, size_t elem_bytes)
+{
+  auto up = [](size_t v) { return (v + 511) / 512 * 512; };
+  const int bin_bytes   = S <= 256 ? 1 : 2;
+  const int64_t pitch_t = (N + 31) / 32 * 32;
+  SketchLayout l;
+  l.proposals = up(sizeof(SketchHeader));
+  l.row_ptr   = l.proposals + up(static_cast<size_t>(F) * S * elem_bytes);
+  l.bins      = l.row_ptr + up(sizeof(int32_t) * (static_cast<size_t>(F) + 1));
+  l.bins_t    = l.bins + up(lbk_bin_matrix_bytes(N, F, bin_bytes));
+  l.bytes     = l.bins_t + up(static_cast<size_t>(F) * pitch_t * bin_bytes + 16);
+  return l;
+}
+
 template <typename T>
 void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t stream)
 {
@@ -107,22 +132,57 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
   unsigned int* split_arrived = s.alloc<unsigned int>(M);  // see BestSplit
   LBK_CUDA(cudaMemsetAsync(split_arrived, 0, sizeof(unsigned int) * M, stream));
 
-  // split proposals -> B (one host synchronisation)
-  T* proposals      = s.alloc<T>(static_cast<size_t>(F) * a.split_samples);
-  int32_t* row_ptr  = s.alloc<int32_t>(F + 1);
-  const ProposalInfo pi = SplitProposals<T>(ctx, s, X, ldx, a.row_offset, N, F, a.split_samples, a.seed,
-                                            a.dataset_rows, proposals, row_ptr, stream);
+  // split proposals -> B (one host synchronisation); with a sketch buffer they and the binned
+  // matrix live in the caller's buffer and may come from an earlier call
+  const bool sketch_save = a.sketch_mode == LBK_SKETCH_SAVE, sketch_reuse = a.sketch_mode == LBK_SKETCH_REUSE;
+  const SketchLayout sk  = SketchLayoutOf(N, F, a.split_samples, sizeof(T));
+  unsigned char* skb     = static_cast<unsigned char*>(a.sketch);
+  const bool in_sketch   = sketch_save || sketch_reuse;
+  T* proposals     = in_sketch ? reinterpret_cast<T*>(skb + sk.proposals) : s.alloc<T>(static_cast<size_t>(F) * a.split_samples);
+  int32_t* row_ptr = in_sketch ? reinterpret_cast<int32_t*>(skb + sk.row_ptr) : s.alloc<int32_t>(F + 1);
+  ProposalInfo pi;
+  SketchHeader head{};
+  if (sketch_reuse) {
+    LBK_CUDA(cudaMemcpyAsync(&head, skb, sizeof(head), cudaMemcpyDeviceToHost, stream));
+    LBK_CUDA(cudaStreamSynchronize(stream));
+    LBK_EXPECT(head.magic == kSketchMagic, "the sketch buffer holds no saved sketch");
+    LBK_EXPECT(head.n_rows == N && head.n_features == F && head.split_samples == a.split_samples &&
+                 head.elem_bytes == static_cast<int32_t>(sizeof(T)),
+               "the sketch was saved for a matrix of another shape or type");
+    LBK_EXPECT(D <= 1 || head.has_feature_major, "the sketch was saved without the feature-major copy");
+    pi.total_bins           = head.total_bins;
+    pi.max_bins_per_feature = head.max_bins_per_feature;
+  } else {
+    pi = SplitProposals<T>(ctx, s, X, ldx, a.row_offset, N, F, a.split_samples, a.seed, a.dataset_rows, proposals,
+                           row_ptr, stream);
+  }
   const int B = pi.total_bins;
   if (a.out_total_bins) *a.out_total_bins = B;
   LBK_EXPECT(B >= F, "every feature must have at least one proposal");
 
   // binned matrix, once per tree
   const int bin_bytes = pi.max_bins_per_feature <= 256 ? 1 : 2;
-  void* bins          = s.alloc_bytes(lbk_bin_matrix_bytes(N, F, bin_bytes));
-  // feature-major copy for the repartition (no copy for a stump: nothing is repartitioned)
+  void* bins          = in_sketch ? static_cast<void*>(skb + sk.bins) : s.alloc_bytes(lbk_bin_matrix_bytes(N, F, bin_bytes));
+  // feature-major copy for the repartition (no copy for a stump: nothing is repartitioned; a saved
+  // sketch always has it, later trees may be deeper)
   const int64_t pitch_t = (N + 31) / 32 * 32;
-  void* bins_t          = D > 1 ? s.alloc_bytes(static_cast<size_t>(F) * pitch_t * bin_bytes + 16) : nullptr;
-  BinMatrix<T>(X, ldx, N, F, proposals, row_ptr, bins, bins_t, pitch_t, bin_bytes, pi.max_bins_per_feature, stream);
+  void* bins_t          = in_sketch ? static_cast<void*>(skb + sk.bins_t)
+                          : D > 1   ? s.alloc_bytes(static_cast<size_t>(F) * pitch_t * bin_bytes + 16)
+                                    : nullptr;
+  if (!sketch_reuse)
+    BinMatrix<T>(X, ldx, N, F, proposals, row_ptr, bins, bins_t, pitch_t, bin_bytes, pi.max_bins_per_feature, stream);
+  if (sketch_save) {
+    head.magic                = kSketchMagic;
+    head.total_bins           = pi.total_bins;
+    head.max_bins_per_feature = pi.max_bins_per_feature;
+    head.n_features           = F;
+    head.split_samples        = a.split_samples;
+    head.elem_bytes           = static_cast<int32_t>(sizeof(T));
+    head.has_feature_major    = 1;
+    head.n_rows               = N;
+    LBK_CUDA(cudaMemcpyAsync(skb, &head, sizeof(head), cudaMemcpyHostToDevice, stream));
+    LBK_CUDA(cudaStreamSynchronize(stream));  // `head` is on this frame
+  }
 
   // quantised pairs and root sums
   QuantParams* qp = s.alloc<QuantParams>(1);
@@ -307,6 +367,12 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
 
 extern "C" {
 
+size_t lbk_sketch_bytes(int64_t n_local_rows, int n_features, int split_samples, int x_dtype)
+{
+  if (n_local_rows < 0 || n_features < 1 || split_samples < 1) return 0;
+  return lbk::SketchLayoutOf(n_local_rows, n_features, split_samples, x_dtype == LBK_F64 ? 8 : 4).bytes;
+}
+
 size_t lbk_bin_matrix_bytes(int64_t n_rows, int n_features, int bin_bytes)
 {
   const int64_t G = (n_features + lbk::kGroup - 1) / lbk::kGroup;
@@ -325,7 +391,10 @@ int lbk_build_tree(lbk_context* ctx, const lbk_build_tree_args* a)
     LBK_EXPECT(a->max_depth >= 0 && a->max_depth <= 29, "max_depth out of range");
     LBK_EXPECT(a->max_nodes == (1 << (a->max_depth + 1)) - 1, "max_nodes must be 2^(max_depth+1)-1");
     LBK_EXPECT(a->split_samples >= 1 && a->split_samples <= 2048, "split_samples must be in [1, 2048]");
-    LBK_EXPECT(a->n_local_rows == 0 || (a->X && a->g && a->h), "null input");
+    LBK_EXPECT(a->sketch_mode == LBK_SKETCH_OFF || a->sketch_mode == LBK_SKETCH_SAVE || a->sketch_mode == LBK_SKETCH_REUSE,
+               "unknown sketch mode");
+    LBK_EXPECT(a->sketch_mode == LBK_SKETCH_OFF || a->sketch != nullptr, "sketch mode without a sketch buffer");
+    LBK_EXPECT(a->n_local_rows == 0 || ((a->X || a->sketch_mode == LBK_SKETCH_REUSE) && a->g && a->h), "null input");
     LBK_EXPECT(a->n_local_rows == 0 || (a->ldx >= a->n_features && a->ldg >= a->n_outputs), "Expected a dense row major store");
     LBK_EXPECT(a->leaf_value && a->feature && a->split_value && a->gain && a->hessian, "null output");
     LBK_EXPECT(a->row_offset >= 0 && a->row_offset + a->n_local_rows <= a->dataset_rows, "row range outside the data set");

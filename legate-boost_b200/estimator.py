@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 from . import library as L
-from .tree import Tree, _row_layout
+from .tree import Sketch, Tree, _row_layout
 
 
 def _all_sum(t: torch.Tensor) -> torch.Tensor:
@@ -100,7 +100,11 @@ class _LBBase:
     _objective = None
 
     def __init__(self, n_estimators: int = 100, learning_rate: float = 0.1, init: Optional[str] = "average",
-                 base_models=(Tree(max_depth=6),), random_state=None, verbose: int = 0):
+                 base_models=(Tree(max_depth=6),), random_state=None, verbose: int = 0, fixed_sketch: bool = False):
+        # fixed_sketch (an extension, off by default): the first tree of every base model saves its
+        # split proposals and binned matrix, the later ones reuse them instead of sampling and
+        # binning X again; the trees then differ from the reference's, which re-samples per tree
+        self.fixed_sketch = fixed_sketch
         self.n_estimators = n_estimators
         self.learning_rate = learning_rate
         self.init = init
@@ -151,11 +155,15 @@ class _LBBase:
         self.train_metric_: List[float] = []
         train_pred = self.model_init_.repeat(X.shape[0], 1)
         layout = _row_layout(X.shape[0])  # this rank's block of rows: the same for every tree
+        sketches = {}
         for i in range(self.n_estimators):
             g, h = self._weighted_gradient(y, train_pred)
             tree = deepcopy(self.base_models[i % len(self.base_models)]).set_random_state(self.random_state_)
             tree.row_layout = layout
+            if self.fixed_sketch:
+                tree.sketch = sketches.setdefault(i % len(self.base_models), Sketch())
             tree.fit(X, g, h)
+            tree.sketch = None  # the buffer belongs to this fit, not to the tree
             self.models_.append(tree)
             train_pred += tree.predict(X)
             if self.verbose:

@@ -19,7 +19,7 @@ UNIQUE_ID_BYTES = 128
 EXPORTS = [
     "lbk_version", "lbk_context_create", "lbk_context_destroy", "lbk_last_error", "lbk_context_trim",
     "lbk_comm_unique_id", "lbk_comm_init", "lbk_comm_attach_nccl", "lbk_comm_set_callback",
-    "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
+    "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_sketch_bytes", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
     "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_histogram_noalloc", "lbk_group_rows",
 ]
 
@@ -45,7 +45,11 @@ class BuildTreeArgs(C.Structure):
         ("stream", C.c_void_p), ("host_buffers", C.c_int32),
         ("trace_node_sums", C.c_void_p), ("trace_hist", C.c_void_p), ("trace_nodes", C.c_int32),
         ("out_total_bins", C.POINTER(C.c_int32)), ("out_leaf", C.c_void_p),
+        ("sketch", C.c_void_p), ("sketch_mode", C.c_int32),
     ]
+
+
+SKETCH_OFF, SKETCH_SAVE, SKETCH_REUSE = 0, 1, 2
 
 
 class UpdateTreeArgs(C.Structure):
@@ -119,6 +123,8 @@ def load():
             lib.lbk_bin_matrix.argtypes = [
                 C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_void_p,
                 C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+            lib.lbk_sketch_bytes.argtypes = [C.c_int64, C.c_int, C.c_int, C.c_int]
+            lib.lbk_sketch_bytes.restype = C.c_size_t
             lib.lbk_bin_matrix_bytes.argtypes = [C.c_int64, C.c_int, C.c_int]
             lib.lbk_bin_matrix_bytes.restype = C.c_size_t
             lib.lbk_quantise.argtypes = [

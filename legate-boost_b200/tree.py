@@ -47,11 +47,34 @@ def _tensor_key(t: torch.Tensor):
     return (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, t.device, t._version)
 
 
+class Sketch:
+    """Split proposals and binned matrix of one training matrix, kept in a device buffer so that
+    later trees on the same matrix skip the sampling and the binning (``lbk_build_tree_args.sketch``).
+    An extension: the reference samples and bins again for every tree (models/tree.py:125), so trees
+    built from a reused sketch differ from the reference's.  The first fit on a matrix saves, fits
+    on the same unmodified tensor with the same ``split_samples`` reuse."""
+
+    def __init__(self) -> None:
+        self.buffer = None
+        self.key = None
+
+    def mode_for(self, X, split_samples, ctx) -> int:
+        need = int(ctx.lib.lbk_sketch_bytes(X.shape[0], X.shape[1], split_samples, _dtype_code(X)))
+        key = (_tensor_key(X), split_samples)
+        if self.buffer is not None and self.key == key and self.buffer.numel() >= need:
+            return L.SKETCH_REUSE
+        if self.buffer is None or self.buffer.numel() < need or self.buffer.device != X.device:
+            self.buffer = torch.empty((need,), dtype=torch.uint8, device=X.device)
+        self.key = None  # set by the caller once the saving call has succeeded
+        return L.SKETCH_SAVE
+
+
 def build_tree_arrays(X, g, h, *, max_depth, split_samples, seed, l1=0.0, l2=1.0, min_split_gain=0.0,
                       feature_set=None, row_offset=None, dataset_rows=None, trace_nodes=0, ctx=None,
-                      want_leaf=False):
+                      want_leaf=False, sketch=None):
     """Run ``lbk_build_tree`` on device tensors.  Returns a dict with the five tree arrays (and the
-    optional traces; with ``want_leaf`` also ``leaf``: the node every local row ends in)."""
+    optional traces; with ``want_leaf`` also ``leaf``: the node every local row ends in).  With a
+    ``Sketch`` the proposals and bins are saved in it or, if it holds those of this matrix, reused."""
     assert X.is_cuda and g.is_cuda and h.is_cuda, "inputs must be CUDA tensors (no CPU fallback)"
     if g.dim() == 1:
         g, h = g[:, None], h[:, None]
@@ -100,8 +123,13 @@ def build_tree_arrays(X, g, h, *, max_depth, split_samples, seed, l1=0.0, l2=1.0
     if want_leaf:
         out["leaf"] = torch.empty((N,), dtype=torch.int32, device=dev)
         a.out_leaf = out["leaf"].data_ptr()
+    if sketch is not None:
+        a.sketch_mode = sketch.mode_for(X, split_samples, ctx)
+        a.sketch = sketch.buffer.data_ptr()
     with torch.cuda.device(dev):
         ctx.check(ctx.lib.lbk_build_tree(ctx.handle, C.byref(a)))
+    if sketch is not None:
+        sketch.key = (_tensor_key(X), split_samples)
     out["B"] = B.value
     if trace is not None:
         # the library wrote with node stride K*B: re-view
@@ -240,7 +268,8 @@ class Tree(BaseModel):
         out = build_tree_arrays(
             X, g, h, max_depth=self.max_depth, split_samples=self.split_samples, seed=seed,
             l1=self.l1_regularization, l2=self.l2_regularization, min_split_gain=self.min_split_gain,
-            feature_set=feature_set, want_leaf=True, row_offset=row_offset, dataset_rows=dataset_rows)
+            feature_set=feature_set, want_leaf=True, row_offset=row_offset, dataset_rows=dataset_rows,
+            sketch=getattr(self, "sketch", None))
         self.leaf_value = out["leaf_value"]
         self.feature = out["feature"]
         self.split_value = out["split_value"]

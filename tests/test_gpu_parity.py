@@ -254,6 +254,71 @@ def test_build_tree_histograms_bit_exact(lb, oracle):
         assert np.array_equal(got["feature"].cpu().numpy(), want.feature)
 
 
+def test_fixed_sketch_save_and_reuse(lb, oracle):
+    """The optional sketch buffer: a saving call gives the oracle's tree, a reusing call with the same
+    seed gives it again without reading X, a reusing call with another seed splits on the saved
+    proposals only; a buffer without a sketch and a sketch of another shape are errors."""
+    from legateboost_b200 import stages
+    from legateboost_b200.tree import Sketch, build_tree_arrays
+
+    N, F, K, D, S = 20000, 37, 2, 6, 64
+    rs = np.random.RandomState(11)
+    X = rs.normal(size=(N, F)).astype(np.float32)
+    g = rs.normal(size=(N, K))
+    h = rs.uniform(0.5, 2.0, size=(N, K))
+    want = oracle.build_tree(X, g, h, max_depth=D, split_samples=S, seed=7, mode="Q")
+    dX, dg, dh = dev(X), dev(g), dev(h)
+    kw = dict(max_depth=D, split_samples=S, row_offset=0, dataset_rows=N, want_leaf=True)
+    sk = Sketch()
+    saved = build_tree_arrays(dX, dg, dh, seed=7, sketch=sk, **kw)
+    assert sk.key is not None
+    reused = build_tree_arrays(dX, dg, dh, seed=7, sketch=sk, **kw)
+    for got in (saved, reused):
+        for name in ("feature", "split_value", "gain", "leaf_value", "hessian"):
+            assert np.array_equal(got[name].cpu().numpy(), getattr(want, name)), name
+    assert torch.equal(saved["leaf"], reused["leaf"])
+    # another seed on the saved sketch: other roundings, the proposals of seed 7
+    other = build_tree_arrays(dX, dg, dh, seed=8, sketch=sk, **kw)
+    props, row_ptr = stages.split_proposals(dX, S, 7)
+    props, row_ptr = props.cpu().numpy().astype(np.float64), row_ptr.cpu().numpy()
+    feat, split = other["feature"].cpu().numpy(), other["split_value"].cpu().numpy()
+    assert (feat >= 0).sum() > 10
+    for f, v in zip(feat, split):
+        if f >= 0:
+            assert v in props[row_ptr[f]:row_ptr[f + 1]]
+    fresh = build_tree_arrays(dX, dg, dh, seed=8, **{**kw, "want_leaf": False})
+    assert not np.array_equal(fresh["split_value"].cpu().numpy(), split)  # seed 8 has proposals of its own
+    # errors
+    from legateboost_b200 import library as L
+    empty = Sketch()
+    empty.mode_for(dX, S, L.context(0))
+    empty.buffer.zero_()
+    empty.key = sk.key  # pretend it was saved
+    with pytest.raises(L.LbkError, match="no saved sketch"):
+        build_tree_arrays(dX, dg, dh, seed=7, sketch=empty, **kw)
+    X36 = dX[:, :36].contiguous()
+    wrong = Sketch()
+    wrong.buffer, wrong.key = sk.buffer, (lb.tree._tensor_key(X36), S)  # pretend it was saved for X36
+    with pytest.raises(L.LbkError, match="another shape"):
+        build_tree_arrays(X36, dg, dh, seed=7, sketch=wrong, **kw)
+
+
+def test_estimator_fixed_sketch(lb):
+    """fixed_sketch=True: the first tree is the one the default driver builds, later trees reuse its
+    bins; the model still fits."""
+    rs = np.random.RandomState(4)
+    X = dev(rs.normal(size=(30000, 20)).astype(np.float32))
+    y = X[:, 0] * 2.0 - X[:, 3] + 0.1 * dev(rs.normal(size=30000)).to(torch.float32)
+    base = (lb.Tree(max_depth=5, split_samples=64),)
+    a = lb.LBRegressor(n_estimators=8, base_models=base, random_state=3).fit(X, y)
+    b = lb.LBRegressor(n_estimators=8, base_models=base, random_state=3, fixed_sketch=True).fit(X, y)
+    assert torch.equal(a.models_[0].feature, b.models_[0].feature)
+    assert torch.equal(a.models_[0].leaf_value, b.models_[0].leaf_value)
+    assert all(getattr(t, "sketch", None) is None for t in b.models_)
+    err = lambda m: float(((m.predict(X).view(-1) - y.double()) ** 2).mean())
+    assert err(b) < 0.5 * float(y.double().var()) and abs(err(b) - err(a)) < 0.2 * err(a) + 1e-3
+
+
 def test_build_tree_level_batching(lb, oracle):
     """More bins than the 1 GB histogram rule holds on the deepest levels: levels are cut into
     batches and built without parents (reference: test_wide_deep, test_tree.py:218-227)."""
