@@ -58,6 +58,16 @@ def _worker(rank, world, port, case, q):
     t.update(torch.from_numpy(X[b:e]).to(dev), torch.from_numpy(g2[b:e]).to(dev), torch.from_numpy(h2[b:e]).to(dev))
     ok = ok and np.allclose(t.leaf_value.cpu().numpy(), ul, rtol=1e-9, atol=1e-12)
     ok = ok and np.allclose(t.hessian.cpu().numpy(), uh, rtol=1e-10, atol=1e-12)
+    # the optional sketch buffer: a saving fit and a reusing fit with the same seed both give the
+    # oracle's tree (the reusing one skips the proposal sampling and its collective on every rank)
+    sk = lb.Sketch()
+    Xd, gd, hd = torch.from_numpy(X[b:e]).to(dev), torch.from_numpy(g[b:e]).to(dev), torch.from_numpy(h[b:e]).to(dev)
+    for _ in range(2):
+        t2 = lb.Tree(max_depth=D, split_samples=S).set_random_state(np.random.RandomState(5))
+        t2.sketch = sk
+        t2.fit(Xd, gd, hd)
+        ok = ok and all(np.array_equal(getattr(t2, n).cpu().numpy(), getattr(want, n))
+                        for n in ("feature", "split_value", "gain", "leaf_value", "hessian"))
     q.put((rank, bool(ok), int((want.feature >= 0).sum())))
     dist.barrier()
     dist.destroy_process_group()
