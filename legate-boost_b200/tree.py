@@ -359,6 +359,14 @@ class Tree(BaseModel):
 
         return recurse_print(0, 0)
 
+    def __getstate__(self):
+        # pickled / deep-copied trees carry the model (the five arrays and the hyper-parameters), not
+        # the per-fit scratch: the record of the training rows and the sketch buffer stay behind
+        state = dict(self.__dict__)
+        state.pop("_fit_rows", None)
+        state.pop("sketch", None)
+        return state
+
     def __mul__(self, scalar: Any) -> "Tree":
         self._fit_rows = None  # the record of the training rows is not worth copying
         new = copy.deepcopy(self)

@@ -303,6 +303,24 @@ def test_fixed_sketch_save_and_reuse(lb, oracle):
         build_tree_arrays(X36, dg, dh, seed=7, sketch=wrong, **kw)
 
 
+def test_tree_pickle_round_trip(lb):
+    """A pickled tree predicts the same bits and leaves the per-fit scratch (leaf record, sketch) behind."""
+    import pickle
+
+    rs = np.random.RandomState(2)
+    X = dev(rs.normal(size=(4000, 9)).astype(np.float32))
+    g, h = dev(rs.normal(size=(4000, 1))), dev(np.ones((4000, 1)))
+    t = lb.Tree(max_depth=4, split_samples=32).set_random_state(np.random.RandomState(1))
+    t.sketch = lb.Sketch()
+    t.fit(X, g, h)
+    blob = pickle.dumps(t)
+    assert len(blob) < 200_000  # neither the 4000-row leaf record nor the sketch buffer
+    u = pickle.loads(blob)
+    assert not hasattr(u, "sketch") and getattr(u, "_fit_rows", None) is None
+    assert torch.equal(u.predict(X), t.predict(X))
+    assert str(u) == str(t)
+
+
 def test_estimator_fixed_sketch(lb):
     """fixed_sketch=True: the first tree is the one the default driver builds, later trees reuse its
     bins; the model still fits."""
