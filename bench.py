@@ -322,8 +322,9 @@ def run_hist(args):
         kms = ksum / args.steps
         achieved = algorithmic_bytes(n_rows) / (kms * 1e-3) / 1e9
         # DRAM traffic of one launch, from the ncu capture of the 2 M-row case summarised in
-        # profiles/k_hist_config2_ncu_full.md (140.2 B read per row, 15.3 MB written), scaled by rows
-        traffic = n_rows * 140.2 + 15.3e6 if mode == 0 else None
+        # profiles/k_hist_config2_ncu_full.md (149.9 B read per row; 45.7 MB written, which does not
+        # grow with the rows: the output and what the flush buffer left dirty in L2), scaled by rows
+        traffic = n_rows * 149.9 + 45.7e6 if mode == 0 else None
         line = {
             "metric": "histogram rows*features/s", "value": value, "unit": "row-features/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
