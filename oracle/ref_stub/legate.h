@@ -1,9 +1,18 @@
-// Host-only stand-in for the parts of the legate runtime API that the reference's CPU tree
-// task bodies (src/models/tree/build_tree.cc, predict.cc and the headers they include) use.
+// Stand-in for the parts of the legate runtime API that the reference's tree task bodies
+// (src/models/tree/build_tree.cc, build_tree.cu, predict.cc, predict.cu and the headers they
+// include) use.
 // TEST INFRASTRUCTURE: it exists so that those unmodified reference sources can be compiled
-// into oracle/_ref/libref_cpu.so and used to check the oracle's restatement.  Stores are thin
-// views over caller-owned memory; there is one rank, no runtime, no task registration.
+// into oracle/_ref/libref_cpu.so (host compiler) and oracle/_ref/libref_gpu.so (nvcc) and used to
+// check the oracle's restatement.  Stores are thin views over caller-owned memory; there is one
+// rank, no runtime, no task registration.  Under nvcc the views are usable in device code and
+// scratch buffers are device memory.
 #pragma once
+#if defined(__CUDACC__)
+#include <cuda_runtime.h>
+#define LBSTUB_HD __host__ __device__
+#else
+#define LBSTUB_HD
+#endif
 #include <array>
 #include <cstddef>
 #include <cstdint>
@@ -31,24 +40,24 @@ using coord_t = long long;
 template <int N, typename T = coord_t>
 struct Point {
   T x[N];
-  Point()
+  LBSTUB_HD Point()
   {
     for (int i = 0; i < N; ++i) x[i] = 0;
   }
   template <typename... A, typename = std::enable_if_t<sizeof...(A) == N>>
-  Point(A... a) : x{static_cast<T>(a)...}
+  LBSTUB_HD Point(A... a) : x{static_cast<T>(a)...}
   {
   }
-  T& operator[](int i) { return x[i]; }
-  const T& operator[](int i) const { return x[i]; }
-  static Point ZEROES() { return Point(); }
-  Point operator+(const Point& o) const
+  LBSTUB_HD T& operator[](int i) { return x[i]; }
+  LBSTUB_HD const T& operator[](int i) const { return x[i]; }
+  LBSTUB_HD static Point ZEROES() { return Point(); }
+  LBSTUB_HD Point operator+(const Point& o) const
   {
     Point r;
     for (int i = 0; i < N; ++i) r.x[i] = x[i] + o.x[i];
     return r;
   }
-  Point operator-(const Point& o) const
+  LBSTUB_HD Point operator-(const Point& o) const
   {
     Point r;
     for (int i = 0; i < N; ++i) r.x[i] = x[i] - o.x[i];
@@ -59,13 +68,13 @@ struct Point {
 template <int N, typename T = coord_t>
 struct Rect {
   Point<N, T> lo, hi;
-  bool empty() const
+  LBSTUB_HD bool empty() const
   {
     for (int i = 0; i < N; ++i)
       if (hi[i] < lo[i]) return true;
     return false;
   }
-  std::size_t volume() const
+  LBSTUB_HD std::size_t volume() const
   {
     if (empty()) return 0;
     std::size_t v = 1;
@@ -149,36 +158,30 @@ struct TaskException : public std::runtime_error {
   explicit TaskException(const std::string& s) : std::runtime_error(s) {}
 };
 
-// strided view; strides are in elements, a promoted dimension has stride 0
+// Strided view; strides are in elements, a promoted dimension has stride 0.  Trivially copyable,
+// so that a device lambda can capture one by value.
 template <typename T, int N>
 struct AccessorBase {
   T* base = nullptr;
-  std::array<long long, N> stride{};
-  Point<N> origin;  // coordinates of base[0]
+  long long stride[N]{};
+  long long origin[N]{};  // coordinates of base[0]
+  // what the reference reaches as `accessor.accessor` (Legion's affine accessor): its own copy of
+  // the strides, set by the store that makes the view
   struct Inner {
-    const AccessorBase* self;
+    long long stride[N]{};
     template <typename R>
     bool is_dense_row_major(const R& r) const
     {
       long long expect = 1;
       for (int d = N - 1; d >= 0; --d) {
         long long extent = r.hi[d] - r.lo[d] + 1;
-        if (extent > 1 && self->stride[d] != expect) return false;
+        if (extent > 1 && stride[d] != expect) return false;
         expect *= extent;
       }
       return true;
     }
-  } accessor{this};
-  AccessorBase() = default;
-  AccessorBase(const AccessorBase& o) : base(o.base), stride(o.stride), origin(o.origin), accessor{this} {}
-  AccessorBase& operator=(const AccessorBase& o)
-  {
-    base   = o.base;
-    stride = o.stride;
-    origin = o.origin;
-    return *this;
-  }
-  T& at(const Point<N>& p) const
+  } accessor;
+  LBSTUB_HD T& at(const Point<N>& p) const
   {
     long long off = 0;
     for (int d = 0; d < N; ++d) off += (p[d] - origin[d]) * stride[d];
@@ -187,11 +190,11 @@ struct AccessorBase {
 };
 template <typename T, int N>
 struct AccessorRO : AccessorBase<const T, N> {
-  const T& operator[](const Point<N>& p) const { return this->at(p); }
+  LBSTUB_HD const T& operator[](const Point<N>& p) const { return this->at(p); }
 };
 template <typename T, int N>
 struct AccessorWO : AccessorBase<T, N> {
-  T& operator[](const Point<N>& p) const { return this->at(p); }
+  LBSTUB_HD T& operator[](const Point<N>& p) const { return this->at(p); }
 };
 
 class PhysicalStore {
@@ -219,8 +222,9 @@ class PhysicalStore {
     AccessorRO<T, N> a;
     a.base = static_cast<const T*>(ptr);
     for (int i = 0; i < N; ++i) {
-      a.stride[i] = stride[i];
-      a.origin[i] = lo[i];
+      a.stride[i]          = stride[i];
+      a.accessor.stride[i] = stride[i];
+      a.origin[i]          = lo[i];
     }
     return a;
   }
@@ -230,8 +234,9 @@ class PhysicalStore {
     AccessorWO<T, N> a;
     a.base = static_cast<T*>(ptr);
     for (int i = 0; i < N; ++i) {
-      a.stride[i] = stride[i];
-      a.origin[i] = lo[i];
+      a.stride[i]          = stride[i];
+      a.accessor.stride[i] = stride[i];
+      a.origin[i]          = lo[i];
     }
     return a;
   }
@@ -285,6 +290,7 @@ class TaskContext {
   struct State {
     std::vector<PhysicalArray> inputs, outputs;
     std::vector<Scalar> scalars;
+    void* stream = nullptr;
   };
   std::shared_ptr<State> st = std::make_shared<State>();
   const PhysicalArray& input(std::size_t i) const { return st->inputs.at(i); }
@@ -295,12 +301,33 @@ class TaskContext {
   Domain get_launch_domain() const { return {}; }
   std::size_t num_communicators() const { return 0; }
   Communicator communicator(int) const { return {}; }
+#if defined(__CUDACC__)
+  cudaStream_t get_task_stream() const { return static_cast<cudaStream_t>(st->stream); }
+#endif
 };
 
 // Scratch buffers live until the end of the task, as the runtime's do: a temporary Buffer
 // object going out of scope must not release its memory.  The driver calls
 // detail::release_task_buffers() after the task body returns.
 namespace detail {
+inline void* raw_alloc(std::size_t bytes)
+{
+#if defined(__CUDACC__)
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes > 0 ? bytes : 1) != cudaSuccess) throw std::runtime_error("stand-in: cudaMalloc failed");
+  return p;
+#else
+  return std::malloc(bytes > 0 ? bytes : 1);
+#endif
+}
+inline void raw_free(void* p)
+{
+#if defined(__CUDACC__)
+  cudaFree(p);
+#else
+  std::free(p);
+#endif
+}
 inline std::vector<void*>& task_buffers()
 {
   static thread_local std::vector<void*> v;
@@ -308,7 +335,8 @@ inline std::vector<void*>& task_buffers()
 }
 inline void release_task_buffers()
 {
-  for (void* p : task_buffers()) std::free(p);
+  for (void* p : task_buffers())
+    if (p) raw_free(p);
   task_buffers().clear();
 }
 }  // namespace detail
@@ -317,21 +345,21 @@ template <typename T, int DIM = 1>
 class Buffer {
  public:
   T* mem = nullptr;
-  std::array<long long, DIM> extent{};
-  long long offset(const Point<DIM>& p) const
+  long long extent[DIM]{};
+  LBSTUB_HD long long offset(const Point<DIM>& p) const
   {
     long long off = 0;
     for (int d = 0; d < DIM; ++d) off = off * extent[d] + p[d];
     return off;
   }
-  T& operator[](const Point<DIM>& p) const { return mem[offset(p)]; }
-  T* ptr(const Point<DIM>& p) const { return mem + offset(p); }
+  LBSTUB_HD T& operator[](const Point<DIM>& p) const { return mem[offset(p)]; }
+  LBSTUB_HD T* ptr(const Point<DIM>& p) const { return mem + offset(p); }
   void destroy()
   {
     auto& v = detail::task_buffers();
     for (auto& q : v)
       if (q == mem) {
-        std::free(q);
+        detail::raw_free(q);
         q = nullptr;
       }
     mem = nullptr;
@@ -347,7 +375,7 @@ Buffer<T, DIM> create_buffer(const Point<DIM>& extents)
     b.extent[d] = extents[d];
     n *= static_cast<std::size_t>(extents[d] > 0 ? extents[d] : 0);
   }
-  b.mem = static_cast<T*>(std::malloc(sizeof(T) * (n > 0 ? n : 1)));
+  b.mem = static_cast<T*>(detail::raw_alloc(sizeof(T) * (n > 0 ? n : 1)));
   detail::task_buffers().push_back(b.mem);
   return b;
 }
@@ -357,6 +385,41 @@ Buffer<T, 1> create_buffer(I n)
 {
   return create_buffer<T, 1>(Point<1>(n));
 }
+
+// Memory kinds and the allocator thrust's temporary storage goes through (nvcc build only uses it).
+struct Memory {
+  enum Kind { SYSTEM_MEM, GPU_FB_MEM, Z_COPY_MEM };
+};
+class ScopedAllocator {
+ public:
+  explicit ScopedAllocator(Memory::Kind) {}
+  ~ScopedAllocator()
+  {
+    for (void* p : live_) detail::raw_free(p);
+  }
+  ScopedAllocator(const ScopedAllocator&)            = delete;
+  ScopedAllocator& operator=(const ScopedAllocator&) = delete;
+  ScopedAllocator(ScopedAllocator&& o) noexcept : live_(std::move(o.live_)) { o.live_.clear(); }
+  void* allocate(std::size_t bytes)
+  {
+    void* p = detail::raw_alloc(bytes);
+    live_.push_back(p);
+    return p;
+  }
+  void deallocate(void* p)
+  {
+    for (auto& q : live_)
+      if (q == p) {
+        detail::raw_free(q);
+        q = live_.back();
+        live_.pop_back();
+        return;
+      }
+  }
+
+ private:
+  std::vector<void*> live_;
+};
 
 struct VariantOptions {
   constexpr VariantOptions with_has_allocations(bool) const { return *this; }
