@@ -254,10 +254,17 @@ def run_hist(args):
     lb.library.load().lbk_profile_enable(ctx.handle, 1)
     import ctypes as C
 
+    by_pos = not args.pairs_by_row
+    gp_by_row = gp
+    if by_pos:
+        # the pairs in row_index order, as the tree builder keeps them (its repartition moves them
+        # together with the row ids); made once, outside the timed region
+        gp = gp[row_index.long()].contiguous()
+
     def step():
         stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, mode=mode, hist=hist, ctx=ctx,
                          max_abs=max_abs if mode == 0 else None, all_reduce=world > 1, max_bins=HIST_BINS,
-                         total_bins=HIST_FEATURES * HIST_BINS)
+                         total_bins=HIST_FEATURES * HIST_BINS, pairs_by_position=by_pos)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -292,7 +299,7 @@ def run_hist(args):
     e2e = None
     if not args.no_e2e:
         hb = bins.cpu().pin_memory()
-        hgp = gp.cpu().pin_memory()
+        hgp = gp_by_row.cpu().pin_memory()
         hidx = row_index.cpu().pin_memory()
         hseg = seg.cpu()
         hrp = row_ptr.cpu()
@@ -492,6 +499,9 @@ def main():
     ap.add_argument("--fixed-sketch", action="store_true",
                     help="train workload: reuse the first tree's proposals and bins (an extension; results differ "
                          "from the reference's)")
+    ap.add_argument("--pairs-by-row", action="store_true",
+                    help="hist workload: gradient pairs indexed by row id (gathered) instead of stored in "
+                         "row_index order")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

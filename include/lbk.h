@@ -286,22 +286,29 @@ typedef struct lbk_histogram_args {
   int32_t all_reduce;       /* 1: hist is summed over the ranks of the context's communicator before
                                the call returns (the nodes are cut into parts so that the sum of
                                one part travels while the next part is built) */
+  int32_t pairs_by_position; /* 1: gpair / gpair_f32 are stored in row_index order, [seg[n_nodes], n_outputs, 2]:
+                               entry i belongs to row row_index[i].  The pairs of a node are then read as a
+                               stream instead of gathered (the tree builder keeps its pairs this way: the
+                               repartition moves them together with the row ids).  mode 0 needs max_abs. */
 } lbk_histogram_args;
 
 int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* args);
 
 /* The same histogram build for callers that cannot allocate device memory at the time of the
- * call (inside a host callback on a stream, under a runtime that has already handed out the whole
- * memory budget, or in a process whose device footprint must stay fixed after start-up).  It has
- * no counterpart in the reference.  No context is needed and nothing is allocated or freed: the
- * per-call scratch lives in a fixed array of about 16 KB inside the library image, present once
- * on every GPU that loads the library until the process exits.
+ * call: a task running under a runtime that has already handed out the whole memory budget (a
+ * cudaMalloc there fails, or takes memory the runtime believes it owns), or a process whose device
+ * footprint must stay fixed after start-up.  It has no counterpart in the reference.  No context
+ * is needed and nothing is allocated or freed: the per-call scratch lives in a fixed array of about
+ * 16 KB inside the library image, present once on every GPU that loads the library until the
+ * process exits.
  * Limits: n_nodes <= LBK_NOALLOC_MAX_NODES, n_features <= LBK_NOALLOC_MAX_FEATURES, device
- * pointers only (host_buffers = 0); anything larger is rejected with LBK_ERR_ARGUMENT.
+ * pointers only (host_buffers = 0), all_reduce = 0 (no context, no communicator); anything else is
+ * rejected with LBK_ERR_ARGUMENT.  max_bins is ignored (row_ptr is read back).
  * The first call on a device looks up the array's device address; make that call before any
- * stream capture.  All calls on a device share the array, so calls that overlap on the GPU
- * race: issue them on one stream.  The call returns after the stream has drained; the error text
- * is read with lbk_last_error(NULL). */
+ * stream capture begins.  All calls on a device share the array, so calls that overlap on the GPU
+ * race: issue them on one stream.  The call blocks until `stream` has drained (do not issue it from
+ * a host callback of a stream); `device` is current during the call and the caller's device is
+ * restored afterwards; the error text is read with lbk_last_error(NULL). */
 #define LBK_NOALLOC_MAX_NODES 4096
 #define LBK_NOALLOC_MAX_FEATURES 4096
 int lbk_histogram_noalloc(int device, const lbk_histogram_args* args);

@@ -211,6 +211,14 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
   int32_t* seg_a  = s.alloc<int32_t>(2 * max_level_nodes + 2);
   int32_t* seg_b  = s.alloc<int32_t>(2 * max_level_nodes + 2);
   InitRows(rows_a, seg_a, N, stream);
+  // With few outputs the quantised pairs are kept in row_index order: at the root that is the order
+  // they are in already, and every repartition moves them together with the row ids (8 K bytes read
+  // and written per row and level, as streams), so that the histogram kernel reads the pairs of a
+  // node as a stream instead of gathering 8 bytes per row from all over the array.
+  constexpr int kMaxStreamedOutputs = 4;
+  const bool stream_pairs = K <= kMaxStreamedOutputs && D > 0;
+  int2* pairs_a = gpair;
+  int2* pairs_b = stream_pairs && D > 1 ? s.alloc<int2>(static_cast<size_t>(N) * K) : nullptr;
 
   SplitParams sp{a.l1_regularization, a.l2_regularization, a.min_split_gain, fset};
 
@@ -286,7 +294,8 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
       lv.B                    = B;
       lv.max_bins_per_feature = pi.max_bins_per_feature;
       lv.row_ptr              = row_ptr;
-      lv.gpair                = gpair;
+      lv.gpair                = stream_pairs ? pairs_a : gpair;
+      lv.pairs_by_position    = stream_pairs;
       lv.gpair_f              = nullptr;
       lv.max_abs              = max_abs;
       lv.row_index            = rows_a;
@@ -329,9 +338,15 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
       pl.n_nodes       = level_nodes;
       pl.feature       = tree.feature;
       pl.split_bin     = tree.split_bin;
+      if (stream_pairs) {
+        pl.pairs_in  = pairs_a;
+        pl.pairs_out = pairs_b;
+        pl.K         = K;
+      }
       PartitionRows(ctx, s, pl, stream);
       std::swap(rows_a, rows_b);
       std::swap(seg_a, seg_b);
+      std::swap(pairs_a, pairs_b);
     }
   }
 
@@ -536,6 +551,9 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
     LBK_EXPECT(a->mode == 0 ? a->gpair != nullptr : a->gpair_f32 != nullptr, "missing gradient pairs");
     LBK_EXPECT(a->bin_bytes == 1 || a->bin_bytes == 2, "bin_bytes must be 1 or 2");
     LBK_EXPECT(a->n_nodes >= 1 && a->n_features >= 1 && a->n_outputs >= 1 && a->total_bins >= a->n_features, "bad shape");
+    LBK_EXPECT(!a->pairs_by_position || !a->host_buffers, "pairs stored by position are for device buffers");
+    LBK_EXPECT(!a->pairs_by_position || a->mode == 1 || a->max_abs != nullptr,
+               "pairs stored by position need max_abs (the library cannot know how many entries the array has)");
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     lbk::Scratch s(ctx, stream);
     const int F = a->n_features, K = a->n_outputs, B = a->total_bins;
@@ -589,6 +607,7 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
     lv.gpair                = a->mode == 0 ? static_cast<const int2*>(gp) : nullptr;
     lv.gpair_f              = a->mode == 1 ? static_cast<const float2*>(gp) : nullptr;
     lv.max_abs              = a->host_buffers ? nullptr : reinterpret_cast<const int*>(a->max_abs);
+    lv.pairs_by_position    = a->pairs_by_position != 0;
     lv.row_index            = row_index;
     lv.seg                  = seg;
     lv.n_nodes              = a->n_nodes;

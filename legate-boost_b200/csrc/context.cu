@@ -147,48 +147,6 @@ void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_r
   nccl_check(nccl().AllReduce(buf, buf, count, nccl_dtype(dtype), nccl_op(op), comm, stream), "ncclAllReduce");
 }
 
-cudaTextureObject_t LinearTexture(lbk_context* ctx, const void* ptr, size_t bytes, int texel_bytes)
-{
-  constexpr size_t kMaxEntries = 8;
-  if (ptr == nullptr || bytes == 0 || (texel_bytes != 8 && texel_bytes != 16)) return 0;
-  if (ctx->tex_alignment == 0) {
-    LBK_CUDA(cudaDeviceGetAttribute(&ctx->tex_alignment, cudaDevAttrTextureAlignment, ctx->device));
-    LBK_CUDA(cudaDeviceGetAttribute(&ctx->tex_max_texels, cudaDevAttrMaxTexture1DLinearWidth, ctx->device));
-    if (ctx->tex_alignment < 16) ctx->tex_alignment = 16;
-  }
-  if (reinterpret_cast<uintptr_t>(ptr) % static_cast<uintptr_t>(ctx->tex_alignment) != 0) return 0;
-  if (bytes % texel_bytes != 0 || bytes / texel_bytes > static_cast<size_t>(ctx->tex_max_texels)) return 0;
-  ++ctx->tex_clock;
-  for (auto& e : ctx->tex_cache) {
-    if (e.ptr == ptr && e.bytes == bytes && e.texel_bytes == texel_bytes) {
-      e.last_use = ctx->tex_clock;
-      return e.obj;
-    }
-  }
-  if (ctx->tex_cache.size() >= kMaxEntries) {
-    size_t victim = 0;
-    for (size_t i = 1; i < ctx->tex_cache.size(); ++i)
-      if (ctx->tex_cache[i].last_use < ctx->tex_cache[victim].last_use) victim = i;
-    LBK_CUDA(cudaDeviceSynchronize());  // a kernel that reads through the victim may still be running
-    LBK_CUDA(cudaDestroyTextureObject(ctx->tex_cache[victim].obj));
-    ctx->tex_cache.erase(ctx->tex_cache.begin() + static_cast<long>(victim));
-  }
-  cudaResourceDesc rd{};
-  rd.resType                = cudaResourceTypeLinear;
-  rd.res.linear.devPtr      = const_cast<void*>(ptr);
-  rd.res.linear.desc        = texel_bytes == 16 ? cudaCreateChannelDesc<int4>() : cudaCreateChannelDesc<int2>();
-  rd.res.linear.sizeInBytes = bytes;
-  cudaTextureDesc td{};
-  td.readMode = cudaReadModeElementType;
-  cudaTextureObject_t obj = 0;
-  if (cudaCreateTextureObject(&obj, &rd, &td, nullptr) != cudaSuccess) {
-    cudaGetLastError();  // not fatal: the caller falls back to plain loads
-    return 0;
-  }
-  ctx->tex_cache.push_back({ptr, bytes, texel_bytes, obj, ctx->tex_clock});
-  return obj;
-}
-
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream)
 {
   int h = 0;
@@ -260,7 +218,6 @@ void lbk_context_destroy(lbk_context* ctx)
   cudaDeviceSynchronize();
   if (ctx->nccl_comm_side && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm_side);
   if (ctx->owns_nccl && ctx->nccl_comm && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm);
-  for (auto& e : ctx->tex_cache) cudaDestroyTextureObject(e.obj);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
   if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);

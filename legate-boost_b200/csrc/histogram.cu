@@ -23,11 +23,14 @@
 //   * accumulation is in int32 like the reference, but guarded: with m = the largest |q| of the
 //     call, at most floor((2^31-1)/m) rows are accumulated between flushes, so no partial sum can
 //     wrap whatever the bins are;
-//   * work is cut into (node chunk, feature groups, output) tickets by a planner on the device
-//     (k_hist_plan); blocks draw tickets from an atomic counter (persistent grid);
-//   * a node in one chunk owns its output region and flushes with plain stores; a node cut into
-//     several chunks leaves int32 partial sums in slots and k_hist_sum adds them up afterwards
-//     (without slot memory: 64-bit global atomics); chunks of <= 128 rows skip shared memory.
+//   * the planner on the device (k_hist_plan) hands the rows of the level to the resident blocks
+//     in equal static ranges (a block walks through the nodes its range touches) or, for small
+//     levels, as tickets drawn from a counter;
+//   * a node built in one piece owns its output region and flushes with plain stores, turned in
+//     shared memory so that the bins of a feature leave as whole 128-byte lines; the pieces of a
+//     node that reaches over a range boundary meet in a merge tree of arrival counters in which
+//     nobody waits (k_hist_smem); without scratch for the tree: 64-bit global atomics; chunks of
+//     <= 128 rows skip shared memory.
 #include <mutex>
 #include <string>
 
@@ -38,12 +41,12 @@ namespace lbk {
 namespace {
 
 constexpr int kHistThreads = 512;
-constexpr int kHistWarps   = kHistThreads / 32;
 constexpr int kTileRows    = 32;    // chunk sizes are multiples of this
-constexpr int kBatchRows   = 16;    // rows a warp takes per step of its pipeline (one per lane pair)
 constexpr int kDirectRows  = 128;   // chunks up to this size go straight to global atomics
 constexpr int kMinChunk    = 2048;
 constexpr int kSmemBins    = 256;   // bins per feature held by the private histogram
+constexpr int kFaultHistLayout = 31;  // status word: shared memory did not start where the kernel needs it
+constexpr int kTreeFanIn   = 4;     // partial sums that meet in one step of the merge tree
 
 struct HistParams {
   const void* bins;
@@ -55,27 +58,20 @@ struct HistParams {
   const int32_t* seg;
   const int32_t* slot_of_node;  // may be null = identity
   int n_nodes;
-  const int32_t* chunk_off;  // [n_nodes+1]
-  const int32_t* part_off;   // [n_nodes+1] partial-sum slots before each node (nodes with > 1 chunk); may be null
-  const int32_t* multi;      // [plan[5]] the nodes that were cut into several chunks; may be null
-  const int32_t* plan;       // [0] rows per chunk, [1] total chunks, [3] rows between flushes, [5] nodes in
-                             // `multi`, [6] slots usable
+  const int32_t* chunk_off;  // [n_nodes+1] chunks before each node (tickets drawn from a counter)
+  const int32_t* wpre;       // [n_nodes+1] built rows before each node (static ranges); may be null
+  const int32_t* plan;       // [0] rows per chunk, [1] total chunks, [3] rows between flushes, [4] rows per
+                             // range (0 = tickets from the counter), [7] ranges
   unsigned int* ticket;
-  cudaTextureObject_t tex_bins;   // the bin matrix as 16-byte texels, the pairs as 8-byte texels: the row
-  cudaTextureObject_t tex_pairs;  // gathers then go through the texture data pipe; 0 = plain loads
-  void* partial;             // partial-sum slots: [slot][2][mb * 32] of the accumulator type; may be null
+  unsigned int* arrive;      // counters of the merge trees (zeroed by the planner); may be null
+  void* partial;             // partial-sum slots of the merge trees: [slot][2][mb * 32 W] of the
+                             // accumulator type; may be null
+  int pairs_by_position;     // 1: gpair is stored in row_index order (pair i belongs to row_index[i]): a stream
+  int* status;               // the context's status word; may be null
   void* out;
 };
 
 __device__ inline unsigned SmemAddr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
-__device__ inline void RedShared(unsigned addr, int v)
-{
-  asm volatile("red.shared.add.s32 [%0], %1;\n" ::"r"(addr), "r"(v) : "memory");
-}
-__device__ inline void RedShared(unsigned addr, float v)
-{
-  asm volatile("red.shared.add.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
-}
 
 // largest |grad| and |hess| of a set of quantised pairs (for the stage-level entry point; the
 // tree builder gets them from the quantiser)
@@ -99,176 +95,137 @@ __global__ void k_max_abs(const int2* __restrict__ gpair, int64_t n, int* __rest
   }
 }
 
-// Single block: how the rows of every built node are cut into chunks on this level.
+// Single block: how the rows of the built nodes are handed to the resident blocks on this level.
 //
-// A ticket is (node chunk, feature group, output).  Resident blocks draw tickets from a counter, so
-// the level takes about ceil(tickets / resident) rounds of the largest ticket, or (list scheduling)
-// total work / resident + the largest ticket, whichever is smaller.  The planner evaluates that
-// bound for "one chunk per node" and for a geometric ladder of chunk sizes, with a per-ticket
-// overhead (clear, flush, partial sums) expressed in rows, and keeps the cheapest.  Chunks of a node
-// are equal in size.  A node with several chunks needs one partial-sum slot per chunk and (feature
-// group, output); candidates that need more slots than `slot_capacity` are not considered, and
-// plan[6] says whether the chosen cut can use the slots (1) or has to flush with atomics (0).
-constexpr int kPlanCandidates = 64;
-constexpr int kPlanCachedNodes = 4096;
-constexpr int kOverheadSingle = 2000;  // rows a block could have processed while it clears and flushes with stores
-constexpr int kOverheadMulti  = 5000;  // the same for clear + partial store + its share of the final sum (measured)
-
+// A unit of work is (rows, group set, output), GK = group sets x outputs per row.
+//
+// Static ranges (needs `wpre`, the merge-tree counters and slots): the built rows of the level, laid
+// end to end in node order, are cut into resident / GK equal ranges; block b takes range b / GK
+// for (group set, output) b % GK and walks through the nodes its range touches.  Every block gets the
+// same number of rows whatever the node sizes are (256 equal tickets on 148 blocks would otherwise
+// take two rounds, the second one partly empty).  A node that reaches over a range boundary is
+// built in pieces whose partial sums meet in a merge tree (see k_hist_smem).  Chosen when every
+// range gets at least 2 * kMinChunk rows.
+//
+// Tickets (everything else): one chunk per node when there are at least as many non-empty nodes as
+// resident blocks, else equal chunks of about total / resident rows whose sums are added to the
+// histogram with 64-bit atomics; blocks draw (chunk, group set, output) tickets from a counter.
 __global__ void __launch_bounds__(1024)
   k_hist_plan(const int32_t* __restrict__ seg, const int32_t* __restrict__ slot_of_node, int n_nodes, int GK,
               int resident, const int* __restrict__ max_abs, long long slot_capacity, int32_t* __restrict__ chunk_off,
-              int32_t* __restrict__ part_off, int32_t* __restrict__ multi, int32_t* __restrict__ plan,
-              unsigned int* __restrict__ ticket)
+              int32_t* __restrict__ wpre, unsigned int* __restrict__ arrive, int n_arrive,
+              int32_t* __restrict__ plan, unsigned int* __restrict__ ticket)
 {
   __shared__ long long red[32];
   __shared__ long long wsum[32];
   __shared__ long long carry;
   __shared__ long long total_s;
-  __shared__ int ch_s, cap_s, mode_s, multi_s;
-  __shared__ double cand_cost[kPlanCandidates];
-  __shared__ int cand_ch[kPlanCandidates];
-  __shared__ int cand_fit[kPlanCandidates];
-  __shared__ int rows_s[kPlanCachedNodes];  // rows of the first nodes (0 for nodes that are not built)
+  __shared__ int ch_s, nodes_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
-  auto rows_global = [&](int j) -> int {
+  auto rows_of = [&](int j) -> int {
     const bool built = slot_of_node == nullptr || slot_of_node[j] >= 0;
     const int r      = seg[j + 1] - seg[j];
     return built ? r : 0;
   };
-  // every later pass reads the node sizes many times: from shared memory where they fit
-  auto rows_of = [&](int j) -> int { return j < kPlanCachedNodes ? rows_s[j] : rows_global(j); };
-  long long rows = 0;
+  for (int i = tid; i < n_arrive; i += blockDim.x) arrive[i] = 0u;
+  long long rows = 0, nonempty = 0;
   for (int j = tid; j < n_nodes; j += blockDim.x) {
-    const int r = rows_global(j);
-    if (j < kPlanCachedNodes) rows_s[j] = r;
+    const int r = rows_of(j);
     rows += r;
+    nonempty += r > 0;
   }
+  rows += nonempty << 40;
   for (int off = 16; off >= 1; off >>= 1) rows += __shfl_down_sync(0xffffffffu, rows, off);
   if (lane == 0) red[warp] = rows;
   __syncthreads();
   if (tid == 0) {
     long long total = 0;
     for (int w = 0; w < n_warps; ++w) total += red[w];
-    total_s = total;
+    nodes_s = static_cast<int>(total >> 40);
+    total_s = total & ((1ll << 40) - 1);
     int m   = 1;
     if (max_abs) m = max(1, max(max_abs[0], max_abs[1]));
-    const int safe = max_abs ? 2147483647 / m : 2147483647;
-    plan[3]        = safe;
-    // chunks that can use partial-sum slots never need a flush in the middle
-    cap_s = safe >= (1 << 30) ? (1 << 30) : (safe & ~(kTileRows - 1));
-    carry = 0;
-    multi_s = 0;
-    chunk_off[0] = 0;
-    if (part_off) part_off[0] = 0;
+    plan[3] = max_abs ? 2147483647 / m : 2147483647;
   }
   __syncthreads();
   const long long total = total_s;
-  const int cap         = cap_s;
 
-  // candidate 0: one chunk per node; candidate c > 0: total work / (resident * 2^(c / 16)) rows
-  for (int c = warp; c < kPlanCandidates; c += n_warps) {
-    long long ch = 1ll << 30;
-    if (c > 0) {
-      const double f = exp2(static_cast<double>(c - 1) / 16.0);
-      ch             = static_cast<long long>(static_cast<double>(total) * GK / (static_cast<double>(resident) * f)) + 1;
-      if (ch < kMinChunk) ch = kMinChunk;
-      ch = (ch + kTileRows - 1) / kTileRows * kTileRows;
-      if (ch > (1ll << 30)) ch = 1ll << 30;
+  // exclusive scan over the nodes: store(j, sum of value(0..j)); 1024 nodes per step
+  auto scan_nodes = [&](auto value, auto store) {
+    __syncthreads();
+    if (tid == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < n_nodes; base += blockDim.x) {
+      const int j       = base + tid;
+      const long long c = j < n_nodes ? value(j) : 0;
+      long long incl    = c;
+      for (int off = 1; off < 32; off <<= 1) {
+        const long long n = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += n;
+      }
+      if (lane == 31) wsum[warp] = incl;
+      __syncthreads();
+      if (warp == 0) {
+        const long long w = lane < n_warps ? wsum[lane] : 0;
+        long long wi      = w;
+        for (int off = 1; off < 32; off <<= 1) {
+          const long long n = __shfl_up_sync(0xffffffffu, wi, off);
+          if (lane >= off) wi += n;
+        }
+        wsum[lane] = wi - w;
+      }
+      __syncthreads();
+      const long long before = carry + wsum[warp];
+      if (j < n_nodes) store(j, before + incl);
+      __syncthreads();
+      if (tid == blockDim.x - 1) carry = before + incl;
+      __syncthreads();
     }
-    const long long chs = cap >= kTileRows && ch > cap ? cap : ch;  // with slots: never beyond the safe count
-    long long tickets = 0, multi = 0, cost = 0;
-    int biggest = 0;
-    for (int j = lane; j < n_nodes; j += 32) {
-      const int r = rows_of(j);
-      if (r <= 0) continue;
-      const int nch  = static_cast<int>((r + chs - 1) / chs);
-      const int size = (r + nch - 1) / nch + (nch > 1 ? kOverheadMulti : kOverheadSingle);
-      tickets += nch;
-      if (nch > 1) multi += nch;
-      cost += static_cast<long long>(size) * nch;
-      biggest = max(biggest, size);
-    }
-    for (int off = 16; off >= 1; off >>= 1) {
-      tickets += __shfl_down_sync(0xffffffffu, tickets, off);
-      multi += __shfl_down_sync(0xffffffffu, multi, off);
-      cost += __shfl_down_sync(0xffffffffu, cost, off);
-      biggest = max(biggest, __shfl_down_sync(0xffffffffu, biggest, off));
-    }
-    if (lane == 0) {
-      const double T      = static_cast<double>(tickets) * GK;
-      const double rounds = ceil(T / resident) * biggest;
-      const double list   = static_cast<double>(cost) * GK / resident + biggest;
-      cand_cost[c]        = rounds < list ? rounds : list;
-      cand_ch[c]          = static_cast<int>(chs);
-      cand_fit[c]         = multi * GK <= slot_capacity;
+  };
+
+  // static ranges
+  int range_rows = 0, ranges = 0;
+  if (wpre != nullptr && arrive != nullptr && GK <= resident && total < (1ll << 31)) {
+    ranges      = resident / GK;
+    long long q = (total + ranges - 1) / ranges;
+    q           = (q + kTileRows - 1) / kTileRows * kTileRows;
+    if (q >= 2 * kMinChunk) {
+      ranges = static_cast<int>((total + q - 1) / q);
+      if (static_cast<long long>(kTreeFanIn) * (ranges - 1) * GK <= slot_capacity &&
+          static_cast<long long>(kTreeFanIn) * (ranges - 1) * GK <= n_arrive)
+        range_rows = static_cast<int>(q);
     }
   }
-  __syncthreads();
+  if (wpre != nullptr) {
+    scan_nodes([&](int j) -> long long { return rows_of(j); },
+               [&](int j, long long incl) { wpre[j + 1] = static_cast<int>(incl); });
+    if (tid == 0) wpre[0] = 0;
+  }
+
+  // tickets
   if (tid == 0) {
-    int best = -1;
-    for (int c = 0; c < kPlanCandidates; ++c)
-      if (slot_capacity > 0 && cap >= kTileRows && cand_fit[c] && (best < 0 || cand_cost[c] < cand_cost[best] * 0.98)) best = c;
-    if (best >= 0) {
-      ch_s   = cand_ch[best];
-      mode_s = 1;
-    } else {
-      // no slots (or too few even for one chunk per node): the cut of the first candidates that
-      // gives every resident block about one ticket, flushed with atomics
-      long long ch = (total * GK + resident - 1) / resident;
-      long long nodes = 0;
-      for (int j = 0; j < n_nodes; ++j) nodes += rows_of(j) > 0;
-      if (nodes * GK >= resident) ch = 1ll << 30;
-      if (ch < kMinChunk) ch = kMinChunk;
-      ch = (ch + kTileRows - 1) / kTileRows * kTileRows;
-      if (ch > (1ll << 30)) ch = 1ll << 30;
-      ch_s   = static_cast<int>(ch);
-      mode_s = 0;
-    }
+    long long ch = (total * GK + resident - 1) / resident;
+    if (static_cast<long long>(nodes_s) * GK >= resident) ch = 1ll << 30;
+    if (ch < kMinChunk) ch = kMinChunk;
+    ch = (ch + kTileRows - 1) / kTileRows * kTileRows;
+    if (ch > (1ll << 30)) ch = 1ll << 30;
+    ch_s = static_cast<int>(ch);
   }
   __syncthreads();
   const int ch = ch_s;
-  // exclusive scans over the nodes: chunks (low word) and partial-sum slots (high word)
-  for (int base = 0; base < n_nodes; base += blockDim.x) {
-    const int j = base + tid;
-    long long c = 0;
-    if (j < n_nodes) {
-      const int r   = rows_of(j);
-      const int nch = r > 0 ? (r + ch - 1) / ch : 0;
-      c             = nch + (nch > 1 ? (static_cast<long long>(nch) << 32) : 0);
-      if (nch > 1 && multi) multi[atomicAdd(&multi_s, 1)] = j;
-    }
-    long long incl = c;
-    for (int off = 1; off < 32; off <<= 1) {
-      const long long n = __shfl_up_sync(0xffffffffu, incl, off);
-      if (lane >= off) incl += n;
-    }
-    if (lane == 31) wsum[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-      const long long w = lane < n_warps ? wsum[lane] : 0;
-      long long wi      = w;
-      for (int off = 1; off < 32; off <<= 1) {
-        const long long n = __shfl_up_sync(0xffffffffu, wi, off);
-        if (lane >= off) wi += n;
-      }
-      wsum[lane] = wi - w;
-    }
-    __syncthreads();
-    const long long before = carry + wsum[warp];
-    if (j < n_nodes) {
-      chunk_off[j + 1] = static_cast<int>((before + incl) & 0xffffffffll);
-      if (part_off) part_off[j + 1] = static_cast<int>((before + incl) >> 32);
-    }
-    __syncthreads();
-    if (tid == blockDim.x - 1) carry = before + incl;
-    __syncthreads();
-  }
+  scan_nodes(
+    [&](int j) -> long long {
+      const int r = rows_of(j);
+      return r > 0 ? (r + ch - 1) / ch : 0;
+    },
+    [&](int j, long long incl) { chunk_off[j + 1] = static_cast<int>(incl); });
   if (tid == 0) {
-    plan[0] = ch;
-    plan[1] = static_cast<int>(carry & 0xffffffffll);
-    plan[5] = multi_s;
-    plan[6] = mode_s;
-    *ticket = 0;
+    chunk_off[0] = 0;
+    plan[0]      = ch;
+    plan[1]      = static_cast<int>(carry);
+    plan[4]      = range_rows;
+    plan[7]      = range_rows > 0 ? ranges : 0;
+    *ticket      = 0;
   }
 }
 
@@ -289,12 +246,15 @@ struct Acc<false> {
     *reinterpret_cast<longlong2*>(dst) = make_longlong2(g, h);
   }
   __device__ static bool nonzero(int g, int h) { return (g | h) != 0; }
-  using wide_t = long long;
-  __device__ static long long widen(int bits) { return bits; }
-  __device__ static void add_wide(out_t* dst, long long g, long long h)
+  __device__ static int4 add4(int4 a, int4 b) { return make_int4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+  __device__ static void red_shared(unsigned addr, int bits)
   {
-    atomicAdd(reinterpret_cast<unsigned long long*>(&dst->grad), static_cast<unsigned long long>(g));
-    atomicAdd(reinterpret_cast<unsigned long long*>(&dst->hess), static_cast<unsigned long long>(h));
+    asm volatile("red.shared.add.s32 [%0], %1;\n" ::"r"(addr), "r"(bits) : "memory");
+  }
+  template <int kOffset>
+  __device__ static void red_shared_at(unsigned addr, int bits)
+  {
+    asm volatile("red.shared.add.s32 [%0+%2], %1;\n" ::"r"(addr), "r"(bits), "n"(kOffset) : "memory");
   }
 };
 template <>
@@ -312,21 +272,36 @@ struct Acc<true> {
     *reinterpret_cast<double2*>(dst) = make_double2(g, h);
   }
   __device__ static bool nonzero(float g, float h) { return g != 0.f || h != 0.f; }
-  using wide_t = double;
-  __device__ static double widen(int bits) { return static_cast<double>(__int_as_float(bits)); }
-  __device__ static void add_wide(out_t* dst, double g, double h)
+  __device__ static int4 add4(int4 a, int4 b)
   {
-    atomicAdd(&dst->grad, g);
-    atomicAdd(&dst->hess, h);
+    return make_int4(__float_as_int(__int_as_float(a.x) + __int_as_float(b.x)),
+                     __float_as_int(__int_as_float(a.y) + __int_as_float(b.y)),
+                     __float_as_int(__int_as_float(a.z) + __int_as_float(b.z)),
+                     __float_as_int(__int_as_float(a.w) + __int_as_float(b.w)));
+  }
+  __device__ static void red_shared(unsigned addr, int bits)
+  {
+    asm volatile("red.shared.add.f32 [%0], %1;\n" ::"r"(addr), "f"(__int_as_float(bits)) : "memory");
+  }
+  template <int kOffset>
+  __device__ static void red_shared_at(unsigned addr, int bits)
+  {
+    asm volatile("red.shared.add.f32 [%0+%2], %1;\n" ::"r"(addr), "f"(__int_as_float(bits)), "n"(kOffset) : "memory");
   }
 };
 
-// What a chunk index means: the node, the chunk's place in it, the rows.
-struct Chunk {
-  int j, ci, nchunks, slot, rb, re;
+// One piece of work of a block: rows [rb, re) of row_index, all of one node.
+struct Piece {
+  int j;          // node of the batch
+  int slot;       // the node's histogram in `out`
+  int rb, re;
+  int index;      // which piece of its node this is, 0 .. pieces-1
+  int pieces;     // pieces the node is built in
+  int tree_base;  // first slot / counter of the node's merge tree (pieces > 1, static ranges)
+  int node_rows;  // rows of the whole node
 };
 
-__device__ inline Chunk DecodeChunk(const HistParams& p, int c)
+__device__ inline Piece DecodeChunk(const HistParams& p, int c)
 {
   // node that owns chunk c: last j with chunk_off[j] <= c
   int lo = 0, hi = p.n_nodes;
@@ -334,17 +309,19 @@ __device__ inline Chunk DecodeChunk(const HistParams& p, int c)
     const int mid = (lo + hi) >> 1;
     if (p.chunk_off[mid] <= c) lo = mid; else hi = mid;
   }
-  Chunk ch;
-  ch.j       = lo;
-  ch.nchunks = p.chunk_off[lo + 1] - p.chunk_off[lo];
-  ch.slot    = p.slot_of_node ? p.slot_of_node[lo] : lo;
-  ch.ci      = c - p.chunk_off[lo];
+  Piece pc;
+  pc.j         = lo;
+  pc.pieces    = p.chunk_off[lo + 1] - p.chunk_off[lo];
+  pc.slot      = p.slot_of_node ? p.slot_of_node[lo] : lo;
+  pc.index     = c - p.chunk_off[lo];
+  pc.tree_base = -1;
   // the chunks of a node are equal in size (a multiple of 32 rows, the last one takes the rest)
   const int nrows = p.seg[lo + 1] - p.seg[lo];
-  const int size  = ch.nchunks > 1 ? ((nrows + ch.nchunks - 1) / ch.nchunks + kTileRows - 1) / kTileRows * kTileRows : nrows;
-  ch.rb = min(p.seg[lo + 1], p.seg[lo] + ch.ci * size);
-  ch.re = min(p.seg[lo + 1], ch.rb + size);
-  return ch;
+  pc.node_rows    = nrows;
+  const int size  = pc.pieces > 1 ? ((nrows + pc.pieces - 1) / pc.pieces + kTileRows - 1) / kTileRows * kTileRows : nrows;
+  pc.rb = min(p.seg[lo + 1], p.seg[lo] + pc.index * size);
+  pc.re = min(p.seg[lo + 1], pc.rb + size);
+  return pc;
 }
 
 // Rows [b, e) of one node, features [f0, f0 + 32 * groups): one lane per feature, the warps of the
@@ -363,7 +340,7 @@ __device__ inline void DirectRows(const HistParams& p, int b, int e, int f0, int
     typename A::out_t* obase = onode + p.row_ptr[feat];
     for (int r = b + warp; r < e; r += n_warps) {
       const int ridx = p.row_index[r];
-      const in_t v   = gpair[static_cast<int64_t>(ridx) * p.K + k];
+      const in_t v   = gpair[static_cast<int64_t>(p.pairs_by_position ? r : ridx) * p.K + k];
       const int bin  = bins[static_cast<int64_t>(ridx) * pitch + feat];
       A::add_global(obase + bin, v.x, v.y);
     }
@@ -387,30 +364,200 @@ __global__ void __launch_bounds__(kHistThreads)
     if (t >= total) break;
     const int k    = static_cast<int>(t % p.K);
     const int g    = static_cast<int>((t / p.K) % p.G);
-    const Chunk ch = DecodeChunk(p, static_cast<int>(t / (static_cast<long long>(p.K) * p.G)));
-    typename A::out_t* onode = static_cast<typename A::out_t*>(p.out) + (static_cast<int64_t>(ch.slot) * p.K + k) * p.B;
-    DirectRows<BinT, A>(p, ch.rb, ch.re, g * kGroup, 1, k, onode, warp, kHistWarps, lane);
+    const Piece pc = DecodeChunk(p, static_cast<int>(t / (static_cast<long long>(p.K) * p.G)));
+    typename A::out_t* onode = static_cast<typename A::out_t*>(p.out) + (static_cast<int64_t>(pc.slot) * p.K + k) * p.B;
+    DirectRows<BinT, A>(p, pc.rb, pc.re, g * kGroup, 1, k, onode, warp, kHistThreads / 32, lane);
+  }
+}
+
+// One update step of a lane: byte J of its 16 bin bytes (already permuted so that step J reads
+// the static byte J), both words of the pair.  `lane_word` is the shared-memory address of the
+// lane's word in bin row 0 of the gradient histogram.
+template <typename A, int W, int J>
+__device__ inline void HistStep(const unsigned (&x)[4], unsigned lane_word, const int2& v)
+{
+  constexpr int kHistBytes = kSmemBins * kGroup * W * 4;
+  if (W == 2) {
+    // the histogram starts on a multiple of its own size (64 KB), a bin row is 256 bytes: the
+    // address is (bin << 8) | (lane_word ^ skew), one byte permute and one three-input logic op
+    constexpr unsigned cj = ((J & 7u) << 2) | ((J >> 3) << 7);
+    const unsigned b8     = __byte_perm(x[J >> 2], 0u, 0x4404u | ((J & 3) << 4));
+    unsigned addr;
+    asm("lop3.b32 %0, %1, %2, %3, 0xF6;\n" : "=r"(addr) : "r"(b8), "r"(lane_word), "n"(cj));
+    A::red_shared(addr, v.x);
+    A::template red_shared_at<kHistBytes>(addr, v.y);
+  } else {
+    constexpr unsigned cj = 4u * J;
+    const unsigned bin    = __byte_perm(x[J >> 2], 0u, 0x4440u | (J & 3));
+    const unsigned addr   = (bin * (kGroup * 4) + lane_word) ^ cj;
+    A::red_shared(addr, v.x);
+    A::template red_shared_at<kHistBytes>(addr, v.y);
+  }
+}
+
+// The rows [sb, se) of row_index, all of one node, added to the block's private histograms: the
+// main loop of k_hist_smem for one warp.  The warps of the block take the batches of 32 / (2 W)
+// rows in turn.  Every load of the loop is unconditional: batch numbers beyond the warp's last one
+// are clamped to it (the rows are fetched again and dropped), lanes whose feature group does not
+// exist read the group that does and add zero pairs, and the last, partial batch of the range is
+// handled after the loop.  In flight per warp: the rows of the next two batches and the row ids of
+// the two after; the loop is unrolled three times so that the three row buffers rotate by name.
+// The row's bin bytes come with a plain load that bypasses L1 and asks L2 for the whole 128-byte
+// line (the other half of the row is wanted soon by the block that builds the neighbouring
+// groups).  kByPosition: the pairs are stored in row_index order and read as a stream; else they are
+// gathered by row id.
+template <typename A, int W, bool kByPosition>
+__device__ __forceinline__ void HistRows(const HistParams& p, int sb, int se, int g0, int groups, int k, int warp,
+                                         int lane, unsigned lane_word)
+{
+  using in_t = typename A::in_t;
+  constexpr int kWarps        = kHistThreads * W / 32;
+  constexpr int kLanesPerRow  = 2 * W;
+  constexpr int kRowsPerBatch = 32 / kLanesPerRow;
+  const unsigned rslot = lane / kLanesPerRow, q = lane % kLanesPerRow;
+  const unsigned wsel = rslot >> 2, bsel = rslot & 3;
+  const unsigned perm = bsel == 0 ? 0x3210u : bsel == 1 ? 0x2301u : bsel == 2 ? 0x1032u : 0x0123u;
+  const unsigned sel0 = perm + ((wsel & 1) ? 0x4444u : 0u), sel1 = perm + ((wsel & 1) ? 0u : 0x4444u);
+  const bool lane_on  = static_cast<int>(q >> 1) < groups;  // the group this lane's 16 bytes belong to exists
+  const unsigned q_eff = lane_on ? q : (q & 1u);
+  const int pair_mask  = lane_on ? -1 : 0;
+  const int64_t pitch  = static_cast<int64_t>(p.G) * kGroup;
+  const unsigned char* gb = static_cast<const unsigned char*>(p.bins) + g0 * kGroup + q_eff * 16;
+  const in_t* gpair    = static_cast<const in_t*>(p.gpair);
+  const int pos0       = sb + static_cast<int>(rslot);  // the lane's row of batch 0, as a position in row_index
+  const int32_t* rp    = p.row_index + pos0;            // + batch * kRowsPerBatch
+
+  // rid: the row; pos: its position in row_index (only used for pairs stored by position)
+  auto load = [&](int rid, int pos, int4& w, int2& v) {
+    const int4* ap = reinterpret_cast<const int4*>(gb + static_cast<int64_t>(rid) * pitch);
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.s32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                 : "l"(ap));
+    if (kByPosition) v = __ldcs(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(pos) * p.K + k));
+    else v = __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid) * p.K + k));
+    if (W == 2) {
+      v.x &= pair_mask;
+      v.y &= pair_mask;
+    }
+  };
+  auto consume = [&](const int4& w, const int2& v) {
+    unsigned x[4];
+    if (W == 2) {
+      x[0] = __byte_perm(w.x, w.y, sel0);
+      x[1] = __byte_perm(w.x, w.y, sel1);
+      x[2] = __byte_perm(w.z, w.w, sel0);
+      x[3] = __byte_perm(w.z, w.w, sel1);
+    } else {
+      const unsigned a0 = (wsel & 2) ? w.z : w.x, a1 = (wsel & 2) ? w.w : w.y;
+      const unsigned b0 = (wsel & 2) ? w.x : w.z, b1 = (wsel & 2) ? w.y : w.w;
+      x[0] = __byte_perm(a0, a1, sel0);
+      x[1] = __byte_perm(a0, a1, sel1);
+      x[2] = __byte_perm(b0, b1, sel0);
+      x[3] = __byte_perm(b0, b1, sel1);
+    }
+    HistStep<A, W, 0>(x, lane_word, v);
+    HistStep<A, W, 1>(x, lane_word, v);
+    HistStep<A, W, 2>(x, lane_word, v);
+    HistStep<A, W, 3>(x, lane_word, v);
+    HistStep<A, W, 4>(x, lane_word, v);
+    HistStep<A, W, 5>(x, lane_word, v);
+    HistStep<A, W, 6>(x, lane_word, v);
+    HistStep<A, W, 7>(x, lane_word, v);
+    HistStep<A, W, 8>(x, lane_word, v);
+    HistStep<A, W, 9>(x, lane_word, v);
+    HistStep<A, W, 10>(x, lane_word, v);
+    HistStep<A, W, 11>(x, lane_word, v);
+    HistStep<A, W, 12>(x, lane_word, v);
+    HistStep<A, W, 13>(x, lane_word, v);
+    HistStep<A, W, 14>(x, lane_word, v);
+    HistStep<A, W, 15>(x, lane_word, v);
+  };
+
+  const int n_here  = se - sb;
+  const int nb_full = n_here / kRowsPerBatch;
+  int cnt           = nb_full > warp ? (nb_full - warp + kWarps - 1) / kWarps : 0;  // this warp's whole batches
+  if (cnt > 0) {
+    const int bl = warp + (cnt - 1) * kWarps;  // the warp's last batch
+    auto rid_at  = [&](int bb) -> int { return __ldcg(rp + bb * kRowsPerBatch); };
+    int b = warp;
+    int4 wa, wb, wc;
+    int2 va, vb, vc;
+    {
+      const int b1 = min(b + kWarps, bl);
+      load(rid_at(b), pos0 + b * kRowsPerBatch, wa, va);
+      load(rid_at(b1), pos0 + b1 * kRowsPerBatch, wb, vb);
+    }
+    int ba = min(b + 2 * kWarps, bl), bb = min(b + 3 * kWarps, bl);
+    int ra = rid_at(ba), rb = rid_at(bb);
+#pragma unroll 1
+    while (cnt >= 3) {
+      load(ra, pos0 + ba * kRowsPerBatch, wc, vc);
+      ba = min(b + 4 * kWarps, bl);
+      ra = rid_at(ba);
+      consume(wa, va);
+      load(rb, pos0 + bb * kRowsPerBatch, wa, va);
+      bb = min(b + 5 * kWarps, bl);
+      rb = rid_at(bb);
+      consume(wb, vb);
+      load(ra, pos0 + ba * kRowsPerBatch, wb, vb);
+      ba = min(b + 6 * kWarps, bl);
+      ra = rid_at(ba);
+      consume(wc, vc);
+      // now the buffers hold batches b + 3, b + 4 (in units of kWarps) and the ids b + 5 (rb), b + 6 (ra)
+      int t = ra; ra = rb; rb = t;
+      t = ba; ba = bb; bb = t;
+      b += 3 * kWarps;
+      cnt -= 3;
+    }
+    if (cnt >= 1) consume(wa, va);
+    if (cnt >= 2) consume(wb, vb);
+  }
+  // the partial batch at the end of the range
+  const int tail = n_here - nb_full * kRowsPerBatch;
+  if (tail > 0 && warp == nb_full % kWarps) {
+    const bool valid = static_cast<int>(rslot) < tail;
+    // lanes without a row read the first row of the range (it exists) and add nothing
+    const int pos    = valid ? pos0 + nb_full * kRowsPerBatch : sb;
+    const int rid    = __ldcg(p.row_index + pos);
+    int4 w;
+    int2 v;
+    load(rid, pos, w, v);
+    if (!valid) v = make_int2(0, 0);
+    consume(w, v);
   }
 }
 
 // One-byte bins, at most 256 per feature: private histograms in shared memory.
 //
-// W = 1: a ticket covers one 32-feature group, 512 threads, two blocks per SM.
-// W = 2: a ticket covers two neighbouring groups (64 features), 1024 threads, one block per SM.
+// W = 1: a unit covers one 32-feature group, 512 threads, two blocks per SM.
+// W = 2: a unit covers two neighbouring groups (64 features), 1024 threads, one block per SM.
 // The wide form exists because the load/store pipe of the SM spends one pass per distinct
 // 128-byte line a gather touches, however few bytes it takes from it: with 64 bin bytes per row
 // the row gather costs half as many passes per update, and the row ids and gradient pairs are
 // fetched once for two groups.
 //
-// Every warp runs its own pipeline over batches of 32 / (2 W) rows (no block barrier inside, no
-// staging in shared memory).  2 W lanes own one row of the batch and load its bin bytes straight
-// from global memory into registers, 16 bytes per lane.  In step j of 16 the lanes of row slot r
-// handle byte (j xor r) of their 16, and the histogram words of a bin are laid out so that the 32
-// lanes of a warp always update 32 different banks, whatever the bins:
+// Shared memory: the gradient histogram [256 bins][32 W words] sits at shared address H = its own
+// size (64 KB for W = 2), the hessian histogram at 2 H, so that the bits of (bin << 8), of the word
+// inside a bin row and of the base never overlap; what lies below H is the staging area of the
+// flush.  Every warp runs its own pipeline over batches of 32 / (2 W) rows (no block barrier
+// inside).  2 W lanes own one row of the batch and load its bin bytes straight from global memory
+// into registers, 16 bytes per lane.  In step j of 16 the lanes of row slot r handle byte (j xor r)
+// of their 16, and the histogram words of a bin are laid out so that the 32 lanes of a warp always
+// update 32 different banks, whatever the bins:
 //   W = 1 (r < 16, quarter q < 2):  word = 16 q + byte                   (bank = word)
 //   W = 2 (r < 8,  quarter q < 4):  word = 32 (byte / 8) + 8 q + byte % 8 (bank = 8 q + byte % 8)
 // The bytes are permuted once per batch (a word swap and one byte permute per word) so that step
 // j reads the static byte j.  Per 32 updates that leaves the two reductions on the pipe.
+//
+// Flush: a warp takes a tile of 8 bins x 32 words, turns it in its staging area (a skewed 8 x 32
+// array, conflict free both ways) and writes, per word, the 8 bins of a feature as 128 contiguous
+// bytes of the output.
+//
+// Merge tree (static ranges): the P pieces of a node that reaches over range boundaries are summed
+// without waits.  A piece writes its 32-bit partial sums to its slot and adds one to the counter
+// of its group of four; the last one to arrive adds the others' slots to its own sums and goes on
+// as one member of the next level, until one block holds the node's total and writes the
+// histogram.  Nobody waits for anybody: whoever arrives first leaves.
 template <bool kFloat, int W>
 __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
   k_hist_smem(const HistParams p)
@@ -422,85 +569,112 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
   constexpr int kThreads      = kHistThreads * W;
   constexpr int kWarps        = kThreads / 32;
   constexpr int kCols         = kGroup * W;   // histogram words per bin
+  constexpr int kHistBytes    = kSmemBins * kCols * 4;
   constexpr int kLanesPerRow  = 2 * W;
   constexpr int kRowsPerBatch = 32 / kLanesPerRow;
+  constexpr int kStageWords   = 256;  // per warp: 8 bins x 32 words
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  // the column arithmetic of the main loop needs the histogram on a 256-byte boundary
-  smem_t* hg = reinterpret_cast<smem_t*>(smem_raw + ((256u - (SmemAddr(smem_raw) & 255u)) & 255u));
-  smem_t* hh = hg + kSmemBins * kCols;  // every byte value is a valid bin row
   __shared__ unsigned int s_ticket;
+  __shared__ int s_rp[kCols + 1];  // row_ptr of the unit's features (clamped at F)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int total_chunks = p.plan[1];
-  const int rows_safe    = p.plan[3];
-  const bool use_slots   = p.plan[6] != 0 && p.partial != nullptr;
-  const int GP           = (p.G + W - 1) / W;  // tickets per chunk and output
-  const long long total  = static_cast<long long>(total_chunks) * GP * p.K;
-  const in_t* gpair      = static_cast<const in_t*>(p.gpair);
-  const int hist_words   = p.mb * kCols;
-  const int64_t pitch    = static_cast<int64_t>(p.G) * kGroup;  // bins are row-major, rows padded to whole groups
-  // feature (relative to the ticket's first) of histogram word w
+  const unsigned base = SmemAddr(smem_raw);
+  unsigned dyn_bytes;
+  asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+  const unsigned hg_addr = static_cast<unsigned>(kHistBytes);
+  // the staging area has to end before the histograms begin, and they inside what was asked for
+  if (base + kWarps * kStageWords * 4 > hg_addr || hg_addr + 2u * kHistBytes > base + dyn_bytes) {
+    if (tid == 0 && p.status != nullptr) atomicExch(p.status, kFaultHistLayout);
+    return;
+  }
+  smem_t* stage_all = reinterpret_cast<smem_t*>(smem_raw);
+  smem_t* hg        = reinterpret_cast<smem_t*>(smem_raw + (hg_addr - base));
+  smem_t* hh        = hg + kSmemBins * kCols;
+
+  const int rows_safe   = p.plan[3];
+  const int GP          = (p.G + W - 1) / W;  // group sets per row
+  const int range_rows  = p.wpre != nullptr ? p.plan[4] : 0;
+  const in_t* gpair     = static_cast<const in_t*>(p.gpair);
+  const int hist_words  = p.mb * kCols;
+  const int64_t pitch   = static_cast<int64_t>(p.G) * kGroup;  // bins are row-major, rows padded to whole groups
+  // chunks that merge through slots never flush in the middle: they stay below the safe count
+  const int cap_rows    = rows_safe >= (1 << 30) ? (1 << 30) : (rows_safe & ~(kTileRows - 1));
+  // feature (relative to the unit's first) of histogram word w
   auto feature_of_word = [](int w) -> int { return W == 1 ? w : 16 * ((w >> 3) & 3) + 8 * (w >> 5) + (w & 7); };
 
-  while (true) {
-    __syncthreads();
-    if (tid == 0) s_ticket = atomicAdd(p.ticket, 1u);
-    __syncthreads();
-    const long long t = s_ticket;
-    if (t >= total) break;
-    const int k    = static_cast<int>(t % p.K);
-    const int gp   = static_cast<int>((t / p.K) % GP);
-    const Chunk ch = DecodeChunk(p, static_cast<int>(t / (static_cast<long long>(p.K) * GP)));
-    const int g0   = gp * W;
-    const int groups = min(W, p.G - g0);
-    out_t* onode   = static_cast<out_t*>(p.out) + (static_cast<int64_t>(ch.slot) * p.K + k) * p.B;
+  const unsigned rslot    = lane / kLanesPerRow, q = lane % kLanesPerRow;
+  const unsigned wsel     = rslot >> 2, bsel = rslot & 3;
+  const unsigned perm     = bsel == 0 ? 0x3210u : bsel == 1 ? 0x2301u : bsel == 2 ? 0x1032u : 0x0123u;
+  const unsigned lane_word = hg_addr + (W == 1 ? 16 * q + rslot : 8 * q + rslot) * 4;
 
-    // a chunk that will leave partial sums in a slot cannot take the direct path: the last
-    // chunk of its node stores the total and would overwrite what the atomics added
-    const bool slots = use_slots && ch.nchunks > 1 && rows_safe >= kTileRows;
-    if (rows_safe < kTileRows || (ch.re - ch.rb <= kDirectRows && !slots)) {
-      DirectRows<uint8_t, A>(p, ch.rb, ch.re, g0 * kGroup, groups, k, onode, warp, kWarps, lane);
-      continue;
+  auto zero = [&]() {
+    int4* g4 = reinterpret_cast<int4*>(hg);
+    int4* h4 = reinterpret_cast<int4*>(hh);
+    for (int e = tid; e < (hist_words >> 2); e += kThreads) {
+      g4[e] = make_int4(0, 0, 0, 0);
+      h4[e] = make_int4(0, 0, 0, 0);
     }
+  };
 
-    // the word a thread meets in the strided loops below is always the same one
-    const int my_word  = tid % kCols;
-    const int my_feat  = g0 * kGroup + feature_of_word(my_word);
-    const int my_fbeg  = my_feat < p.F ? p.row_ptr[my_feat] : 0;
-    const int my_fbins = my_feat < p.F ? p.row_ptr[my_feat + 1] - my_fbeg : 0;
-    bool use_atomics   = ch.nchunks > 1 && !slots;
-    auto flush = [&](bool atomics) {
-      out_t* obase = onode + my_fbeg;
-      for (int e = tid; e < hist_words; e += kThreads) {  // e % kCols == my_word for every e of a thread
-        const int bin = e / kCols;
-        if (bin < my_fbins) {
-          const smem_t vg = hg[e], vh = hh[e];
-          if (A::nonzero(vg, vh)) {
-            if (atomics) A::add_global(obase + bin, vg, vh); else A::store_global(obase + bin, vg, vh);
-          }
-        }
-      }
-    };
-    auto zero = [&]() {
-      for (int e = tid; e < hist_words; e += kThreads) {
-        hg[e] = smem_t(0);
-        hh[e] = smem_t(0);
-      }
-    };
+  // One piece: accumulate its rows, then flush / merge.
+  auto process = [&](const Piece& pc, int gp, int k) {
+    const int g0     = gp * W;
+    const int groups = min(W, p.G - g0);
+    out_t* onode     = static_cast<out_t*>(p.out) + (static_cast<int64_t>(pc.slot) * p.K + k) * p.B;
+    const bool tree  = pc.pieces > 1 && pc.tree_base >= 0 && p.partial != nullptr && pc.node_rows <= cap_rows &&
+                      rows_safe >= kTileRows;
+    if (rows_safe < kTileRows || (pc.re - pc.rb <= kDirectRows && !tree)) {
+      DirectRows<uint8_t, A>(p, pc.rb, pc.re, g0 * kGroup, groups, k, onode, warp, kWarps, lane);
+      return;
+    }
+    __syncthreads();  // whoever still reads the histogram or s_rp of the piece before
+    for (int i = tid; i <= kCols; i += kThreads) s_rp[i] = p.row_ptr[min(p.F, g0 * kGroup + i)];
     zero();
     __syncthreads();
 
-    const unsigned rslot    = lane / kLanesPerRow, q = lane % kLanesPerRow;
-    const bool lane_on      = static_cast<int>(q >> 1) < groups;  // the group this lane's 16 bytes belong to exists
-    const unsigned wsel     = rslot >> 2, bsel = rslot & 3;
-    const unsigned perm     = bsel == 0 ? 0x3210u : bsel == 1 ? 0x2301u : bsel == 2 ? 0x1032u : 0x0123u;
-    const unsigned lanebase = SmemAddr(hg) + (W == 1 ? 16 * q + rslot : 8 * q + rslot) * 4;
-    const unsigned hh_off   = static_cast<unsigned>(kSmemBins) * kCols * 4;
-    const unsigned char* gb = static_cast<const unsigned char*>(p.bins) + g0 * kGroup + q * 16;
+    // the flush: tiles of 8 bins x 32 words, turned in the warp's staging area
+    auto flush = [&](bool atomics) {
+      smem_t* stage      = stage_all + warp * kStageWords;
+      const int n_btiles = (p.mb + 7) >> 3;
+      const int a = lane >> 3, b = lane & 7;
+      for (int t = warp; t < n_btiles * W; t += kWarps) {
+        const int half = t / n_btiles, bin0 = (t - half * n_btiles) << 3;
+        smem_t gv[8];
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+          const smem_t* src = (pass == 0 ? hg : hh) + half * 32 + lane;
+#pragma unroll
+          for (int bb = 0; bb < 8; ++bb) {
+            const int bin = bin0 + bb;
+            stage[bb * 32 + ((lane + 4 * bb) & 31)] = bin < p.mb ? src[bin * kCols] : smem_t(0);
+          }
+          __syncwarp();
+          if (pass == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) gv[i] = stage[b * 32 + ((4 * i + a + 4 * b) & 31)];
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const smem_t hv = stage[b * 32 + ((4 * i + a + 4 * b) & 31)];
+              const int f     = feature_of_word(half * 32 + 4 * i + a);
+              const int fbeg  = s_rp[f];
+              const int bin   = bin0 + b;
+              if (bin < s_rp[f + 1] - fbeg && A::nonzero(gv[i], hv)) {
+                if (atomics) A::add_global(onode + fbeg + bin, gv[i], hv);
+                else A::store_global(onode + fbeg + bin, gv[i], hv);
+              }
+            }
+          }
+          __syncwarp();
+        }
+      }
+    };
+
+    bool use_atomics   = pc.pieces > 1 && !tree;
     const int seg_rows = rows_safe >= (1 << 30) ? (1 << 30) : (rows_safe & ~31);
-    for (int sb = ch.rb; sb < ch.re; sb += seg_rows) {
-      const int se = min(ch.re, sb + seg_rows);
-      if (sb > ch.rb) {
+    for (int sb = pc.rb; sb < pc.re; sb += seg_rows) {
+      const int se = min(pc.re, sb + seg_rows);
+      if (sb > pc.rb) {
         __syncthreads();
         flush(true);
         use_atomics = true;
@@ -508,165 +682,113 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
         zero();
         __syncthreads();
       }
-      const int nb = (se - sb + kRowsPerBatch - 1) / kRowsPerBatch;
-      auto load_rid = [&](int batch) -> int {
-        const int r = sb + batch * kRowsPerBatch + static_cast<int>(rslot);
-        return (batch < nb && r < se && lane_on) ? __ldcg(p.row_index + r) : -1;
-      };
-      // rows beyond the end carry zero pairs and bin 0: they add nothing
-      auto load_row = [&](int rid, int4& w, int2& v) {
-        if (rid >= 0) {
-          // through the texture pipe where the buffers have texture objects: the load/store pipe,
-          // which the reductions saturate, is spared the gathers
-          if (p.tex_bins != 0) {
-            w = tex1Dfetch<int4>(p.tex_bins, static_cast<int>((static_cast<int64_t>(rid) * pitch + g0 * kGroup + q * 16) >> 4));
-          } else {
-            w = __ldcs(reinterpret_cast<const int4*>(gb + static_cast<int64_t>(rid) * pitch));
-          }
-          if (p.tex_pairs != 0) {
-            v = tex1Dfetch<int2>(p.tex_pairs, static_cast<int>(static_cast<int64_t>(rid) * p.K + k));
-          } else {
-            v = __ldcg(reinterpret_cast<const int2*>(gpair + static_cast<int64_t>(rid) * p.K + k));
-          }
-        } else {
-          w = make_int4(0, 0, 0, 0);
-          v = make_int2(0, 0);
-        }
-      };
-      auto consume = [&](const int4& w, const int2& v) {
-        unsigned x[4];
-        x[0] = (wsel & 1) ? w.y : w.x;
-        x[1] = (wsel & 1) ? w.x : w.y;
-        x[2] = (wsel & 1) ? w.w : w.z;
-        x[3] = (wsel & 1) ? w.z : w.w;
-        if (W == 1 && (wsel & 2)) {
-          unsigned t2 = x[0]; x[0] = x[2]; x[2] = t2;
-          t2 = x[1]; x[1] = x[3]; x[3] = t2;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) x[i] = __byte_perm(x[i], 0u, perm);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const unsigned bin  = __byte_perm(x[j >> 2], 0u, 0x4440u | (j & 3));
-          const unsigned cj   = W == 1 ? 4u * j : (((j & 7u) << 2) | ((j >> 3) << 7));
-          const unsigned addr = (bin * (kCols * 4) + lanebase) ^ cj;
-          if (kFloat) {
-            RedShared(addr, __int_as_float(v.x));
-            RedShared(addr + hh_off, __int_as_float(v.y));
-          } else {
-            RedShared(addr, v.x);
-            RedShared(addr + hh_off, v.y);
-          }
-        }
-      };
-      // in flight per warp: the rows of the next two batches and the row ids of the two after
-      int4 w0, w1, w2;
-      int2 v0, v1, v2;
-      load_row(load_rid(warp), w0, v0);
-      load_row(load_rid(warp + kWarps), w1, v1);
-      int rid_a = load_rid(warp + 2 * kWarps);
-      int rid_b = load_rid(warp + 3 * kWarps);
-      for (int b = warp; b < nb; b += kWarps) {
-        load_row(rid_a, w2, v2);  // batch b + 2 * kWarps
-        rid_a = rid_b;
-        rid_b = load_rid(b + 4 * kWarps);
-        consume(w0, v0);
-        w0 = w1; v0 = v1;
-        w1 = w2; v1 = v2;
-      }
+      if (p.pairs_by_position != 0) HistRows<A, W, true>(p, sb, se, g0, groups, k, warp, lane, lane_word);
+      else HistRows<A, W, false>(p, sb, se, g0, groups, k, warp, lane, lane_word);
     }
     __syncthreads();
-    if (!slots) {
+    if (!tree) {
       flush(use_atomics);
-      continue;
+      return;
     }
-    // Several chunks of this node: every chunk leaves its sums in a slot; k_hist_sum adds the slots
-    // up afterwards and stores the total (no atomics on the histogram itself).
-    smem_t* part        = static_cast<smem_t*>(p.partial);
-    const size_t stride = static_cast<size_t>(hist_words) * 2;
-    const size_t first  = ((static_cast<size_t>(p.part_off[ch.j]) * p.K + k) * GP + gp);  // slot of chunk 0
-    const size_t step   = static_cast<size_t>(p.K) * GP;                                  // slot distance between chunks
-    smem_t* mine        = part + (first + ch.ci * step) * stride;
-    const int n4        = hist_words >> 2;  // 16-byte pieces: four neighbouring features of one bin
-    for (int e4 = tid; e4 < n4; e4 += kThreads) {
-      __stcg(reinterpret_cast<int4*>(mine) + e4, reinterpret_cast<const int4*>(hg)[e4]);
-      __stcg(reinterpret_cast<int4*>(mine + hist_words) + e4, reinterpret_cast<const int4*>(hh)[e4]);
-    }
-  }
-}
-
-// Adds up the partial-sum slots of every node that was cut into several chunks and adds the
-// totals to the (zeroed) histogram.  A work item is one (node of the `multi` list, group set,
-// output), 1/kSumSplits of its histogram words and 1/kSumParts of its slots; the blocks of a
-// fixed-size grid take items in turn (no items, no work).  A thread reads 16 bytes of every slot of
-// the item's part (four neighbouring features of one bin), four slots in flight, and finishes with
-// one pair of 64-bit atomics per feature (kSumParts items meet in every word).
-constexpr int kSumSplits  = 16;
-constexpr int kSumParts   = 8;
-constexpr int kSumThreads = 256;
-
-template <bool kFloat, int W>
-__global__ void __launch_bounds__(kSumThreads)
-  k_hist_sum(const HistParams p)
-{
-  using A      = Acc<kFloat>;
-  using smem_t = typename A::smem_t;
-  using out_t  = typename A::out_t;
-  constexpr int kCols = kGroup * W;
-  if (p.plan[6] == 0) return;
-  const int GP         = (p.G + W - 1) / W;
-  const long long items = static_cast<long long>(p.plan[5]) * GP * p.K * kSumSplits * kSumParts;
-  const int hist_words = p.mb * kCols;
-  const int n4         = hist_words >> 2;
-  const smem_t* part   = static_cast<const smem_t*>(p.partial);
-  const size_t stride  = static_cast<size_t>(hist_words) * 2;
-  const size_t step    = static_cast<size_t>(p.K) * GP;
-  for (long long item = blockIdx.x; item < items; item += gridDim.x) {
-    const int zpart = static_cast<int>(item % kSumParts);
-    const int split = static_cast<int>((item / kSumParts) % kSumSplits);
-    const long long t = item / (kSumParts * kSumSplits);
-    const int k  = static_cast<int>(t % p.K);
-    const int gp = static_cast<int>((t / p.K) % GP);
-    const int j  = p.multi[t / (static_cast<long long>(p.K) * GP)];
-    const int nchunks = p.chunk_off[j + 1] - p.chunk_off[j];
-    const int per = (nchunks + kSumParts - 1) / kSumParts;
-    const int qb  = zpart * per, qe = min(nchunks, qb + per);
-    if (qb >= qe) continue;
-    const int slot     = p.slot_of_node ? p.slot_of_node[j] : j;
-    const size_t first = (static_cast<size_t>(p.part_off[j]) * p.K + k) * GP + gp;
-    out_t* onode       = static_cast<out_t*>(p.out) + (static_cast<int64_t>(slot) * p.K + k) * p.B;
-    for (int e4 = split * kSumThreads + threadIdx.x; e4 < n4; e4 += kSumSplits * kSumThreads) {
-      typename A::wide_t sg[4], sh[4];
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) sg[c4] = sh[c4] = 0;
-      for (int q0 = qb; q0 < qe; q0 += 4) {
-        int4 vg[4], vh[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (q0 + u < qe) {
-            const smem_t* src = part + (first + (q0 + u) * step) * stride;
-            vg[u] = __ldcg(reinterpret_cast<const int4*>(src) + e4);
-            vh[u] = __ldcg(reinterpret_cast<const int4*>(src + hist_words) + e4);
-          } else {
-            vg[u] = vh[u] = make_int4(0, 0, 0, 0);
+    // merge tree
+    const int GK          = GP * p.K;
+    const int gk          = gp * p.K + k;
+    const size_t stride   = static_cast<size_t>(hist_words) * 2;  // words per slot
+    smem_t* slots         = static_cast<smem_t*>(p.partial);
+    const int n4          = hist_words >> 2;
+    int idx = pc.index, members = pc.pieces, soff = 0, coff = 0;
+    while (true) {
+      const int n_groups = (members + kTreeFanIn - 1) / kTreeFanIn;
+      const int grp      = idx / kTreeFanIn;
+      const int gsize    = min(kTreeFanIn, members - grp * kTreeFanIn);
+      if (gsize > 1) {
+        // leave my sums where the last one of the group finds them, then count myself in
+        smem_t* mine = slots + (static_cast<size_t>(pc.tree_base + soff + idx) * GK + gk) * stride;
+        for (int e4 = tid; e4 < n4; e4 += kThreads) {
+          __stcg(reinterpret_cast<int4*>(mine) + e4, reinterpret_cast<const int4*>(hg)[e4]);
+          __stcg(reinterpret_cast<int4*>(mine + hist_words) + e4, reinterpret_cast<const int4*>(hh)[e4]);
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_ticket = atomicAdd(p.arrive + static_cast<size_t>(pc.tree_base + coff + grp) * GK + gk, 1u);
+        __syncthreads();
+        const int arrived = static_cast<int>(s_ticket);
+        if (arrived != gsize - 1) return;  // somebody else carries the group on
+        __threadfence();
+        for (int m = grp * kTreeFanIn; m < grp * kTreeFanIn + gsize; ++m) {
+          if (m == idx) continue;
+          const smem_t* other = slots + (static_cast<size_t>(pc.tree_base + soff + m) * GK + gk) * stride;
+          for (int e4 = tid; e4 < n4; e4 += kThreads) {
+            int4* mg = reinterpret_cast<int4*>(hg) + e4;
+            int4* mh = reinterpret_cast<int4*>(hh) + e4;
+            *mg = A::add4(*mg, __ldcg(reinterpret_cast<const int4*>(other) + e4));
+            *mh = A::add4(*mh, __ldcg(reinterpret_cast<const int4*>(other + hist_words) + e4));
           }
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          sg[0] += A::widen(vg[u].x); sg[1] += A::widen(vg[u].y); sg[2] += A::widen(vg[u].z); sg[3] += A::widen(vg[u].w);
-          sh[0] += A::widen(vh[u].x); sh[1] += A::widen(vh[u].y); sh[2] += A::widen(vh[u].z); sh[3] += A::widen(vh[u].w);
-        }
+        __syncthreads();
       }
-      const int bin = (e4 * 4) / kCols, w0 = (e4 * 4) % kCols;
-      const int f0  = (gp * W) * kGroup + (W == 1 ? w0 : 16 * ((w0 >> 3) & 3) + 8 * (w0 >> 5) + (w0 & 7));
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        const int f = f0 + c4;
-        if (f >= p.F) continue;
-        const int fbeg = p.row_ptr[f];
-        if (bin < p.row_ptr[f + 1] - fbeg && (sg[c4] != 0 || sh[c4] != 0)) A::add_wide(onode + fbeg + bin, sg[c4], sh[c4]);
-      }
+      if (n_groups == 1) break;  // this block holds the node's total
+      soff += members;
+      coff += n_groups;
+      idx     = grp;
+      members = n_groups;
     }
+    flush(false);
+  };
+
+  // The pieces of this block: the nodes its static range touches, or the chunks it draws as
+  // tickets; one loop so that the piece code exists once.
+  const int GK = GP * p.K;
+  int gp = 0, k = 0, bj = 0;
+  long long lo = 0, hi = 0;
+  if (range_rows > 0) {
+    // static ranges: block b = (range, group set, output)
+    const int c = static_cast<int>(blockIdx.x) / GK;
+    if (c >= p.plan[7]) return;
+    const int gk = static_cast<int>(blockIdx.x) - c * GK;
+    gp = gk / p.K;
+    k  = gk - gp * p.K;
+    const long long all = p.wpre[p.n_nodes];
+    lo = static_cast<long long>(c) * range_rows;
+    hi = lo + range_rows < all ? lo + range_rows : all;
+    int a = 0, b = p.n_nodes;  // last node whose rows begin at or before lo
+    while (b - a > 1) {
+      const int m = (a + b) >> 1;
+      if (p.wpre[m] <= lo) a = m; else b = m;
+    }
+    bj = a;
+  }
+  const long long total = static_cast<long long>(p.plan[1]) * GK;
+  while (true) {
+    Piece pc;
+    if (range_rows > 0) {
+      if (lo >= hi) break;
+      const int c = static_cast<int>(blockIdx.x) / GK;
+      while (p.wpre[bj + 1] <= lo) ++bj;  // nodes without built rows
+      const long long ws = p.wpre[bj], we = p.wpre[bj + 1];
+      const long long pe = we < hi ? we : hi;
+      const int first_c  = static_cast<int>(ws / range_rows);        // range that holds the node's first row
+      const int last_c   = static_cast<int>((we - 1) / range_rows);  // ... and its last one
+      pc.j         = bj;
+      pc.slot      = p.slot_of_node ? p.slot_of_node[bj] : bj;
+      pc.pieces    = last_c - first_c + 1;
+      pc.index     = c - first_c;
+      pc.tree_base = kTreeFanIn * first_c;  // the node owns the boundaries first_c+1 .. last_c
+      pc.node_rows = static_cast<int>(we - ws);
+      pc.rb        = p.seg[bj] + static_cast<int>(lo - ws);
+      pc.re        = p.seg[bj] + static_cast<int>(pe - ws);
+      lo           = pe;
+    } else {
+      __syncthreads();
+      if (tid == 0) s_ticket = atomicAdd(p.ticket, 1u);
+      __syncthreads();
+      const long long t = s_ticket;
+      if (t >= total) break;
+      k  = static_cast<int>(t % p.K);
+      gp = static_cast<int>((t / p.K) % GP);
+      pc = DecodeChunk(p, static_cast<int>(t / GK));
+    }
+    process(pc, gp, k);
   }
 }
 
@@ -677,11 +799,10 @@ constexpr int kGroupTile = 4096;
 // occupancy calculator) for one combination of bin width, pair type and path.
 struct HistLaunch {
   void (*fn)(HistParams);
-  void (*sum)(HistParams);  // adds up partial-sum slots; null for the kernels that have none
   size_t smem;
   int threads;
   int grid;
-  int width;  // feature groups per ticket
+  int width;  // feature groups per unit of work
 };
 
 HistLaunch PickHistKernel(bool smem_path, int bin_bytes, bool float_mode, int n_groups, int sm_count)
@@ -689,15 +810,10 @@ HistLaunch PickHistKernel(bool smem_path, int bin_bytes, bool float_mode, int n_
   HistLaunch h;
   h.width   = smem_path && n_groups >= 2 ? 2 : 1;
   h.threads = kHistThreads * h.width;
-  h.smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * h.width * 8 + 256 : 0;
-  h.sum = nullptr;
-  if (smem_path && h.width == 2) {
-    h.fn  = float_mode ? k_hist_smem<true, 2> : k_hist_smem<false, 2>;
-    h.sum = float_mode ? k_hist_sum<true, 2> : k_hist_sum<false, 2>;
-  } else if (smem_path) {
-    h.fn  = float_mode ? k_hist_smem<true, 1> : k_hist_smem<false, 1>;
-    h.sum = float_mode ? k_hist_sum<true, 1> : k_hist_sum<false, 1>;
-  }
+  // staging below H, the two histograms at H and 2 H (H = 256 bins x 32 W words x 4 bytes)
+  h.smem    = smem_path ? static_cast<size_t>(kSmemBins) * kGroup * h.width * 4 * 3 : 0;
+  if (smem_path && h.width == 2) h.fn = float_mode ? k_hist_smem<true, 2> : k_hist_smem<false, 2>;
+  else if (smem_path) h.fn = float_mode ? k_hist_smem<true, 1> : k_hist_smem<false, 1>;
   else if (bin_bytes == 1) h.fn = float_mode ? k_hist_direct<uint8_t, true> : k_hist_direct<uint8_t, false>;
   else h.fn = float_mode ? k_hist_direct<uint16_t, true> : k_hist_direct<uint16_t, false>;
   if (h.smem > 48 * 1024)
@@ -811,17 +927,12 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   p.chunk_off        = chunk_off;
   p.plan             = plan;
   p.ticket           = reinterpret_cast<unsigned int*>(plan + 2);
+  p.status           = ctx->d_status;
+  p.pairs_by_position = lv.pairs_by_position ? 1 : 0;
   p.out              = lv.out;
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
-  p.tex_bins           = 0;
-  p.tex_pairs          = 0;
-  // (measured: the float path, bound by its float reductions, is slower with the texture fetches)
-  if (smem_path && lv.n_rows > 0 && !lv.float_mode) {
-    p.tex_bins  = LinearTexture(ctx, lv.bins, static_cast<size_t>(lv.n_rows) * p.G * kGroup, 16);
-    p.tex_pairs = LinearTexture(ctx, p.gpair, static_cast<size_t>(lv.n_rows) * lv.K * 8, 8);
-  }
   const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, p.G, ctx->sm_count - (lv.reserve_sms < ctx->sm_count ? lv.reserve_sms : 0));
 
   const int* max_abs = lv.max_abs;
@@ -836,36 +947,31 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
     }
     max_abs = m;
   }
-  const int tickets_per_chunk = (p.G + hl.width - 1) / hl.width * p.K;
-  // partial-sum slots for nodes that are cut into several chunks: ten per resident block
+  const int units_per_row = (p.G + hl.width - 1) / hl.width * p.K;
+  // static ranges need the rows before each node, and slots and counters for the merge trees of
+  // the nodes that reach over a range boundary: kTreeFanIn per resident block covers every cut
   long long slot_capacity = 0;
-  p.part_off = nullptr;
-  p.multi    = nullptr;
-  p.partial  = nullptr;
+  int n_arrive            = 0;
+  p.wpre    = nullptr;
+  p.arrive  = nullptr;
+  p.partial = nullptr;
+  int32_t* wpre = nullptr;
   if (smem_path) {
-    slot_capacity           = 10ll * hl.grid;
+    slot_capacity           = static_cast<long long>(kTreeFanIn) * hl.grid;
+    n_arrive                = kTreeFanIn * hl.grid;
     const size_t slot_bytes = static_cast<size_t>(p.mb) * kGroup * hl.width * 8;
-    int32_t* part_off       = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes) + 1);
-    int32_t* multi          = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes));
-    p.part_off              = part_off;
-    p.multi                 = multi;
+    wpre                    = s.alloc<int32_t>(static_cast<size_t>(lv.n_nodes) + 1);
+    p.wpre                  = wpre;
+    p.arrive                = s.alloc<unsigned int>(static_cast<size_t>(n_arrive));
     p.partial               = s.alloc<unsigned char>(slot_bytes * slot_capacity);
-    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, tickets_per_chunk, hl.grid,
-                                        lv.float_mode ? nullptr : max_abs, slot_capacity, chunk_off, part_off,
-                                        multi, plan, p.ticket);
-  } else {
-    k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, tickets_per_chunk, hl.grid,
-                                        lv.float_mode ? nullptr : max_abs, 0, chunk_off, nullptr, nullptr, plan,
-                                        p.ticket);
   }
+  k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, p.slot_of_node, p.n_nodes, units_per_row, hl.grid,
+                                      lv.float_mode ? nullptr : max_abs, slot_capacity, chunk_off, wpre, p.arrive,
+                                      n_arrive, plan, p.ticket);
   LBK_LAUNCH_CHECK();
   if (ctx->profile) LBK_CUDA(cudaEventRecord(ctx->ev_start, stream));
   hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
   LBK_LAUNCH_CHECK();
-  if (p.partial) {
-    hl.sum<<<ctx->sm_count * 8, kSumThreads, 0, stream>>>(p);
-    LBK_LAUNCH_CHECK();
-  }
   if (ctx->profile) {
     LBK_CUDA(cudaEventRecord(ctx->ev_stop, stream));
     ctx->profile_recorded = true;
@@ -969,23 +1075,26 @@ void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t
 // ---------------------------------------------------------------------------------------------
 // lbk_histogram_noalloc: the histogram build for callers that must not allocate device memory.
 //
-// Who needs it: code that runs where cudaMalloc / cudaFree are off limits - inside a stream
-// callback or another thread's critical section where the allocator's implicit device
-// synchronisation would deadlock or stall every stream, under a memory budget that a runtime
-// has already handed out completely (a task variant registered without the right to allocate),
-// or in a process that wants its device footprint fixed after start-up.  lbk_histogram takes its
+// Who needs it: code that runs under a memory budget that a runtime has already handed out
+// completely (a task variant registered without the right to allocate: any cudaMalloc there fails or
+// takes memory the runtime believes it owns), or a process that wants its device footprint fixed
+// after start-up so that no later call can fail for lack of memory.  lbk_histogram takes its
 // per-call scratch (chunk offsets, the level plan, the largest magnitudes) from the context's
 // pool; this entry point keeps that scratch in a fixed array inside the library image instead
 // and needs no context at all.
 //
 // Limits and rules
 //   * at most LBK_NOALLOC_MAX_NODES nodes and LBK_NOALLOC_MAX_FEATURES features per call,
-//     device pointers only (host_buffers must be 0); larger calls are rejected with
-//     LBK_ERR_ARGUMENT before anything is launched;
+//     device pointers only (host_buffers must be 0), one rank (all_reduce must be 0: there is no
+//     context and so no communicator); larger or other calls are rejected with LBK_ERR_ARGUMENT
+//     before anything is launched;
 //   * the array (about 16 KB) exists once per GPU that loads the library, until the process ends;
 //   * the first call on a device looks the array's device address up (the array's name is only a
 //     host-side handle; kernels get the address found here).  Make that first call before any
-//     stream capture;
+//     stream capture begins;
+//   * the call blocks: it reads row_ptr back and synchronises `stream` before it returns (so it is
+//     not something to issue from a host callback of a stream); it makes `device` current for the
+//     duration of the call and restores the caller's device before it returns;
 //   * all calls on a device share the array: what has to start at zero is cleared by each call, and
 //     two calls whose kernels overlap on the GPU (different streams, different threads) race -
 //     serialise them on one stream.
@@ -1025,6 +1134,9 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     LBK_EXPECT(a != nullptr, "null argument");
     LBK_EXPECT(device >= 0 && device < kMaxDevices, "device index out of range");
     LBK_EXPECT(a->host_buffers == 0, "lbk_histogram_noalloc takes device pointers only");
+    LBK_EXPECT(a->all_reduce == 0, "lbk_histogram_noalloc has no communicator: all_reduce must be 0");
+    LBK_EXPECT(!a->pairs_by_position || a->mode == 1 || a->max_abs != nullptr,
+               "pairs stored by position need max_abs (the library cannot know how many entries the array has)");
     LBK_EXPECT(a->bins && a->row_ptr && a->row_index && a->seg && a->hist, "null argument");
     LBK_EXPECT(a->mode == 0 || a->mode == 1, "mode must be 0 or 1");
     LBK_EXPECT(a->mode == 0 ? a->gpair != nullptr : a->gpair_f32 != nullptr, "missing gradient pairs");
@@ -1034,6 +1146,12 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
                "lbk_histogram_noalloc handles at most " + std::to_string(kNoAllocMaxNodes) + " nodes per call");
     LBK_EXPECT(a->n_features <= kNoAllocMaxFeatures,
                "lbk_histogram_noalloc handles at most " + std::to_string(kNoAllocMaxFeatures) + " features per call");
+    int caller_device = -1;
+    LBK_CUDA(cudaGetDevice(&caller_device));
+    struct RestoreDevice {
+      int d;
+      ~RestoreDevice() { cudaSetDevice(d); }
+    } restore{caller_device};
     LBK_CUDA(cudaSetDevice(device));
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     int32_t* scratch    = HistScratchAddress(device);
@@ -1046,7 +1164,7 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     LBK_CUDA(cudaMemcpyAsync(rp, a->row_ptr, sizeof(int32_t) * (F + 1), cudaMemcpyDeviceToHost, stream));
     LBK_CUDA(cudaStreamSynchronize(stream));
     LBK_EXPECT(rp[F] == B, "total_bins does not match row_ptr");
-    int mb = 1;
+    int mb = 1;  // (max_bins is not needed here: row_ptr has been read back anyway)
     for (int f = 0; f < F; ++f) mb = rp[f + 1] - rp[f] > mb ? rp[f + 1] - rp[f] : mb;
     LBK_EXPECT(a->bin_bytes == 2 || mb <= 256, "one-byte bins need <= 256 proposals per feature");
 
@@ -1087,14 +1205,15 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
         LBK_LAUNCH_CHECK();
       }
     }
-    // no partial-sum slots here (they would have to be allocated): nodes cut into chunks flush with atomics
-    p.part_off  = nullptr;
-    p.multi     = nullptr;
+    // no merge-tree slots here (they would have to be allocated): nodes cut into chunks flush with atomics
+    p.wpre      = nullptr;
+    p.arrive    = nullptr;
     p.partial   = nullptr;
-    p.tex_bins  = 0;  // texture objects belong to a context; this entry point has none
-    p.tex_pairs = 0;
+    p.status    = nullptr;
+    p.pairs_by_position = a->pairs_by_position != 0 ? 1 : 0;
     k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, (p.G + hl.width - 1) / hl.width * p.K, hl.grid,
-                                        float_mode ? nullptr : max_abs, 0, chunk_off, nullptr, nullptr, plan, p.ticket);
+                                        float_mode ? nullptr : max_abs, 0, chunk_off, nullptr, nullptr, 0, plan,
+                                        p.ticket);
     LBK_LAUNCH_CHECK();
     hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
     LBK_LAUNCH_CHECK();

@@ -76,17 +76,6 @@ struct lbk_context {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ev_part[4]   = {nullptr, nullptr, nullptr, nullptr};
   cudaEvent_t ev_comm_done = nullptr;
-  // linear textures over buffers the histogram kernel gathers from (see LinearTexture)
-  struct TexEntry {
-    const void* ptr;
-    size_t bytes;
-    int texel_bytes;
-    cudaTextureObject_t obj;
-    unsigned long long last_use;
-  };
-  std::vector<TexEntry> tex_cache;
-  unsigned long long tex_clock = 0;
-  int tex_alignment = 0, tex_max_texels = 0;
   // optional timing of the histogram kernel alone (events on the caller's stream)
   bool profile            = false;
   cudaEvent_t ev_start    = nullptr, ev_stop = nullptr;
@@ -121,11 +110,6 @@ class Scratch {
 // is limited to a few CTAs, if there is one.
 void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream,
                bool beside_kernel = false);
-// A texture object that presents `bytes` of device memory at `ptr` as a 1-D array of 8- or 16-byte
-// texels, or 0 when the buffer cannot be one (alignment, more texels than a linear texture holds).
-// Objects are kept in a small per-context cache keyed by (pointer, size, texel); the least recently
-// used one is destroyed, after a device synchronisation, when the cache is full.
-cudaTextureObject_t LinearTexture(lbk_context* ctx, const void* ptr, size_t bytes, int texel_bytes);
 // Reads the device status word (synchronises the stream) and throws LBK_ERR_DEVICE if set.
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream);
 
@@ -161,6 +145,7 @@ struct HistLevel {
   const int32_t* row_ptr;
   const int2* gpair;       // int path
   const float2* gpair_f;   // float path
+  bool pairs_by_position = false;  // gpair / gpair_f are stored in row_index order: entry i belongs to row_index[i]
   const int* max_abs;      // device [2]: largest |grad|, |hess| of gpair (null: computed by the call)
   const int32_t* row_index;
   const int32_t* seg;      // [n_level_nodes+1] offsets for nodes node_begin.. of the level range
@@ -223,6 +208,10 @@ struct PartitionLevel {
   int node_begin, n_nodes;
   const int32_t* feature;
   const int32_t* split_bin;
+  // optional: the quantised pairs in row_index order, moved together with the row ids
+  const int2* pairs_in = nullptr;  // [rows of the level][K]
+  int2* pairs_out      = nullptr;
+  int K                = 0;
 };
 void PartitionRows(lbk_context* ctx, Scratch& s, const PartitionLevel& pl, cudaStream_t stream);
 void InitRows(int32_t* row_index, int32_t* seg, int64_t n_rows, cudaStream_t stream);

@@ -171,7 +171,8 @@ __global__ void __launch_bounds__(kPartThreads)
   k_part_scatter(const int32_t* __restrict__ row_index, const int32_t* __restrict__ seg,
                  const int32_t* __restrict__ chunk_off, int n_nodes, const uint8_t* __restrict__ masks,
                  const int32_t* __restrict__ left_prefix, const int32_t* __restrict__ seg_out,
-                 int32_t* __restrict__ row_index_out)
+                 int32_t* __restrict__ row_index_out, const int2* __restrict__ pairs_in, int2* __restrict__ pairs_out,
+                 int K)
 {
   const int c = blockIdx.x;
   if (c >= chunk_off[n_nodes]) return;
@@ -204,7 +205,12 @@ __global__ void __launch_bounds__(kPartThreads)
   for (int i = 0; i < kPartItems; ++i) {
     if (i < nvalid) {
       const int ridx = row_index[r0 + i];
-      if (mask & (1u << i)) row_index_out[lpos++] = ridx; else row_index_out[rpos++] = ridx;
+      const int dst  = (mask & (1u << i)) ? lpos++ : rpos++;
+      row_index_out[dst] = ridx;
+      // the gradient pairs travel with the row ids, so that the histogram kernel reads them as a stream
+      if (pairs_in != nullptr)
+        for (int k = 0; k < K; ++k)
+          pairs_out[static_cast<int64_t>(dst) * K + k] = pairs_in[static_cast<int64_t>(r0 + i) * K + k];
     }
   }
 }
@@ -248,7 +254,7 @@ void PartitionRows(lbk_context* ctx, Scratch& s, const PartitionLevel& pl, cudaS
                                             pl.seg_out);
   LBK_LAUNCH_CHECK();
   k_part_scatter<<<grid, kPartThreads, 0, stream>>>(pl.row_index_in, pl.seg_in, chunk_off, n, masks, left_prefix,
-                                                    pl.seg_out, pl.row_index_out);
+                                                    pl.seg_out, pl.row_index_out, pl.pairs_in, pl.pairs_out, pl.K);
   LBK_LAUNCH_CHECK();
 }
 

@@ -82,6 +82,7 @@ class HistogramArgs(C.Structure):
         ("row_index", C.c_void_p), ("seg", C.c_void_p), ("n_nodes", C.c_int32),
         ("mode", C.c_int32), ("hist", C.c_void_p), ("stream", C.c_void_p),
         ("host_buffers", C.c_int32), ("max_abs", C.c_void_p), ("max_bins", C.c_int32), ("all_reduce", C.c_int32),
+        ("pairs_by_position", C.c_int32),
     ]
 
 

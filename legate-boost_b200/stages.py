@@ -82,10 +82,11 @@ def group_rows(node_of_row, node_begin, n_nodes, ctx=None):
 
 
 def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=None, ctx=None, host=False,
-              max_abs=None, all_reduce=False, max_bins=0, total_bins=None):
+              max_abs=None, all_reduce=False, max_bins=0, total_bins=None, pairs_by_position=False):
     """Histogram [n_nodes, K, B, 2] (int64 for mode 0, float64 for mode 1) of node-grouped rows.
 
-    ``host=True`` takes CPU tensors and lets the library do the copies (the end-to-end path)."""
+    ``host=True`` takes CPU tensors and lets the library do the copies (the end-to-end path).
+    ``pairs_by_position``: gpair[i] belongs to row_index[i] (the pairs were moved with the row ids)."""
     dev = bins.device
     ctx = ctx or L.context(None if host else dev.index)
     N = bins.shape[0]
@@ -110,5 +111,6 @@ def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=Non
     a.max_abs = max_abs.data_ptr() if max_abs is not None else None
     a.all_reduce = 1 if all_reduce else 0
     a.max_bins = int(max_bins)
+    a.pairs_by_position = 1 if pairs_by_position else 0
     ctx.check(ctx.lib.lbk_histogram(ctx.handle, C.byref(a)))
     return hist

@@ -9,10 +9,12 @@ unmodified build_tree.cu / predict.cu compiled with nvcc against a stand-in of t
 tree is present; the built object is all this script needs).  Needs one CUDA device.  Inputs are
 small and valid (hundreds to thousands of rows).  Run from the repository root:
 
-    python tests/golden/make_golden_q.py [--out DIR] [--compare]
+    python tests/golden/make_golden_q.py [--out DIR] [--compare] [--lib FILE]
 
 ``--compare`` also runs the CPU oracle's quantised mode on every case and prints which arrays are
-bit-for-bit equal (the record the parity statement rests on).
+bit-for-bit equal (the record the parity statement rests on).  ``--lib`` names another build of the
+same driver (oracle/_ref/libref_gpu_nofma.so, built without multiply-add contraction): its vectors,
+written to another folder, tell the effect of contraction apart from everything else.
 """
 import argparse
 import ctypes as C
@@ -24,7 +26,9 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 
-MAX_STORED_TRACE = 400_000  # int64 pairs kept in full per case; beyond that only the digests
+MAX_STORED_TRACE = 100_000  # int64 pairs of traced histograms kept in full per case; every traced node has a digest
+MAX_STORED_INPUT = 25_000   # elements of X up to which the inputs themselves are stored; larger cases are
+                            # regenerated from their seeds by cases() and checked against the stored hashes
 
 
 def cases():
@@ -112,6 +116,33 @@ def _ptr(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
 
+def input_hash(c):
+    """sha256 over the bytes of X, g and h (as the reference receives them)."""
+    import hashlib
+
+    m = hashlib.sha256()
+    m.update(np.ascontiguousarray(c["X"]).tobytes())
+    m.update(np.ascontiguousarray(c["g"], dtype=np.float64).tobytes())
+    m.update(np.ascontiguousarray(c["h"], dtype=np.float64).tobytes())
+    return m.hexdigest()
+
+
+def load_case(path):
+    """A stored case with its inputs: taken from the file, or regenerated from the seeds and
+    checked against the stored hash.  Returns (npz, dict as cases() makes it)."""
+    z = np.load(path)
+    name = os.path.basename(path)[len("treeq_"):-len(".npz")]
+    if "X" in z.files:
+        fs = z["feature_set"] if z["feature_set"].size else None
+        c = dict(X=z["X"], g=z["g"], h=z["h"], max_depth=int(z["max_depth"]), split_samples=int(z["split_samples"]),
+                 seed=int(z["seed"]), l1=float(z["l1"]), l2=float(z["l2"]), min_split_gain=float(z["min_split_gain"]),
+                 feature_set=fs, trace_nodes=int(z["trace_nodes"]))
+    else:
+        c = cases()[name]
+    assert input_hash(c) == str(z["input_sha256"]), "inputs of %s are not the ones the vectors were made from" % name
+    return z, c
+
+
 def digest(hist):
     """One 64-bit number per traced node: sum of value * (2 * index + 1) modulo 2**64."""
     flat = hist.reshape(hist.shape[0], -1).astype(np.uint64)
@@ -180,13 +211,14 @@ def main():
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
     ap.add_argument("--compare", action="store_true")
     ap.add_argument("--only", default=None)
+    ap.add_argument("--lib", default=os.path.join(ROOT, "oracle", "_ref", "libref_gpu.so"))
+    ap.add_argument("--nofma-dir", default=None,
+                    help="folder written by a run with --lib .../libref_gpu_nofma.so: its float arrays are stored "
+                         "beside the default build's as *_nofma")
     args = ap.parse_args()
     os.makedirs(args.out, exist_ok=True)
-    ref_dir = os.path.join(ROOT, "oracle", "_ref")
-    lib = C.CDLL(os.path.join(ref_dir, "libref_gpu.so"))
+    lib = C.CDLL(args.lib)
     assert lib.ref_gpu_device_count() > 0, "a CUDA device is needed"
-    nofma_path = os.path.join(ref_dir, "libref_gpu_nofma.so")
-    nofma = C.CDLL(nofma_path) if os.path.exists(nofma_path) else None
     for name, c in cases().items():
         if args.only and name != args.only:
             continue
@@ -197,29 +229,25 @@ def main():
         pred = run_predict(lib, c, r)
         tn = c["trace_nodes"]
         dig = digest(r["trace_hist"])
-        stored = tn
         per_node = r["trace_hist"][0].size // 2
-        if tn * per_node > MAX_STORED_TRACE:
-            stored = max(1, MAX_STORED_TRACE // per_node)
+        stored = min(tn, MAX_STORED_TRACE // per_node)
         fs = c["feature_set"]
-        np.savez_compressed(
-            os.path.join(args.out, "treeq_%s.npz" % name), X=c["X"], g=c["g"], h=c["h"], max_depth=c["max_depth"],
-            split_samples=c["split_samples"], seed=c["seed"], l1=c["l1"], l2=c["l2"], min_split_gain=c["min_split_gain"],
-            feature_set=np.zeros(0, dtype=np.uint8) if fs is None else fs,
-            leaf_value=r["leaf_value"], feature=r["feature"], split_value=r["split_value"], gain=r["gain"],
-            hessian=r["hessian"], node_sums=r["node_sums"], total_bins=r["total_bins"], trace_nodes=tn,
-            trace_hist=r["trace_hist"][:stored], trace_digest=dig, pred=pred)
+        keep = dict(max_depth=c["max_depth"], split_samples=c["split_samples"], seed=c["seed"], l1=c["l1"], l2=c["l2"],
+                    min_split_gain=c["min_split_gain"], feature_set=np.zeros(0, dtype=np.uint8) if fs is None else fs,
+                    input_sha256=input_hash(c), leaf_value=r["leaf_value"], feature=r["feature"],
+                    split_value=r["split_value"], gain=r["gain"], hessian=r["hessian"], node_sums=r["node_sums"],
+                    total_bins=r["total_bins"], trace_nodes=tn, trace_hist=r["trace_hist"][:stored], trace_digest=dig,
+                    pred=pred)
+        if c["X"].size <= MAX_STORED_INPUT:
+            keep.update(X=c["X"], g=c["g"], h=c["h"])
+        if args.nofma_dir:
+            z2 = np.load(os.path.join(args.nofma_dir, "treeq_%s.npz" % name))
+            for k in ("feature", "split_value", "node_sums", "trace_digest"):
+                assert same(keep[k], z2[k]), "the build without contraction differs in %s" % k
+            keep.update(leaf_value_nofma=z2["leaf_value"], gain_nofma=z2["gain"], hessian_nofma=z2["hessian"])
+        np.savez_compressed(os.path.join(args.out, "treeq_%s.npz" % name), **keep)
         line = "wrote %-10s split nodes %4d  B %6d  traced %4d (stored %d)" % (
             name, int((r["feature"] >= 0).sum()), r["total_bins"], tn, stored)
-        if nofma is not None:
-            r2 = run_reference(nofma, c, traced=True)
-            diffs = [k for k in ("leaf_value", "feature", "split_value", "gain", "hessian", "node_sums", "trace_hist")
-                     if not same(r[k], r2[k])]
-            line += "  | without contraction differs in: %s" % (",".join(diffs) or "nothing")
-            for k in diffs:
-                if r[k].dtype.kind == "f":
-                    d = np.abs(r[k] - r2[k])
-                    line += " [%s max abs %.3g, max rel %.3g]" % (k, d.max(), (d / np.maximum(np.abs(r[k]), 1e-300)).max())
         print(line, flush=True)
         if args.compare:
             from oracle import oracle as O

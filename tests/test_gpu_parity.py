@@ -120,6 +120,18 @@ def test_histogram_int_exact(lb, oracle, N, F, K, n_nodes, nb):
         assert np.all(node[r] == j + n_nodes - 1) and np.all(np.diff(r) > 0)
     got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
     assert np.array_equal(got.cpu().numpy(), want)
+    # the same pairs stored in row_index order (as the tree builder keeps them)
+    got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), _by_position(dev(q), row_index), row_index, seg,
+                           F, mode=0, pairs_by_position=True, max_abs=_max_abs(q))
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def _by_position(pairs, row_index):
+    return pairs[row_index.long()].contiguous()
+
+
+def _max_abs(q):
+    return dev(np.abs(q.astype(np.int64)).reshape(-1, 2).max(axis=0).astype(np.int32))
 
 
 @pytest.mark.parametrize("F,K", [(32, 2), (64, 1)])
@@ -365,6 +377,49 @@ def test_golden_trees_on_gpu(lb, oracle):
         assert np.array_equal(p.cpu().numpy(), z["pred"])
 
 
+GOLDEN_Q = sorted(glob.glob(os.path.join(HERE, "golden", "treeq_*.npz")))
+SAME_SCALE = {"batching", "deep", "mask", "reg", "rows20k", "softmax10"}
+
+
+@pytest.mark.parametrize("path", GOLDEN_Q, ids=[os.path.basename(p)[6:-4] for p in GOLDEN_Q])
+def test_reference_gpu_vectors_on_gpu(lb, path):
+    """liblbk.so against what the reference's own GPU code produced for the same inputs
+    (tests/golden/make_golden_q.py).  Bit for bit: bins, feature, split_value, quantised node sums,
+    traced histograms, predictions.  The float outputs that pass through the quantiser's scale
+    (a float sum whose order the reference leaves to thrust::reduce) or a contracted multiply-add:
+    bit for bit equal to the reference built without contraction where the scale is the same
+    float (SAME_SCALE), within 1e-12 relative everywhere."""
+    import sys
+
+    from legateboost_b200.tree import build_tree_arrays, predict_arrays
+
+    sys.path.insert(0, os.path.join(HERE, "golden"))
+    import make_golden_q as G
+
+    z, c = G.load_case(path)
+    name = os.path.basename(path)[6:-4]
+    tn = int(z["trace_nodes"])
+    fs = None if c["feature_set"] is None else torch.from_numpy(np.asarray(c["feature_set"]))
+    got = build_tree_arrays(dev(c["X"]), dev(np.asarray(c["g"], dtype=np.float64)), dev(np.asarray(c["h"], dtype=np.float64)),
+                            max_depth=c["max_depth"], split_samples=c["split_samples"], seed=c["seed"], l1=c["l1"],
+                            l2=c["l2"], min_split_gain=c["min_split_gain"], feature_set=fs, row_offset=0,
+                            dataset_rows=c["X"].shape[0], trace_nodes=tn)
+    assert got["B"] == int(z["total_bins"])
+    assert np.array_equal(got["feature"].cpu().numpy(), z["feature"])
+    assert np.array_equal(got["split_value"].cpu().numpy().view(np.int64), z["split_value"].view(np.int64))
+    assert np.array_equal(got["node_sums"].cpu().numpy(), z["node_sums"])
+    trace = got["trace_hist"].cpu().numpy()
+    assert np.array_equal(G.digest(trace), z["trace_digest"])
+    assert np.array_equal(trace[:z["trace_hist"].shape[0]], z["trace_hist"])
+    for k in ("hessian", "leaf_value", "gain"):
+        a = got[k].cpu().numpy()
+        assert np.all(np.abs(a - z[k]) <= 1e-12 * np.maximum(np.abs(a), np.abs(z[k]))), k
+        if name in SAME_SCALE:
+            assert np.array_equal(a.view(np.int64), z[k + "_nofma"].view(np.int64)), k
+    pred = predict_arrays(dev(c["X"]), [(dev(z["leaf_value"]), dev(z["feature"]), dev(z["split_value"]))])
+    assert np.array_equal(pred.cpu().numpy().view(np.int64), z["pred"].view(np.int64))
+
+
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("N,F,K,T,D", [(1000, 10, 1, 5, 4), (5000, 100, 1, 40, 8), (777, 33, 5, 7, 6), (129, 3, 2, 1, 0)])
@@ -516,10 +571,24 @@ def test_first_predict_on_the_training_matrix_uses_the_leaf_record(lb):
     assert torch.equal(stump.predict(X), lb.Tree.batch_predict([stump], X))
 
 
-def test_full_size_histogram_checksums(lb):
-    """Size-independent properties at the benchmark's own size (10 M x 128, 128 nodes): within
-    every node the bins of every feature add up to the node's total pair, and the grand total is the
-    total of all pairs (integer arithmetic: exact)."""
+def _torch_histogram(bins, gpair, node, node_begin, n_nodes, F, n_bins):
+    """An independent integer histogram on the device: index_add_ of the pairs at
+    node * B + feature * n_bins + bin, a few features at a time (int64, exact)."""
+    B = F * n_bins
+    out = torch.zeros((n_nodes * B, 2), dtype=torch.int64, device=bins.device)
+    base = (node.long() - node_begin) * B
+    vals = gpair[:, 0, :].long()
+    step = 8
+    for f0 in range(0, F, step):
+        f1 = min(F, f0 + step)
+        idx = base[:, None] + bins[:, f0:f1].long() + (torch.arange(f0, f1, device=bins.device) * n_bins)[None, :]
+        out.index_add_(0, idx.reshape(-1), vals[:, None, :].expand(-1, f1 - f0, -1).reshape(-1, 2))
+    return out.view(n_nodes, 1, B, 2)
+
+
+def test_full_size_histogram_exact(lb):
+    """The benchmark's own size (10 M x 128, 128 nodes of level 7): every bin of every node equals an
+    independent histogram of the same inputs (integer arithmetic: exact)."""
     import bench
     from legateboost_b200 import stages
 
@@ -527,13 +596,49 @@ def test_full_size_histogram_checksums(lb):
     bins, row_ptr, gpair, _, row_index, seg, node, max_abs = bench.hist_inputs(torch, n, 7, torch.device("cuda"))
     hist = stages.histogram(bins, row_ptr, gpair, row_index, seg, bench.HIST_FEATURES, mode=0, max_abs=max_abs)
     n_nodes = seg.shape[0] - 1
-    per_feature = hist.view(n_nodes, bench.HIST_FEATURES, bench.HIST_BINS, 2).sum(dim=2)      # [node, feature, 2]
-    want = torch.zeros((n_nodes, 2), dtype=torch.int64, device=hist.device)
-    want.index_add_(0, (node - (n_nodes - 1)).long(), gpair[:, 0, :].long())
-    assert torch.equal(per_feature, want[:, None, :].expand_as(per_feature))
-    assert torch.equal(per_feature[:, 0, :].sum(dim=0), gpair[:, 0, :].long().sum(dim=0))
+    want = _torch_histogram(bins, gpair, node, n_nodes - 1, n_nodes, bench.HIST_FEATURES, bench.HIST_BINS)
+    assert torch.equal(hist, want)
     # the same call without the magnitudes handed in (the library finds them) gives the same bits
     assert torch.equal(stages.histogram(bins, row_ptr, gpair, row_index, seg, bench.HIST_FEATURES, mode=0), hist)
+
+
+@pytest.mark.parametrize("N,F,K,weights,mode,qmax", [
+    (1_500_000, 64, 1, [0.80, 0.0, 0.15, 0.05], 0, 300),    # one node in about 120 pieces: a deep merge tree
+    (1_500_000, 64, 1, [0.80, 0.0, 0.15, 0.05], 0, 5000),   # ... too many rows for 32-bit sums: atomics instead
+    (1_500_000, 96, 3, [0.3, 0.3, 0.2, 0.1, 0.1], 0, 300),  # three groups: the second group set is half empty
+    (2_000_000, 32, 2, [1.0] * 37, 0, 300),                 # one group per unit (two blocks per SM)
+    (1_500_000, 128, 1, [0.55, 0.45], 1, 0),                # float pairs through the same ranges
+])
+def test_histogram_static_ranges(lb, oracle, N, F, K, weights, mode, qmax):
+    """Enough rows for the planner to hand out equal static ranges: nodes reach over range
+    boundaries and their pieces meet in the merge tree; sums stay exact (floats within 1e-5)."""
+    from legateboost_b200 import stages
+
+    rng = np.random.default_rng(N + F)
+    n_nodes = len(weights)
+    edges = np.cumsum(np.asarray(weights) / np.sum(weights))
+    node = np.minimum(np.searchsorted(edges, rng.random(N), side="right"), n_nodes - 1).astype(np.int32) + (n_nodes - 1)
+    bins = rng.integers(0, 256, size=(N, F), dtype=np.uint8)
+    row_ptr = (np.arange(F + 1) * 256).astype(np.int32)
+    row_index, seg = stages.group_rows(dev(node), n_nodes - 1, n_nodes)
+    if mode == 0:
+        q = rng.integers(-qmax, qmax, size=(N, K, 2), dtype=np.int32)
+        q[:, :, 1] = np.abs(q[:, :, 1])
+        want = oracle.histogram_q(bins, row_ptr, q, node, n_nodes - 1, 2 * n_nodes - 1)
+        got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), dev(q), row_index, seg, F, mode=0)
+        assert np.array_equal(got.cpu().numpy(), want)
+        got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), _by_position(dev(q), row_index), row_index,
+                               seg, F, mode=0, pairs_by_position=True, max_abs=_max_abs(q))
+        assert np.array_equal(got.cpu().numpy(), want)
+    else:
+        gh = np.stack([rng.normal(size=(N, K)), np.ones((N, K))], axis=2).astype(np.float32)
+        want = oracle.histogram_d(bins, row_ptr, gh[:, :, 0].copy(), gh[:, :, 1].copy(), node, n_nodes - 1, 2 * n_nodes - 1)
+        for by_pos in (False, True):
+            pairs = _by_position(dev(gh), row_index) if by_pos else dev(gh)
+            got = stages.histogram(stages.to_padded_rows(dev(bins)), dev(row_ptr), pairs, row_index, seg, F, mode=1,
+                                   pairs_by_position=by_pos)
+            err = np.abs(got.cpu().numpy() - want).max()
+            assert err <= 1e-5 * np.abs(want).max()
 
 
 def test_full_size_tree_properties(lb):

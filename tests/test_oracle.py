@@ -209,3 +209,60 @@ def test_golden_vectors(oracle):
                                         l2=float(z["l2"]))
         assert np.array_equal(leaf, z["upd_leaf_value"]), path
         assert np.array_equal(hess, z["upd_hessian"]), path
+
+
+# ---------------------------------------------------------------------------------------------
+# The quantised mode against vectors made by the reference's own GPU code (its unmodified
+# build_tree.cu / predict.cu compiled with nvcc against the runtime stand-in and run on a B200:
+# tests/golden/make_golden_q.py).
+#
+# What is bit for bit: the number of bins, feature[], split_value[], the quantised node sums, every
+# traced node's histogram as the split search read it (scan write-skip rule, sibling subtraction,
+# cache / batching rule) and the predictions.  What is not: the three float outputs that pass
+# through the quantiser's scale or a contracted multiply-add.  The scale comes from a float sum
+# over all rows whose order the reference leaves to thrust::reduce; where that order gives the
+# same float as the oracle's fixed order (SAME_SCALE below) the float outputs are bit for bit equal
+# to a build of the reference without multiply-add contraction (stored as *_nofma), elsewhere they
+# differ by a few units in the last place.  The bound asserted for all of them is 1e-12 relative.
+import sys  # noqa: E402
+
+GOLDEN_Q = sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "treeq_*.npz")))
+SAME_SCALE = {"batching", "deep", "mask", "reg", "rows20k", "softmax10"}
+FLOAT_RTOL = 1e-12
+
+
+def _close(a, b):
+    return np.all(np.abs(a - b) <= FLOAT_RTOL * np.maximum(np.abs(a), np.abs(b)))
+
+
+@pytest.mark.parametrize("path", GOLDEN_Q, ids=[os.path.basename(p)[6:-4] for p in GOLDEN_Q])
+def test_mode_q_matches_the_reference_gpu_vectors(oracle, path):
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    import make_golden_q as G
+
+    z, c = G.load_case(path)
+    name = os.path.basename(path)[6:-4]
+    tn = int(z["trace_nodes"])
+    t = oracle.build_tree(c["X"], c["g"], c["h"], max_depth=c["max_depth"], split_samples=c["split_samples"],
+                          seed=c["seed"], l1=c["l1"], l2=c["l2"], min_split_gain=c["min_split_gain"],
+                          feature_set=c["feature_set"], mode="Q", trace_nodes=tn)
+    assert t.B == int(z["total_bins"])
+    assert np.array_equal(t.feature, z["feature"])
+    assert np.array_equal(t.split_value.view(np.int64), z["split_value"].view(np.int64))
+    assert np.array_equal(t.node_sums, z["node_sums"])
+    assert np.array_equal(G.digest(t.trace_hist), z["trace_digest"])
+    stored = z["trace_hist"].shape[0]
+    assert np.array_equal(t.trace_hist[:stored], z["trace_hist"])
+    for k in ("hessian", "leaf_value", "gain"):
+        assert _close(getattr(t, k), z[k]), k
+        if name in SAME_SCALE:
+            assert np.array_equal(getattr(t, k).view(np.int64), z[k + "_nofma"].view(np.int64)), k
+        else:
+            assert _close(getattr(t, k), z[k + "_nofma"]), k
+    # the reference's GPU predict of its own tree
+    pred = oracle.predict(c["X"], [(z["leaf_value"], z["feature"], z["split_value"])])
+    assert np.array_equal(pred.view(np.int64), z["pred"].view(np.int64))
+
+
+def test_golden_q_vectors_are_present():
+    assert len(GOLDEN_Q) >= 10
