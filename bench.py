@@ -261,10 +261,37 @@ def run_hist(args):
         # together with the row ids); made once, outside the timed region
         gp = gp[row_index.long()].contiguous()
 
+    # with several ranks the level's histograms are summed as the tree builder does it: every rank
+    # ends with the sums of the bins of the features it owns (a reduce-scatter over NVLink)
+    sum_mode = 2 if world > 1 else 0
+
     def step():
         stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, mode=mode, hist=hist, ctx=ctx,
-                         max_abs=max_abs if mode == 0 else None, all_reduce=world > 1, max_bins=HIST_BINS,
+                         max_abs=max_abs if mode == 0 else None, all_reduce=sum_mode, max_bins=HIST_BINS,
                          total_bins=HIST_FEATURES * HIST_BINS, pairs_by_position=by_pos)
+
+    # once, outside the timed region: the sums over the ranks against torch.distributed's all-reduce of
+    # the local histograms, for the owned bins (the timed form) and for all bins (all_reduce = 1)
+    allreduce_check = None
+    if world > 1:
+        kw = dict(mode=mode, ctx=ctx, max_abs=max_abs if mode == 0 else None, max_bins=HIST_BINS,
+                  total_bins=HIST_FEATURES * HIST_BINS, pairs_by_position=by_pos)
+        want = stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, all_reduce=0, **kw).clone()
+        dist.all_reduce(want)
+        own = stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, all_reduce=2, **kw).clone()
+        full = stages.histogram(bins, row_ptr, gp, row_index, seg, HIST_FEATURES, all_reduce=1, **kw)
+        f0, f1 = lb.library.owned_features(rank, world, HIST_FEATURES)
+        lo, hi = f0 * HIST_BINS, f1 * HIST_BINS
+        if mode == 0:
+            good = bool(torch.equal(own[:, :, lo:hi], want[:, :, lo:hi])) and bool(torch.equal(full, want))
+        else:
+            tol = 1e-5 * float(want.abs().max())
+            good = float((own[:, :, lo:hi] - want[:, :, lo:hi]).abs().max()) <= tol and \
+                float((full - want).abs().max()) <= tol
+        flag = torch.tensor([1 if good else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        allreduce_check = "ok" if int(flag[0]) == 1 else "mismatch"
+        del want, own, full
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -307,14 +334,14 @@ def run_hist(args):
         n_e2e = max(2, min(args.steps, 5))
         for _ in range(2):
             stages.histogram(hb, hrp, hgp, hidx, hseg, HIST_FEATURES, mode=mode, hist=hh, ctx=ctx, host=True,
-                             all_reduce=world > 1)
+                             all_reduce=sum_mode)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         t0 = time.perf_counter()
         for _ in range(n_e2e):
             stages.histogram(hb, hrp, hgp, hidx, hseg, HIST_FEATURES, mode=mode, hist=hh, ctx=ctx, host=True,
-                             all_reduce=world > 1)
+                             all_reduce=sum_mode)
         torch.cuda.synchronize()
         dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
         if world > 1:
@@ -340,12 +367,16 @@ def run_hist(args):
             "config": {"workload": "histogram build, level 7 (128 nodes), %d rows x %d features x %d bins per GPU, "
                                    "%s gradient pairs%s" % (n_rows, HIST_FEATURES, HIST_BINS,
                                                             "float32" if mode else "quantised int32",
-                                                            ", NCCL all-reduce of the level's histograms" if world > 1 else ""),
+                                                            ", summed over the ranks by feature ownership (every rank "
+                                                            "reads its features' bins from all ranks over NVLink)"
+                                                            if world > 1 else ""),
                        "l2": "160 MB flush buffer written between timed steps; inputs (1.4 GB) exceed L2"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_source": which, "kernel": "k_hist_smem", "kernel_ms": kms},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * args.steps,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": (3 if world == 1 else 5) * args.steps,
         }
+        if allreduce_check is not None:
+            line["allreduce_check"] = allreduce_check
         if not args.no_cpu and world == 1:
             threads = os.cpu_count() or 1
             v, dt, kind = cpu_hist_sample(5_000_000, 7, threads)
@@ -355,6 +386,8 @@ def run_hist(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if allreduce_check == "mismatch":
+        sys.exit(3)
 
 
 def run_train(args):

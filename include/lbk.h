@@ -65,6 +65,11 @@ typedef int (*lbk_allreduce_fn)(void* user, void* buf, size_t count, int dtype /
                                 int op /* lbk_redop */, void* stream);
 int lbk_comm_set_callback(lbk_context* ctx, lbk_allreduce_fn fn, void* user, int rank, int n_ranks);
 int lbk_comm_size(const lbk_context* ctx);
+/* The features rank `rank` of `n_ranks` owns when the features are divided among the ranks for the
+ * sum of a level's histograms and the split search: [*begin, *end).  Contiguous, in rank order, every
+ * feature exactly once; a pure function of its arguments (no device needed).  The reference has no
+ * counterpart: all of its ranks reduce and search everything (build_tree.cu:1107-1151). */
+int lbk_owned_features(int rank, int n_ranks, int n_features, int* begin, int* end);
 
 /* Timing of the histogram kernel alone (no counterpart in the reference, which leaves profiling
  * to external tools): when enabled, every histogram launch is bracketed by CUDA events on the
@@ -258,7 +263,7 @@ int lbk_quantise(lbk_context* ctx, const double* g, const double* h, int64_t ldg
  *   hist[j][k][row_ptr[f] + bin(row,f)] += value(row,k)
  * mode 0: value = int32 pair from gpair, hist = int64 pairs  [n_nodes, n_outputs, B, 2]
  * mode 1: value = float32 pair from gpair_f32, hist = float64 pairs of the same shape.
- * hist is zeroed by the call.  With device buffers the call is asynchronous on `stream` (unless it
+ * hist is overwritten by the call.  With device buffers the call is asynchronous on `stream` (unless it
  * has to read row_ptr back, see max_bins); with host buffers it returns when hist is filled. */
 typedef struct lbk_histogram_args {
   const void* bins;   /* layout of lbk_bin_matrix */
@@ -283,9 +288,13 @@ typedef struct lbk_histogram_args {
                                feature (max of row_ptr[f+1] - row_ptr[f]); with it the call does not
                                read row_ptr back and nothing waits before the kernels are queued.
                                0 = found by the call.  A bound that is too small gives wrong sums. */
-  int32_t all_reduce;       /* 1: hist is summed over the ranks of the context's communicator before
-                               the call returns (the nodes are cut into parts so that the sum of
-                               one part travels while the next part is built) */
+  int32_t all_reduce;       /* 1: hist is summed over the ranks of the context's communicator: every rank
+                               ends with the sums of all bins.  2: every rank ends with the sums of the
+                               bins of the features it owns (lbk_owned_features) - what the tree builder
+                               uses, half of the bytes of 1 on the wire; the other bins of hist are not
+                               written (or hold sums too).  Both go through buffers the ranks' GPUs read
+                               from each other over NVLink where those can be mapped, else through one
+                               all-reduce (then 2 also sums every bin). */
   int32_t pairs_by_position; /* 1: gpair / gpair_f32 are stored in row_index order, [seg[n_nodes], n_outputs, 2]:
                                entry i belongs to row row_index[i].  The pairs of a node are then read as a
                                stream instead of gathered (the tree builder keeps its pairs this way: the

@@ -9,7 +9,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "liblbk.so")
 SOURCES = ["context.cu", "proposals.cu", "quantise.cu", "histogram.cu", "split.cu", "partition.cu",
-           "predict.cu", "update_tree.cu", "objective.cu", "build_tree.cu"]
+           "predict.cu", "update_tree.cu", "objective.cu", "exchange.cu", "build_tree.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-fmad=false", "-I", INCLUDE, "-I", CSRC]

@@ -230,6 +230,12 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
   // the most recently replaced "cache" of the reference, to decide parent availability
   int ref_hist_begin = 0, ref_hist_end = cache_end_ref;
 
+  // the exchange buffers of a multi-rank call, sized once for the largest batch of the tree (the
+  // receive form needs up to twice a batch: see BuildHistogramSummed)
+  const size_t exchange_bytes =
+    2 * sizeof(GPairI64) * node_elems * static_cast<size_t>(std::min<int64_t>(max_batch, static_cast<int64_t>(max_level_nodes))) +
+    (size_t{1} << 20);
+
   for (int depth = 0; depth < D; ++depth) {
     const int level_begin = LevelBegin(depth), level_end = LevelEnd(depth);
     const int level_nodes = level_end - level_begin;
@@ -267,6 +273,12 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
         level_hist = fresh;
       }
       const int n_slots = (parent_available && nb > 0) ? n_nodes / 2 : n_nodes;
+      // With several ranks the level is built into a buffer the other ranks' GPUs can read, and
+      // every rank sums, scans and searches only the features it owns (see exchange.cu); where the
+      // peers cannot be mapped the whole buffer is all-reduced and every rank does everything.
+      const bool owned = ctx->n_ranks > 1 && EnsureExchange(ctx, exchange_bytes, stream);
+      const int f_begin = owned ? OwnedBegin(ctx->rank, ctx->n_ranks, F) : 0;
+      const int f_end   = owned ? OwnedBegin(ctx->rank + 1, ctx->n_ranks, F) : F;
       // built buffer: when nothing is derived the level histogram itself is the target
       GPairI64* target;
       if (n_slots == n_nodes) {
@@ -280,7 +292,7 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
         target = built;
         LBK_CUDA(cudaMemsetAsync(level_hist, 0, sizeof(GPairI64) * n_nodes * node_elems, stream));
       }
-      LBK_CUDA(cudaMemsetAsync(target, 0, sizeof(GPairI64) * n_slots * node_elems, stream));
+      // (the build zeroes the target where it needs it zeroed)
 
       int32_t* slot_of_node = s.alloc<int32_t>(n_nodes);
       PlanBuilt(tree.node_sums, K, nb, n_nodes, parent_available, slot_of_node, stream);
@@ -306,7 +318,8 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
       lv.out                  = target;
       lv.float_mode           = false;
       // build + sum over ranks (reference: :1107-1113 reduces the whole batch; only built nodes here)
-      BuildHistogramAllReduce(ctx, s, lv, n_slots, n_slots != n_nodes, stream);
+      const GPairI64* summed = static_cast<const GPairI64*>(
+        BuildHistogramSummed(ctx, s, lv, n_slots, HistSum::kSumOwned, false, true, stream));
 
       const GPairI64* parent_hist = nullptr;
       int parent_begin            = 0;
@@ -314,14 +327,15 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
         parent_begin = LevelBegin(depth - 1);
         parent_hist  = cache + static_cast<size_t>(parent_begin) * node_elems;
       }
-      ScanLevel(target, slot_of_node, level_hist, parent_hist, parent_begin, tree.node_sums, nb, n_nodes, K, F, B,
-                row_ptr, parent_available, stream);
+      ScanLevel(summed, slot_of_node, level_hist, parent_hist, parent_begin, tree.node_sums, nb, n_nodes, K, f_begin,
+                f_end, B, row_ptr, parent_available, stream);
       if (a.trace_hist && nb < a.trace_nodes) {
         const int cnt = std::min(ne, a.trace_nodes) - nb;
         LBK_CUDA(cudaMemcpyAsync(a.trace_hist + static_cast<size_t>(nb) * node_elems * 2, level_hist,
                                  sizeof(GPairI64) * cnt * node_elems, cudaMemcpyDeviceToDevice, stream));
       }
-      BestSplit<T>(s, level_hist, nb, n_nodes, K, F, B, row_ptr, proposals, qp, sp, tree, split_arrived, ctx->sm_count, stream);
+      BestSplit<T>(ctx, s, level_hist, nb, n_nodes, K, F, B, row_ptr, proposals, qp, sp, tree, split_arrived, f_begin,
+                   f_end, owned, stream);
       s.free_one(slot_of_node);
     }
     if (depth < D - 1) {
@@ -551,6 +565,7 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
     LBK_EXPECT(a->mode == 0 ? a->gpair != nullptr : a->gpair_f32 != nullptr, "missing gradient pairs");
     LBK_EXPECT(a->bin_bytes == 1 || a->bin_bytes == 2, "bin_bytes must be 1 or 2");
     LBK_EXPECT(a->n_nodes >= 1 && a->n_features >= 1 && a->n_outputs >= 1 && a->total_bins >= a->n_features, "bad shape");
+    LBK_EXPECT(a->all_reduce >= 0 && a->all_reduce <= 2, "all_reduce must be 0, 1 or 2");
     LBK_EXPECT(!a->pairs_by_position || !a->host_buffers, "pairs stored by position are for device buffers");
     LBK_EXPECT(!a->pairs_by_position || a->mode == 1 || a->max_abs != nullptr,
                "pairs stored by position need max_abs (the library cannot know how many entries the array has)");
@@ -594,7 +609,9 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
       for (int f = 0; f < F; ++f) mb = std::max(mb, rp[f + 1] - rp[f]);
     }
     LBK_EXPECT(a->bin_bytes == 2 || mb <= 256, "one-byte bins need <= 256 proposals per feature");
-    LBK_CUDA(cudaMemsetAsync(hist, 0, hist_bytes, stream));
+    // (the summed forms zero what they need themselves; the staging copy of a host buffer is fresh
+    // scratch and must not return what it held before)
+    if (a->all_reduce == 0 || a->host_buffers) LBK_CUDA(cudaMemsetAsync(hist, 0, hist_bytes, stream));
     lbk::HistLevel lv;
     lv.bins                 = bins;
     lv.bin_bytes            = a->bin_bytes;
@@ -615,7 +632,8 @@ int lbk_histogram(lbk_context* ctx, const lbk_histogram_args* a)
     lv.slot_of_node         = nullptr;
     lv.out                  = hist;
     lv.float_mode           = a->mode == 1;
-    if (a->all_reduce) lbk::BuildHistogramAllReduce(ctx, s, lv, a->n_nodes, false, stream);
+    if (a->all_reduce == 1) lbk::BuildHistogramSummed(ctx, s, lv, a->n_nodes, lbk::HistSum::kSumEverywhere, true, true, stream);
+    else if (a->all_reduce == 2) lbk::BuildHistogramSummed(ctx, s, lv, a->n_nodes, lbk::HistSum::kSumOwned, true, true, stream);
     else lbk::BuildHistogram(ctx, s, lv, stream);
     // host buffers: the histogram has to be back before the call returns; device buffers: the call
     // is one more piece of work on the caller's stream

@@ -6,7 +6,6 @@
 // needs no NCCL at all and a multi-GPU user shares the copy already loaded in the process.
 #include <dlfcn.h>
 
-#include <climits>
 #include <cstring>
 #include <mutex>
 
@@ -22,29 +21,10 @@ struct NcclApi {
   int (*GetUniqueId)(void*)                                                              = nullptr;
   int (*CommDestroy)(void*)                                                              = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t)            = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t)                 = nullptr;
   const char* (*GetErrorString)(int)                                                     = nullptr;
   void* CommInitRankRaw                                                                  = nullptr;
-  void* CommSplitRaw                                                                     = nullptr;
 };
-
-// The leading fields of ncclConfig_t as they have been since NCCL 2.18; the library reads `size`
-// and `version` and takes its defaults for the fields a shorter structure does not have.
-struct NcclConfigPrefix {
-  size_t size;
-  unsigned int magic;
-  unsigned int version;
-  int blocking;
-  int cgaClusterSize;
-  int minCTAs;
-  int maxCTAs;
-  const char* netName;
-  int splitShare;
-};
-// CTAs the side communicator may use per collective: the histogram kernel leaves 20 SMs free while
-// an all-reduce runs beside it (see BuildHistogramAllReduce); a collective that took more would
-// push histogram blocks into a second round.  Collectives that run alone use the main
-// communicator with the library's own choice of CTAs.
-constexpr int kSideCommMaxCtas = 16;
 
 struct UniqueId {
   char bytes[LBK_UNIQUE_ID_BYTES];
@@ -63,10 +43,11 @@ NcclApi& nccl()
     if (!api.handle) return;
     api.GetUniqueId     = reinterpret_cast<int (*)(void*)>(dlsym(api.handle, "ncclGetUniqueId"));
     api.CommInitRankRaw = dlsym(api.handle, "ncclCommInitRank");
-    api.CommSplitRaw    = dlsym(api.handle, "ncclCommSplit");
     api.CommDestroy     = reinterpret_cast<int (*)(void*)>(dlsym(api.handle, "ncclCommDestroy"));
     api.AllReduce       = reinterpret_cast<int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t)>(
       dlsym(api.handle, "ncclAllReduce"));
+    api.AllGather = reinterpret_cast<int (*)(const void*, void*, size_t, int, void*, cudaStream_t)>(
+      dlsym(api.handle, "ncclAllGather"));
     api.GetErrorString = reinterpret_cast<const char* (*)(int)>(dlsym(api.handle, "ncclGetErrorString"));
   });
   return api;
@@ -132,8 +113,7 @@ void Scratch::free_one(void* p)
     }
 }
 
-void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream,
-               bool beside_kernel)
+void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream)
 {
   if (ctx->n_ranks <= 1 || count == 0) return;
   if (ctx->cb) {
@@ -143,8 +123,16 @@ void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_r
   }
   if (!ctx->nccl_comm) throw Error(LBK_ERR_COMM, "Expected a communicator for a multi-rank call.");
   require_nccl();
-  void* comm = beside_kernel && ctx->nccl_comm_side ? ctx->nccl_comm_side : ctx->nccl_comm;
-  nccl_check(nccl().AllReduce(buf, buf, count, nccl_dtype(dtype), nccl_op(op), comm, stream), "ncclAllReduce");
+  nccl_check(nccl().AllReduce(buf, buf, count, nccl_dtype(dtype), nccl_op(op), ctx->nccl_comm, stream), "ncclAllReduce");
+}
+
+bool AllGatherBytes(lbk_context* ctx, const void* send, void* recv, size_t bytes, cudaStream_t stream)
+{
+  if (ctx->cb != nullptr || ctx->nccl_comm == nullptr) return false;
+  require_nccl();
+  if (nccl().AllGather == nullptr) return false;
+  nccl_check(nccl().AllGather(send, recv, bytes, 0 /* ncclInt8 */, ctx->nccl_comm, stream), "ncclAllGather");
+  return true;
 }
 
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream)
@@ -216,14 +204,10 @@ void lbk_context_destroy(lbk_context* ctx)
   if (!ctx) return;
   cudaSetDevice(ctx->device);
   cudaDeviceSynchronize();
-  if (ctx->nccl_comm_side && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm_side);
+  lbk::DestroyExchange(ctx);
   if (ctx->owns_nccl && ctx->nccl_comm && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
-  if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);
-  for (cudaEvent_t e : ctx->ev_part)
-    if (e) cudaEventDestroy(e);
-  if (ctx->ev_comm_done) cudaEventDestroy(ctx->ev_comm_done);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   delete ctx;
@@ -266,23 +250,6 @@ int lbk_comm_init(lbk_context* ctx, const void* id, int rank, int n_ranks)
     auto init    = reinterpret_cast<InitFn>(nccl().CommInitRankRaw);
     void* comm   = nullptr;
     nccl_check(init(&comm, n_ranks, uid, rank), "ncclCommInitRank");
-    void* side = nullptr;
-    if (n_ranks > 1 && nccl().CommSplitRaw != nullptr) {
-      using SplitFn = int (*)(void*, int, int, void**, void*);  // ncclCommSplit(comm, color, key, newcomm*, config*)
-      NcclConfigPrefix cfg;
-      cfg.size           = sizeof(cfg);
-      cfg.magic          = 0xcafebeefu;
-      cfg.version        = 21800;       // NCCL_VERSION(2, 18, 0): the release this layout is from
-      cfg.blocking       = INT_MIN;     // NCCL_CONFIG_UNDEF_INT: the library's default
-      cfg.cgaClusterSize = INT_MIN;
-      cfg.minCTAs        = INT_MIN;
-      cfg.maxCTAs        = kSideCommMaxCtas;
-      cfg.netName        = nullptr;
-      cfg.splitShare     = INT_MIN;
-      // every rank calls alike; an NCCL that refuses leaves every rank without a side communicator
-      if (reinterpret_cast<SplitFn>(nccl().CommSplitRaw)(comm, 0, rank, &side, &cfg) != 0) side = nullptr;
-    }
-    ctx->nccl_comm_side = side;
     ctx->nccl_comm = comm;
     ctx->owns_nccl = true;
     ctx->rank      = rank;
@@ -318,6 +285,16 @@ int lbk_comm_set_callback(lbk_context* ctx, lbk_allreduce_fn fn, void* user, int
 }
 
 int lbk_comm_size(const lbk_context* ctx) { return ctx ? ctx->n_ranks : 0; }
+
+int lbk_owned_features(int rank, int n_ranks, int n_features, int* begin, int* end)
+{
+  return lbk::Guard(nullptr, [&] {
+    LBK_EXPECT(begin && end, "null argument");
+    LBK_EXPECT(n_ranks >= 1 && rank >= 0 && rank < n_ranks && n_features >= 0, "bad rank or shape");
+    *begin = lbk::OwnedBegin(rank, n_ranks, n_features);
+    *end   = lbk::OwnedBegin(rank + 1, n_ranks, n_features);
+  });
+}
 
 int lbk_profile_enable(lbk_context* ctx, int on)
 {

@@ -133,5 +133,21 @@ __device__ inline void StorePair(GPairI64* p, GPairI64 v)
 {
   *reinterpret_cast<longlong2*>(p) = make_longlong2(v.grad, v.hess);
 }
+__device__ inline void StorePair(GPairF64* p, GPairF64 v)
+{
+  *reinterpret_cast<double2*>(p) = make_double2(v.grad, v.hess);
+}
+// 16-byte loads that go to L2 / the owning GPU every time (no L1 copy): for memory that another
+// GPU or an earlier level wrote
+__device__ inline GPairI64 LoadPairStreaming(const GPairI64* p)
+{
+  const longlong2 v = __ldcg(reinterpret_cast<const longlong2*>(p));
+  return GPairI64{v.x, v.y};
+}
+__device__ inline GPairF64 LoadPairStreaming(const GPairF64* p)
+{
+  const double2 v = __ldcg(reinterpret_cast<const double2*>(p));
+  return GPairF64{v.x, v.y};
+}
 
 }  // namespace lbk

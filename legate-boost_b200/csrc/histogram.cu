@@ -69,7 +69,27 @@ struct HistParams {
   int pairs_by_position;     // 1: gpair is stored in row_index order (pair i belongs to row_index[i]): a stream
   int* status;               // the context's status word; may be null
   void* out;
+  // Several ranks, features divided among them: the histogram of a feature goes straight into the
+  // memory of the rank that owns the feature (a peer store over NVLink), into that rank's receive
+  // slot for this rank: recv[owner][this rank][slot * K + k][bins of the owner's features].
+  void* const* push_recv;    // [push_ranks] receive buffers as this device addresses them; null = `out`
+  int push_rank, push_ranks;
+  long long push_slot_pairs; // pairs per (source rank) block of a receive buffer: segments x push_len
+  int push_len;              // pairs per segment in a receive buffer (bound of the owned bins)
 };
+
+// Where the bins of feature `f` of segment (slot * K + k) go: the base to which the bin is added.
+template <typename out_t>
+__device__ inline out_t* FeatureBase(const HistParams& p, int f, int seg)
+{
+  if (p.push_recv == nullptr) return static_cast<out_t*>(p.out) + static_cast<int64_t>(seg) * p.B + p.row_ptr[f];
+  // owner of f: the largest r with r * F / R <= f
+  int o = static_cast<int>((static_cast<long long>(f + 1) * p.push_ranks - 1) / p.F);
+  if (o > p.push_ranks - 1) o = p.push_ranks - 1;
+  const int lo = p.row_ptr[OwnedBegin(o, p.push_ranks, p.F)];
+  return static_cast<out_t*>(p.push_recv[o]) + static_cast<long long>(p.push_rank) * p.push_slot_pairs +
+         static_cast<long long>(seg) * p.push_len + (p.row_ptr[f] - lo);
+}
 
 __device__ inline unsigned SmemAddr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
 
@@ -328,7 +348,7 @@ __device__ inline Piece DecodeChunk(const HistParams& p, int c)
 // block stride over the rows, every update is a pair of 64-bit global atomics.
 template <typename BinT, typename A>
 __device__ inline void DirectRows(const HistParams& p, int b, int e, int f0, int groups, int k,
-                                  typename A::out_t* onode, int warp, int n_warps, int lane)
+                                  int seg, int warp, int n_warps, int lane)
 {
   using in_t          = typename A::in_t;
   const BinT* bins    = static_cast<const BinT*>(p.bins);
@@ -337,7 +357,7 @@ __device__ inline void DirectRows(const HistParams& p, int b, int e, int f0, int
   for (int u = 0; u < groups; ++u) {
     const int feat = f0 + u * kGroup + lane;
     if (feat >= p.F) continue;
-    typename A::out_t* obase = onode + p.row_ptr[feat];
+    typename A::out_t* obase = FeatureBase<typename A::out_t>(p, feat, seg);
     for (int r = b + warp; r < e; r += n_warps) {
       const int ridx = p.row_index[r];
       const in_t v   = gpair[static_cast<int64_t>(p.pairs_by_position ? r : ridx) * p.K + k];
@@ -365,8 +385,7 @@ __global__ void __launch_bounds__(kHistThreads)
     const int k    = static_cast<int>(t % p.K);
     const int g    = static_cast<int>((t / p.K) % p.G);
     const Piece pc = DecodeChunk(p, static_cast<int>(t / (static_cast<long long>(p.K) * p.G)));
-    typename A::out_t* onode = static_cast<typename A::out_t*>(p.out) + (static_cast<int64_t>(pc.slot) * p.K + k) * p.B;
-    DirectRows<BinT, A>(p, pc.rb, pc.re, g * kGroup, 1, k, onode, warp, kHistThreads / 32, lane);
+    DirectRows<BinT, A>(p, pc.rb, pc.re, g * kGroup, 1, k, pc.slot * p.K + k, warp, kHistThreads / 32, lane);
   }
 }
 
@@ -576,6 +595,7 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ unsigned int s_ticket;
   __shared__ int s_rp[kCols + 1];  // row_ptr of the unit's features (clamped at F)
+  __shared__ typename Acc<kFloat>::out_t* s_base[kCols];  // where bin 0 of each of them goes, for the piece at hand
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned base = SmemAddr(smem_raw);
@@ -620,15 +640,19 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
   auto process = [&](const Piece& pc, int gp, int k) {
     const int g0     = gp * W;
     const int groups = min(W, p.G - g0);
-    out_t* onode     = static_cast<out_t*>(p.out) + (static_cast<int64_t>(pc.slot) * p.K + k) * p.B;
+    const int seg    = pc.slot * p.K + k;
     const bool tree  = pc.pieces > 1 && pc.tree_base >= 0 && p.partial != nullptr && pc.node_rows <= cap_rows &&
                       rows_safe >= kTileRows;
     if (rows_safe < kTileRows || (pc.re - pc.rb <= kDirectRows && !tree)) {
-      DirectRows<uint8_t, A>(p, pc.rb, pc.re, g0 * kGroup, groups, k, onode, warp, kWarps, lane);
+      DirectRows<uint8_t, A>(p, pc.rb, pc.re, g0 * kGroup, groups, k, seg, warp, kWarps, lane);
       return;
     }
     __syncthreads();  // whoever still reads the histogram or s_rp of the piece before
-    for (int i = tid; i <= kCols; i += kThreads) s_rp[i] = p.row_ptr[min(p.F, g0 * kGroup + i)];
+    for (int i = tid; i <= kCols; i += kThreads) {
+      const int f = g0 * kGroup + i;
+      s_rp[i]     = p.row_ptr[min(p.F, f)];
+      if (i < kCols) s_base[i] = f < p.F ? FeatureBase<out_t>(p, f, seg) : nullptr;
+    }
     zero();
     __syncthreads();
 
@@ -657,11 +681,10 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
             for (int i = 0; i < 8; ++i) {
               const smem_t hv = stage[b * 32 + ((4 * i + a + 4 * b) & 31)];
               const int f     = feature_of_word(half * 32 + 4 * i + a);
-              const int fbeg  = s_rp[f];
               const int bin   = bin0 + b;
-              if (bin < s_rp[f + 1] - fbeg && A::nonzero(gv[i], hv)) {
-                if (atomics) A::add_global(onode + fbeg + bin, gv[i], hv);
-                else A::store_global(onode + fbeg + bin, gv[i], hv);
+              if (bin < s_rp[f + 1] - s_rp[f] && A::nonzero(gv[i], hv)) {
+                if (atomics) A::add_global(s_base[f] + bin, gv[i], hv);
+                else A::store_global(s_base[f] + bin, gv[i], hv);
               }
             }
           }
@@ -930,10 +953,15 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   p.status           = ctx->d_status;
   p.pairs_by_position = lv.pairs_by_position ? 1 : 0;
   p.out              = lv.out;
+  p.push_recv        = lv.push_recv;
+  p.push_rank        = ctx->rank;
+  p.push_ranks       = ctx->n_ranks;
+  p.push_slot_pairs  = lv.push_slot_pairs;
+  p.push_len         = lv.push_len;
 
   const bool smem_path = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
   p.mb                 = smem_path ? lv.max_bins_per_feature : 0;
-  const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, p.G, ctx->sm_count - (lv.reserve_sms < ctx->sm_count ? lv.reserve_sms : 0));
+  const HistLaunch hl  = PickHistKernel(smem_path, lv.bin_bytes, lv.float_mode, p.G, ctx->sm_count);
 
   const int* max_abs = lv.max_abs;
   if (!lv.float_mode && max_abs == nullptr) {
@@ -980,73 +1008,59 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
   if (p.partial) s.free_one(p.partial);
 }
 
-void BuildHistogramAllReduce(lbk_context* ctx, Scratch& s, const HistLevel& lv, int n_slots, bool pairs,
-                             cudaStream_t stream)
+void* BuildHistogramSummed(lbk_context* ctx, Scratch& s, const HistLevel& lv, int n_slots, HistSum mode,
+                           bool result_in_out, bool zero_out, cudaStream_t stream)
 {
   const size_t slot_words = static_cast<size_t>(lv.K) * lv.B * 2;  // 64-bit words per slot
-  const lbk_dtype dtype   = lv.float_mode ? LBK_F64 : LBK_I64;
+  const size_t bytes      = static_cast<size_t>(n_slots) * slot_words * 8;
   if (ctx->n_ranks <= 1) {
+    if (zero_out) LBK_CUDA(cudaMemsetAsync(lv.out, 0, bytes, stream));
     if (lv.n_rows > 0) BuildHistogram(ctx, s, lv, stream);
-    return;
+    return lv.out;
   }
-  // Parts: only with NCCL (a callback communicator is not known to be stream-safe), only when every
-  // part still has a ticket for every resident block, and only when there is something to hide.
-  constexpr int kReserve = 20;  // SMs left to the all-reduce kernel
-  const int G            = (lv.F + kGroup - 1) / kGroup;
-  const bool smem_path   = lv.bin_bytes == 1 && lv.max_bins_per_feature <= kSmemBins;
-  const int width        = smem_path && G >= 2 ? 2 : 1;
-  const long long tickets = static_cast<long long>(lv.n_nodes) / (pairs ? 2 : 1) * ((G + width - 1) / width) * lv.K;
-  const int resident     = (ctx->sm_count - kReserve) * (width == 2 ? 1 : 2);
-  int parts              = static_cast<int>(tickets / (resident > 0 ? resident : 1));
-  if (parts > 4) parts = 4;
-  if (ctx->cb != nullptr || ctx->nccl_comm == nullptr || !smem_path || lv.n_rows <= 0 ||
-      static_cast<size_t>(n_slots) * slot_words * 8 < (size_t{8} << 20))
-    parts = 1;
-  if (parts <= 1) {
-    if (lv.n_rows > 0) BuildHistogram(ctx, s, lv, stream);
-    AllReduce(ctx, lv.out, static_cast<size_t>(n_slots) * slot_words, dtype, LBK_SUM, stream);
-    return;
-  }
-  if (ctx->comm_stream == nullptr) {
-    int lo = 0, hi = 0;
-    LBK_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-    LBK_CUDA(cudaStreamCreateWithPriority(&ctx->comm_stream, cudaStreamNonBlocking, hi));
-    for (cudaEvent_t& e : ctx->ev_part) LBK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    LBK_CUDA(cudaEventCreateWithFlags(&ctx->ev_comm_done, cudaEventDisableTiming));
-  }
-  const int unit = pairs ? 2 : 1;  // nodes per slot
-  // the optional timing covers the histogram kernels of all parts (they run back to back)
-  const bool timed = ctx->profile;
-  ctx->profile     = false;
-  if (timed) LBK_CUDA(cudaEventRecord(ctx->ev_start, stream));
-  for (int i = 0; i < parts; ++i) {
-    // node range of the part, on slot boundaries
-    const int s0 = static_cast<int>(static_cast<long long>(n_slots) * i / parts);
-    const int s1 = static_cast<int>(static_cast<long long>(n_slots) * (i + 1) / parts);
-    if (s1 <= s0) continue;
-    HistLevel sub       = lv;
-    sub.seg_node_offset = lv.seg_node_offset + s0 * unit;
-    sub.n_nodes         = (s1 - s0) * unit;
-    sub.reserve_sms     = kReserve;
-    if (lv.slot_of_node != nullptr) {
-      sub.slot_of_node = lv.slot_of_node + s0 * unit;  // absolute slots: `out` stays the base
-    } else {
-      sub.out = static_cast<unsigned char*>(lv.out) + static_cast<size_t>(s0) * slot_words * 8;
+  // every decision below depends only on what is equal on every rank (the shapes, the kind of
+  // communicator, the collective answer of EnsureExchange): all ranks issue the same collectives
+  // The owned sums by push: every rank's kernel stores the histogram of a feature straight into
+  // the owner's receive slot while it runs, a barrier, then the owner adds up its slots locally.
+  // The receive buffers hold ranks x segments x (a bound of the owned bins): where the features'
+  // bin counts are so uneven that the bound is far above the real size, the pull form below is used.
+  if (mode == HistSum::kSumOwned) {
+    const int R          = ctx->n_ranks;
+    const long long fo   = (lv.F + R - 1) / R;  // features of the largest owner
+    long long push_len   = fo * (lv.max_bins_per_feature > 0 ? lv.max_bins_per_feature : lv.B);
+    if (push_len > lv.B) push_len = lv.B;
+    const int n_seg      = n_slots * lv.K;
+    const size_t push_bytes = static_cast<size_t>(R) * n_seg * static_cast<size_t>(push_len) * 16;
+    if (push_bytes <= 2 * bytes + (size_t{1} << 20) && EnsureExchange(ctx, push_bytes, stream)) {
+      void* dst = lv.out;  // every owned bin is written below; the others are not touched
+      HistLevel sub       = lv;
+      sub.push_recv       = NextPushBuffers(ctx, stream);
+      sub.push_slot_pairs = static_cast<long long>(n_seg) * push_len;
+      sub.push_len        = static_cast<int>(push_len);
+      if (lv.n_rows > 0) BuildHistogram(ctx, s, sub, stream);
+      ExchangeReducePushed(ctx, dst, n_seg, static_cast<int>(push_len), lv.B, lv.F, lv.row_ptr, lv.float_mode, stream);
+      return dst;
     }
-    BuildHistogram(ctx, s, sub, stream);
-    if (timed && i == parts - 1) {
-      LBK_CUDA(cudaEventRecord(ctx->ev_stop, stream));
-      ctx->profile_recorded = true;
-    }
-    LBK_CUDA(cudaEventRecord(ctx->ev_part[i], stream));
-    LBK_CUDA(cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_part[i], 0));
-    // every part but the last has the next part's kernel beside it
-    AllReduce(ctx, static_cast<unsigned char*>(lv.out) + static_cast<size_t>(s0) * slot_words * 8,
-              static_cast<size_t>(s1 - s0) * slot_words, dtype, LBK_SUM, ctx->comm_stream, i + 1 < parts);
   }
-  ctx->profile = timed;
-  LBK_CUDA(cudaEventRecord(ctx->ev_comm_done, ctx->comm_stream));
-  LBK_CUDA(cudaStreamWaitEvent(stream, ctx->ev_comm_done, 0));
+  if (EnsureExchange(ctx, bytes, stream)) {
+    void* buf = NextExchangeBuffer(ctx, bytes, stream);
+    HistLevel sub = lv;
+    sub.out       = buf;
+    if (lv.n_rows > 0) BuildHistogram(ctx, s, sub, stream);
+    const int n_seg = n_slots * lv.K;
+    if (mode == HistSum::kSumOwned) {
+      void* dst = result_in_out ? lv.out : buf;
+      ExchangeReduceOwned(ctx, buf, dst, n_seg, lv.B, lv.F, lv.row_ptr, lv.float_mode, stream);
+      return dst;
+    }
+    ExchangeReduceOwned(ctx, buf, buf, n_seg, lv.B, lv.F, lv.row_ptr, lv.float_mode, stream);
+    ExchangeGatherAll(ctx, buf, lv.out, n_seg, lv.B, lv.F, lv.row_ptr, stream);
+    return lv.out;
+  }
+  if (zero_out) LBK_CUDA(cudaMemsetAsync(lv.out, 0, bytes, stream));
+  if (lv.n_rows > 0) BuildHistogram(ctx, s, lv, stream);
+  AllReduce(ctx, lv.out, static_cast<size_t>(n_slots) * slot_words, lv.float_mode ? LBK_F64 : LBK_I64, LBK_SUM, stream);
+  return lv.out;
 }
 
 void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t n_rows, int node_begin,
@@ -1210,6 +1224,11 @@ extern "C" int lbk_histogram_noalloc(int device, const lbk_histogram_args* a)
     p.arrive    = nullptr;
     p.partial   = nullptr;
     p.status    = nullptr;
+    p.push_recv = nullptr;
+    p.push_rank = 0;
+    p.push_ranks = 1;
+    p.push_slot_pairs = 0;
+    p.push_len  = 0;
     p.pairs_by_position = a->pairs_by_position != 0 ? 1 : 0;
     k_hist_plan<<<1, 1024, 0, stream>>>(p.seg, nullptr, p.n_nodes, (p.G + hl.width - 1) / hl.width * p.K, hl.grid,
                                         float_mode ? nullptr : max_abs, 0, chunk_off, nullptr, nullptr, 0, plan,

@@ -56,6 +56,10 @@ constexpr int kGroup = 32;  // features per feature group (one lane per feature)
 
 }  // namespace lbk
 
+namespace lbk {
+struct PeerExchange;
+}
+
 // The context is an opaque C struct for callers.
 struct lbk_context {
   int device        = 0;
@@ -68,14 +72,11 @@ struct lbk_context {
   // communicator
   int rank = 0, n_ranks = 1;
   void* nccl_comm     = nullptr;
-  void* nccl_comm_side = nullptr;  // same ranks, few CTAs per collective: for all-reduces that run beside a kernel
   bool owns_nccl      = false;
   lbk_allreduce_fn cb = nullptr;
   void* cb_user       = nullptr;
-  // second stream for all-reduces that run beside the next histogram kernel (made on first use)
-  cudaStream_t comm_stream = nullptr;
-  cudaEvent_t ev_part[4]   = {nullptr, nullptr, nullptr, nullptr};
-  cudaEvent_t ev_comm_done = nullptr;
+  // buffers that the other ranks' GPUs can read (see exchange.cu); made on first use
+  lbk::PeerExchange* xchg = nullptr;
   // optional timing of the histogram kernel alone (events on the caller's stream)
   bool profile            = false;
   cudaEvent_t ev_start    = nullptr, ev_stop = nullptr;
@@ -106,10 +107,44 @@ class Scratch {
 };
 
 // In-place all-reduce over the context's communicator; no-op for a single rank.
-// `beside_kernel`: the collective shares the GPU with a kernel of ours; use the communicator that
-// is limited to a few CTAs, if there is one.
-void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream,
-               bool beside_kernel = false);
+void AllReduce(lbk_context* ctx, void* buf, size_t count, lbk_dtype dtype, lbk_redop op, cudaStream_t stream);
+// Every rank contributes `bytes` bytes at `send` and receives all contributions, in rank order, at
+// `recv` (device pointers; NCCL communicators only: returns false where the communicator is a
+// callback or missing).
+bool AllGatherBytes(lbk_context* ctx, const void* send, void* recv, size_t bytes, cudaStream_t stream);
+
+// ---- peer exchange (exchange.cu) ------------------------------------------------------------
+// Two buffers per rank that every other rank's GPU can read directly over NVLink (CUDA IPC between
+// processes, plain peer access inside one process), used to sum the histograms of a level: every
+// rank builds into its own buffer, a barrier, then rank r reads the bins of the features it owns
+// from all ranks and adds them up (a reduce-scatter made of peer loads).  The two buffers
+// alternate so that one barrier per level is enough.
+//
+// Collective: every rank calls with the same `bytes`.  Returns false (on every rank alike) where the
+// peers cannot be mapped or the communicator is not NCCL; callers then fall back to AllReduce.
+bool EnsureExchange(lbk_context* ctx, size_t bytes, cudaStream_t stream);
+void DestroyExchange(lbk_context* ctx);
+// The buffer the next build goes into (alternates on every call), its first `bytes` bytes zeroed.
+void* NextExchangeBuffer(lbk_context* ctx, size_t bytes, cudaStream_t stream);
+// Features [OwnedBegin(r), OwnedBegin(r + 1)) belong to rank r.
+__host__ __device__ inline int OwnedBegin(int rank, int n_ranks, int F) { return static_cast<int>(static_cast<long long>(rank) * F / n_ranks); }
+// After every rank has built [n_seg][B] pairs into `buf` (the buffer NextExchangeBuffer returned):
+// dst[seg][b] = sum over ranks of their buf[seg][b] for the bins b of this rank's features; dst may
+// be `buf` itself (in place).  Includes the barrier.
+void ExchangeReduceOwned(lbk_context* ctx, void* buf, void* dst, int n_seg, int B, int F, const int32_t* row_ptr,
+                         bool float_mode, cudaStream_t stream);
+// The push form.  NextPushBuffers: the device array of every rank's receive buffer for the next
+// build (alternating, all zero when handed out).  ExchangeReducePushed, after every rank has built
+// with them: a barrier, then dst[seg][b] = sum over source ranks of this rank's receive slots, for the
+// bins b of its features (dst is local memory, [n_seg][B] pairs); the slots are zeroed as they are
+// read, so the buffer is clean when its turn comes again.
+void* const* NextPushBuffers(lbk_context* ctx, cudaStream_t stream);
+void ExchangeReducePushed(lbk_context* ctx, void* dst, int n_seg, int push_len, int B, int F, const int32_t* row_ptr,
+                          bool float_mode, cudaStream_t stream);
+// After ExchangeReduceOwned in place on every rank: dst[seg][b] = the owner's sum, for all bins.
+// Includes a barrier.
+void ExchangeGatherAll(lbk_context* ctx, void* buf, void* dst, int n_seg, int B, int F, const int32_t* row_ptr,
+                       cudaStream_t stream);
 // Reads the device status word (synchronises the stream) and throws LBK_ERR_DEVICE if set.
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream);
 
@@ -155,15 +190,26 @@ struct HistLevel {
   const int32_t* slot_of_node;
   void* out;               // [n_slots, K, B] pairs (int64 or double), already zeroed
   bool float_mode;
-  int reserve_sms = 0;     // SMs the persistent grid leaves free (for a collective that runs beside it)
+  // set by BuildHistogramSummed only: the histograms go into the owners' receive buffers (see
+  // HistParams in histogram.cu)
+  void* const* push_recv     = nullptr;
+  long long push_slot_pairs = 0;
+  int push_len              = 0;
 };
 void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStream_t stream);
-// BuildHistogram followed by the sum over ranks of the n_slots histograms of `out`.  With an NCCL
-// communicator and enough tickets the nodes are cut into parts: the all-reduce of one part runs
-// on a second stream beside the histogram kernel of the next.  `pairs` says that slot s holds
-// the built child of nodes 2s, 2s+1 of the batch (else slot = node).
-void BuildHistogramAllReduce(lbk_context* ctx, Scratch& s, const HistLevel& lv, int n_slots, bool pairs,
-                             cudaStream_t stream);
+// BuildHistogram followed by the sum over ranks of the n_slots histograms.
+//   kSumEverywhere: lv.out holds the sums of all bins on every rank when the call returns.
+//   kSumOwned:      only the bins of the features this rank owns are summed (OwnedBegin); the
+//                   result is where the returned pointer says: lv.out, or the exchange buffer the
+//                   level was built in (which stays valid until the build after the next).
+// Through the peer exchange where it is available, else one all-reduce of the whole buffer (then
+// every bin is summed on every rank, whatever the mode).  The sequence of collectives depends only
+// on values that are equal on every rank; a rank without rows skips the kernel, nothing else.
+// zero_out: lv.out has not been zeroed; the call zeroes it where the build goes into it (through the
+// exchange it does not: what is not written there stays as it was).
+enum class HistSum { kSumEverywhere, kSumOwned };
+void* BuildHistogramSummed(lbk_context* ctx, Scratch& s, const HistLevel& lv, int n_slots, HistSum mode,
+                           bool result_in_out, bool zero_out, cudaStream_t stream);
 void GroupRows(lbk_context* ctx, Scratch& s, const int32_t* node_of_row, int64_t n_rows, int node_begin,
                int n_nodes, int32_t* row_index, int32_t* seg, cudaStream_t stream);
 // split.cu
@@ -184,15 +230,21 @@ struct SplitParams {
 void PlanBuilt(const GPairI64* node_sums, int K, int node_begin, int n_nodes, bool parent_available,
                int32_t* slot_of_node, cudaStream_t stream);
 // Scan built histograms into the level histogram, derive siblings from the parent.
+// Only the features [f_begin, f_end) are scanned / derived (all of them on one rank; the owned ones
+// when the features are divided among the ranks).
 void ScanLevel(const GPairI64* built, const int32_t* slot_of_node, GPairI64* level_hist /* node_begin based */,
                const GPairI64* parent_hist /* level above, may be null */, int parent_begin,
-               const GPairI64* node_sums, int node_begin, int n_nodes, int K, int F, int B,
+               const GPairI64* node_sums, int node_begin, int n_nodes, int K, int f_begin, int f_end, int B,
                const int32_t* row_ptr, bool parent_available, cudaStream_t stream);
-// arrived: one counter per tree node, zero before the first call of a tree
+// arrived: one counter per tree node, zero before the first call of a tree.  The bins of the features
+// [f_begin, f_end) are evaluated; with exchange_records every rank's best candidate of every node
+// (and the sums left of it) is gathered on all ranks and the best of them becomes the tree - the same
+// total order as within a rank, so the tree is the one a single rank would grow.
 template <typename T>
-void BestSplit(Scratch& s, const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B,
+void BestSplit(lbk_context* ctx, Scratch& s, const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B,
                const int32_t* row_ptr, const T* proposals, const QuantParams* qp, const SplitParams& sp,
-               TreeArrays tree, unsigned int* arrived, int sm_count, cudaStream_t stream);
+               TreeArrays tree, unsigned int* arrived, int f_begin, int f_end, bool exchange_records,
+               cudaStream_t stream);
 void RootLeaf(TreeArrays tree, int K, const QuantParams* qp, double l1, double l2, cudaStream_t stream);
 void WriteHessian(const GPairI64* node_sums, const QuantParams* qp, double* hessian, int64_t n, cudaStream_t stream);
 // partition.cu

@@ -167,6 +167,10 @@ __global__ void __launch_bounds__(1024)
   if (threadIdx.x == 0) seg_out[2 * n_nodes] = node_base[n_nodes];
 }
 
+// One block per chunk.  The rows that go left leave the chunk as one contiguous run of the left
+// child's segment and the rows that go right as one run of the right child's, so the block first
+// orders its rows (and, if the gradient pairs travel with them, the pairs) in shared memory and then
+// copies the two runs out with coalesced stores.
 __global__ void __launch_bounds__(kPartThreads)
   k_part_scatter(const int32_t* __restrict__ row_index, const int32_t* __restrict__ seg,
                  const int32_t* __restrict__ chunk_off, int n_nodes, const uint8_t* __restrict__ masks,
@@ -174,14 +178,19 @@ __global__ void __launch_bounds__(kPartThreads)
                  int32_t* __restrict__ row_index_out, const int2* __restrict__ pairs_in, int2* __restrict__ pairs_out,
                  int K)
 {
+  __shared__ int32_t s_rows[kPartTile];
+  __shared__ int2 s_pairs[kPartTile];
+  __shared__ int wsum[kPartThreads / 32];
   const int c = blockIdx.x;
   if (c >= chunk_off[n_nodes]) return;
   const int j      = FindOwner(chunk_off, n_nodes, c);
   const int lc     = c - chunk_off[j];
   const int rb     = seg[j] + lc * kPartTile;
   const int re     = min(seg[j + 1], rb + kPartTile);
+  const int n_here = re - rb;
   const int lefts_before  = left_prefix[c] - left_prefix[chunk_off[j]];
   const int rights_before = lc * kPartTile - lefts_before;
+  const int block_lefts   = left_prefix[c + 1] - left_prefix[c];
   const int tid    = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r0     = rb + tid * kPartItems;
   const int nvalid = max(0, min(kPartItems, re - r0));
@@ -192,25 +201,36 @@ __global__ void __launch_bounds__(kPartThreads)
     int v = __shfl_up_sync(0xffffffffu, incl, off);
     if (lane >= off) incl += v;
   }
-  __shared__ int wsum[kPartThreads / 32];
   if (lane == 31) wsum[warp] = incl;
   __syncthreads();
   int wbefore = 0;
   for (int w = 0; w < warp; ++w) wbefore += wsum[w];
-  const int left_rank  = wbefore + incl - my_left;                // lefts before this thread in the chunk
-  const int right_rank = tid * kPartItems - left_rank;           // rights before this thread
-  int lpos = seg_out[2 * j] + lefts_before + left_rank;
-  int rpos = seg_out[2 * j + 1] + rights_before + right_rank;
+  const int left_rank  = wbefore + incl - my_left;        // lefts before this thread in the chunk
+  const int right_rank = tid * kPartItems - left_rank;    // rights before this thread
+  // place inside the chunk: the lefts first, then the rights, each in row order
+  int local[kPartItems];
+  {
+    int lp = left_rank, rp = block_lefts + right_rank;
 #pragma unroll
-  for (int i = 0; i < kPartItems; ++i) {
-    if (i < nvalid) {
-      const int ridx = row_index[r0 + i];
-      const int dst  = (mask & (1u << i)) ? lpos++ : rpos++;
-      row_index_out[dst] = ridx;
-      // the gradient pairs travel with the row ids, so that the histogram kernel reads them as a stream
-      if (pairs_in != nullptr)
-        for (int k = 0; k < K; ++k)
-          pairs_out[static_cast<int64_t>(dst) * K + k] = pairs_in[static_cast<int64_t>(r0 + i) * K + k];
+    for (int i = 0; i < kPartItems; ++i) local[i] = (mask & (1u << i)) ? lp++ : rp++;
+  }
+#pragma unroll
+  for (int i = 0; i < kPartItems; ++i)
+    if (i < nvalid) s_rows[local[i]] = row_index[r0 + i];
+  __syncthreads();
+  const int lbase = seg_out[2 * j] + lefts_before;
+  const int rbase = seg_out[2 * j + 1] + rights_before - block_lefts;  // + t for t >= block_lefts
+  for (int t = tid; t < n_here; t += kPartThreads) row_index_out[(t < block_lefts ? lbase : rbase) + t] = s_rows[t];
+  // the gradient pairs travel with the row ids, so that the histogram kernel reads them as a stream
+  if (pairs_in != nullptr) {
+    for (int k = 0; k < K; ++k) {
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < kPartItems; ++i)
+        if (i < nvalid) s_pairs[local[i]] = pairs_in[static_cast<int64_t>(r0 + i) * K + k];
+      __syncthreads();
+      for (int t = tid; t < n_here; t += kPartThreads)
+        pairs_out[static_cast<int64_t>((t < block_lefts ? lbase : rbase) + t) * K + k] = s_pairs[t];
     }
   }
 }

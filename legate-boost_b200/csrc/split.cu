@@ -45,14 +45,14 @@ __global__ void k_plan_built(const GPairI64* __restrict__ node_sums, int K, int 
 __global__ void __launch_bounds__(256)
   k_scan(const GPairI64* __restrict__ built, const int32_t* __restrict__ slot_of_node,
          GPairI64* __restrict__ level_hist, const GPairI64* __restrict__ parent_hist, int parent_begin,
-         const GPairI64* __restrict__ node_sums, int node_begin, int n_nodes, int K, int F, int B,
-         const int32_t* __restrict__ row_ptr, bool parent_available)
+         const GPairI64* __restrict__ node_sums, int node_begin, int n_nodes, int K, int f_begin, int n_features,
+         int B, const int32_t* __restrict__ row_ptr, bool parent_available)
 {
   const int lane    = threadIdx.x & 31;
   const int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  if (wid >= static_cast<int64_t>(n_nodes) * F) return;
-  const int j    = static_cast<int>(wid / F);
-  const int f    = static_cast<int>(wid % F);
+  if (wid >= static_cast<int64_t>(n_nodes) * n_features) return;
+  const int j    = static_cast<int>(wid / n_features);
+  const int f    = f_begin + static_cast<int>(wid % n_features);
   const int k    = blockIdx.y;
   const int node = node_begin + j;
   const int slot = slot_of_node[j];
@@ -130,6 +130,50 @@ struct SliceBest {
   int pad;
 };
 
+// The winner of a node becomes the tree: feature, split value, gain, and the sums and leaf values
+// of the two children.  left_sums[k * left_stride] = the sums left of the winning bin, output k.
+template <typename T>
+__device__ inline void ApplyWinner(const Cand& nb, int node, int K, int F, const int32_t* __restrict__ row_ptr,
+                                   const T* __restrict__ proposals, const QuantParams& qp, double l1, double l2,
+                                   TreeArrays tree, const GPairI64* __restrict__ left_sums, int64_t left_stride, int tid,
+                                   int n_threads)
+{
+  if (!(nb.gain > 1e-5)) return;
+  GPairI64* node_sums = tree.node_sums;
+  int lo = 0, hi = F;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (row_ptr[mid] <= nb.bin) lo = mid; else hi = mid;
+  }
+  const int bf = lo;
+  const int l = 2 * node + 1, r = 2 * node + 2;
+  for (int k = tid; k < K; k += n_threads) {
+    const GPairI64 ns = LoadPair(node_sums + static_cast<int64_t>(node) * K + k);
+    const GPairI64 ls = LoadPair(left_sums + static_cast<int64_t>(k) * left_stride);
+    const GPairI64 rs{ns.grad - ls.grad, ns.hess - ls.hess};
+    StorePair(node_sums + static_cast<int64_t>(l) * K + k, ls);
+    StorePair(node_sums + static_cast<int64_t>(r) * K + k, rs);
+    const GPairF64 dl = Dequantise(ls, qp), dr = Dequantise(rs, qp);
+    tree.leaf_value[static_cast<int64_t>(l) * K + k] = CalculateLeafValue(dl.grad, dl.hess, l1, l2);
+    tree.leaf_value[static_cast<int64_t>(r) * K + k] = CalculateLeafValue(dr.grad, dr.hess, l1, l2);
+    if (k == 0) {
+      tree.feature[node]     = bf;
+      tree.split_value[node] = static_cast<double>(proposals[nb.bin]);
+      tree.gain[node]        = nb.gain;
+      tree.split_bin[node]   = nb.bin - row_ptr[bf];
+    }
+  }
+}
+
+// What a rank knows about its best split of a node when the features are divided among the ranks:
+// the candidate and the sums left of it; K pairs follow the header.
+struct SplitRecordHeader {
+  double gain;
+  int bin;
+  int pad;
+};
+__host__ __device__ inline size_t SplitRecordBytes(int K) { return sizeof(SplitRecordHeader) + sizeof(GPairI64) * K; }
+
 // grid = (nodes, slices): a block evaluates one slice of the node's bins (all of them when there is
 // one slice).  With several slices every block leaves its best candidate in `slice_best`, and the
 // block that arrives last (a counter per node, zeroed once per tree) picks the winner and writes
@@ -140,7 +184,7 @@ __global__ void __launch_bounds__(kSplitThreads)
                const int32_t* __restrict__ row_ptr, const T* __restrict__ proposals,
                const QuantParams* __restrict__ qp_ptr, double l1, double l2, double msg,
                const uint8_t* __restrict__ feature_set, TreeArrays tree, SliceBest* __restrict__ slice_best,
-               unsigned int* __restrict__ arrived)
+               unsigned int* __restrict__ arrived, int f_begin, int f_end, unsigned char* __restrict__ records)
 {
   const int j      = blockIdx.x;
   const int slices = gridDim.y;
@@ -153,8 +197,10 @@ __global__ void __launch_bounds__(kSplitThreads)
   __shared__ Cand s_best;
   __shared__ bool s_last;
   const int tid = threadIdx.x;
-  const int per = (B + slices - 1) / slices;
-  const int b0  = blockIdx.y * per, b1 = min(B, b0 + per);
+  // the bins this rank evaluates (all of them unless the features are divided among the ranks)
+  const int bin_begin = row_ptr[f_begin], bin_end = row_ptr[f_end];
+  const int per = (bin_end - bin_begin + slices - 1) / slices;
+  const int b0  = bin_begin + blockIdx.y * per, b1 = min(bin_end, b0 + per);
   Cand best{0.0, -1};
   for (int b = b0 + tid; b < b1; b += kSplitThreads) {
     if (feature_set) {
@@ -224,30 +270,52 @@ __global__ void __launch_bounds__(kSplitThreads)
     block_best();
   }
   const Cand nb = s_best;
-  if (!(nb.gain > 1e-5)) return;
-  int lo = 0, hi = F;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (row_ptr[mid] <= nb.bin) lo = mid; else hi = mid;
+  if (records != nullptr) {
+    // leave the candidate and its left sums for the exchange among the ranks
+    unsigned char* rec = records + static_cast<size_t>(j) * SplitRecordBytes(K);
+    if (tid == 0) {
+      SplitRecordHeader h;
+      h.gain = nb.gain;
+      h.bin  = nb.bin;
+      h.pad  = 0;
+      *reinterpret_cast<SplitRecordHeader*>(rec) = h;
+    }
+    GPairI64* ls = reinterpret_cast<GPairI64*>(rec + sizeof(SplitRecordHeader));
+    for (int k = tid; k < K; k += kSplitThreads)
+      StorePair(ls + k, nb.bin >= 0 ? LoadPair(hist + static_cast<int64_t>(k) * B + nb.bin) : GPairI64{0, 0});
+    return;
   }
-  const int bf = lo;
-  const int l = 2 * node + 1, r = 2 * node + 2;
-  for (int k = tid; k < K; k += kSplitThreads) {
-    const GPairI64 ns = LoadPair(node_sums + static_cast<int64_t>(node) * K + k);
-    const GPairI64 ls = LoadPair(hist + static_cast<int64_t>(k) * B + nb.bin);
-    const GPairI64 rs{ns.grad - ls.grad, ns.hess - ls.hess};
-    StorePair(node_sums + static_cast<int64_t>(l) * K + k, ls);
-    StorePair(node_sums + static_cast<int64_t>(r) * K + k, rs);
-    const GPairF64 dl = Dequantise(ls, qp), dr = Dequantise(rs, qp);
-    tree.leaf_value[static_cast<int64_t>(l) * K + k] = CalculateLeafValue(dl.grad, dl.hess, l1, l2);
-    tree.leaf_value[static_cast<int64_t>(r) * K + k] = CalculateLeafValue(dr.grad, dr.hess, l1, l2);
-    if (k == 0) {
-      tree.feature[node]     = bf;
-      tree.split_value[node] = static_cast<double>(proposals[nb.bin]);
-      tree.gain[node]        = nb.gain;
-      tree.split_bin[node]   = nb.bin - row_ptr[bf];
+  ApplyWinner<T>(nb, node, K, F, row_ptr, proposals, qp, l1, l2, tree, nb.bin >= 0 ? hist + nb.bin : hist, B, tid,
+                 kSplitThreads);
+}
+
+// One block per node: the best of the ranks' candidates (the same total order as inside a rank, so
+// the winner is the one a single rank would have found over all features) becomes the tree.
+template <typename T>
+__global__ void __launch_bounds__(64)
+  k_apply_records(const unsigned char* __restrict__ all_records, int n_ranks, int n_nodes, int node_begin, int K, int F,
+                  const int32_t* __restrict__ row_ptr, const T* __restrict__ proposals,
+                  const QuantParams* __restrict__ qp_ptr, double l1, double l2, TreeArrays tree)
+{
+  const int j    = blockIdx.x;
+  const int node = node_begin + j;
+  if (LoadPair(tree.node_sums + static_cast<int64_t>(node) * K).hess <= 0) return;
+  const size_t rb = SplitRecordBytes(K);
+  Cand best{0.0, -1};
+  int best_rank = -1;
+  for (int r = 0; r < n_ranks; ++r) {
+    const SplitRecordHeader* h =
+      reinterpret_cast<const SplitRecordHeader*>(all_records + (static_cast<size_t>(r) * n_nodes + j) * rb);
+    const Cand c{h->gain, h->bin};
+    if (c.gain > 0 && c.bin >= 0 && Better(c, best)) {
+      best      = c;
+      best_rank = r;
     }
   }
+  if (best_rank < 0) return;
+  const GPairI64* ls = reinterpret_cast<const GPairI64*>(
+    all_records + (static_cast<size_t>(best_rank) * n_nodes + j) * rb + sizeof(SplitRecordHeader));
+  ApplyWinner<T>(best, node, K, F, row_ptr, proposals, *qp_ptr, l1, l2, tree, ls, 1, threadIdx.x, blockDim.x);
 }
 
 __global__ void k_root_leaf(TreeArrays tree, int K, const QuantParams* __restrict__ qp_ptr, double l1, double l2)
@@ -276,34 +344,61 @@ void PlanBuilt(const GPairI64* node_sums, int K, int node_begin, int n_nodes, bo
 }
 
 void ScanLevel(const GPairI64* built, const int32_t* slot_of_node, GPairI64* level_hist, const GPairI64* parent_hist,
-               int parent_begin, const GPairI64* node_sums, int node_begin, int n_nodes, int K, int F, int B,
-               const int32_t* row_ptr, bool parent_available, cudaStream_t stream)
+               int parent_begin, const GPairI64* node_sums, int node_begin, int n_nodes, int K, int f_begin, int f_end,
+               int B, const int32_t* row_ptr, bool parent_available, cudaStream_t stream)
 {
-  const int64_t warps  = static_cast<int64_t>(n_nodes) * F;
+  const int n_features = f_end - f_begin;
+  if (n_features <= 0 || n_nodes <= 0) return;
+  const int64_t warps  = static_cast<int64_t>(n_nodes) * n_features;
   const int64_t blocks = (warps + 7) / 8;
   dim3 grid(static_cast<unsigned>(blocks), K);
   k_scan<<<grid, 256, 0, stream>>>(built, slot_of_node, level_hist, parent_hist, parent_begin, node_sums, node_begin,
-                                   n_nodes, K, F, B, row_ptr, parent_available);
+                                   n_nodes, K, f_begin, n_features, B, row_ptr, parent_available);
   LBK_LAUNCH_CHECK();
 }
 
 template <typename T>
-void BestSplit(Scratch& s, const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B,
+void BestSplit(lbk_context* ctx, Scratch& s, const GPairI64* level_hist, int node_begin, int n_nodes, int K, int F, int B,
                const int32_t* row_ptr, const T* proposals, const QuantParams* qp, const SplitParams& sp, TreeArrays tree,
-               unsigned int* arrived, int sm_count, cudaStream_t stream)
+               unsigned int* arrived, int f_begin, int f_end, bool exchange_records, cudaStream_t stream)
 {
+  const int sm_count = ctx->sm_count;
+  // the bins of the features [f_begin, f_end): row_ptr lives on the device, so the kernel gets the
+  // range through two small reads of its own; here only an upper bound of its length matters
+  const int n_bins_bound = exchange_records ? (B + ctx->n_ranks - 1) / ctx->n_ranks + 1 : B;
   // enough blocks for two per SM, at least one thread per bin in a block's slice
   int slices = (2 * sm_count + n_nodes - 1) / n_nodes;
-  const int most = (B + kSplitThreads - 1) / kSplitThreads;
+  const int most = (n_bins_bound + kSplitThreads - 1) / kSplitThreads;
   if (slices > most) slices = most;
   if (slices > kSplitThreads) slices = kSplitThreads;
   if (slices < 1) slices = 1;
   SliceBest* slice_best = slices > 1 ? s.alloc<SliceBest>(static_cast<size_t>(n_nodes) * slices) : nullptr;
-  k_best_split<T><<<dim3(n_nodes, slices), kSplitThreads, 0, stream>>>(level_hist, node_begin, K, F, B, row_ptr, proposals,
-                                                                      qp, sp.l1, sp.l2, sp.min_split_gain, sp.feature_set,
-                                                                      tree, slice_best, arrived);
+  if (!exchange_records) {
+    k_best_split<T><<<dim3(n_nodes, slices), kSplitThreads, 0, stream>>>(
+      level_hist, node_begin, K, F, B, row_ptr, proposals, qp, sp.l1, sp.l2, sp.min_split_gain, sp.feature_set, tree,
+      slice_best, arrived, f_begin, f_end, nullptr);
+    LBK_LAUNCH_CHECK();
+    if (slice_best) s.free_one(slice_best);
+    return;
+  }
+  // every rank searches its own features, then the candidates of all ranks meet on every rank
+  const size_t rb   = SplitRecordBytes(K);
+  const int R       = ctx->n_ranks;
+  unsigned char* mine = s.alloc<unsigned char>(rb * n_nodes);
+  unsigned char* all  = s.alloc<unsigned char>(rb * n_nodes * R);
+  LBK_CUDA(cudaMemsetAsync(mine, 0, rb * n_nodes, stream));
+  k_best_split<T><<<dim3(n_nodes, slices), kSplitThreads, 0, stream>>>(
+    level_hist, node_begin, K, F, B, row_ptr, proposals, qp, sp.l1, sp.l2, sp.min_split_gain, sp.feature_set, tree,
+    slice_best, arrived, f_begin, f_end, mine);
+  LBK_LAUNCH_CHECK();
+  if (!AllGatherBytes(ctx, mine, all, rb * n_nodes, stream))
+    throw Error(LBK_ERR_COMM, "the split records need an NCCL communicator");
+  k_apply_records<T><<<n_nodes, 64, 0, stream>>>(all, R, n_nodes, node_begin, K, F, row_ptr, proposals, qp, sp.l1, sp.l2,
+                                                  tree);
   LBK_LAUNCH_CHECK();
   if (slice_best) s.free_one(slice_best);
+  s.free_one(mine);
+  s.free_one(all);
 }
 
 void RootLeaf(TreeArrays tree, int K, const QuantParams* qp, double l1, double l2, cudaStream_t stream)
@@ -318,9 +413,11 @@ void WriteHessian(const GPairI64* node_sums, const QuantParams* qp, double* hess
   LBK_LAUNCH_CHECK();
 }
 
-template void BestSplit<float>(Scratch&, const GPairI64*, int, int, int, int, int, const int32_t*, const float*,
-                               const QuantParams*, const SplitParams&, TreeArrays, unsigned int*, int, cudaStream_t);
-template void BestSplit<double>(Scratch&, const GPairI64*, int, int, int, int, int, const int32_t*, const double*,
-                                const QuantParams*, const SplitParams&, TreeArrays, unsigned int*, int, cudaStream_t);
+template void BestSplit<float>(lbk_context*, Scratch&, const GPairI64*, int, int, int, int, int, const int32_t*,
+                               const float*, const QuantParams*, const SplitParams&, TreeArrays, unsigned int*, int, int,
+                               bool, cudaStream_t);
+template void BestSplit<double>(lbk_context*, Scratch&, const GPairI64*, int, int, int, int, int, const int32_t*,
+                                const double*, const QuantParams*, const SplitParams&, TreeArrays, unsigned int*, int, int,
+                                bool, cudaStream_t);
 
 }  // namespace lbk

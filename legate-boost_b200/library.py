@@ -19,7 +19,7 @@ UNIQUE_ID_BYTES = 128
 EXPORTS = [
     "lbk_version", "lbk_context_create", "lbk_context_destroy", "lbk_last_error", "lbk_context_trim",
     "lbk_comm_unique_id", "lbk_comm_init", "lbk_comm_attach_nccl", "lbk_comm_set_callback",
-    "lbk_comm_size", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_sketch_bytes", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
+    "lbk_comm_size", "lbk_owned_features", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_sketch_bytes", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
     "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_histogram_noalloc", "lbk_group_rows",
 ]
 
@@ -112,6 +112,7 @@ def load():
             lib.lbk_comm_init.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
             lib.lbk_comm_attach_nccl.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
             lib.lbk_comm_size.argtypes = [C.c_void_p]
+            lib.lbk_owned_features.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
             lib.lbk_profile_enable.argtypes = [C.c_void_p, C.c_int]
             lib.lbk_profile_histogram_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
             lib.lbk_build_tree.argtypes = [C.c_void_p, C.POINTER(BuildTreeArgs)]
@@ -169,6 +170,16 @@ class Context:
         if self.handle:
             self.lib.lbk_context_destroy(self.handle)
             self.handle = None
+
+
+def owned_features(rank: int, n_ranks: int, n_features: int):
+    """[begin, end) of the features a rank owns when they are divided among the ranks."""
+    lib = load()
+    b, e = C.c_int(0), C.c_int(0)
+    rc = lib.lbk_owned_features(rank, n_ranks, n_features, C.byref(b), C.byref(e))
+    if rc != 0:
+        raise LbkError(rc, lib.lbk_last_error(None).decode())
+    return b.value, e.value
 
 
 def unique_id() -> bytes:

@@ -109,7 +109,7 @@ def histogram(bins, row_ptr, gpair, row_index, seg, n_features, mode=0, hist=Non
     a.stream = _stream_ptr()
     a.host_buffers = 1 if host else 0
     a.max_abs = max_abs.data_ptr() if max_abs is not None else None
-    a.all_reduce = 1 if all_reduce else 0
+    a.all_reduce = int(all_reduce)  # False / True, or 2 = only the owned features are summed
     a.max_bins = int(max_bins)
     a.pairs_by_position = 1 if pairs_by_position else 0
     ctx.check(ctx.lib.lbk_histogram(ctx.handle, C.byref(a)))

@@ -60,3 +60,24 @@ def test_two_ranks_gloo():
     assert np.allclose(l0, np.log(np.array([1, 1, 3]) / 5)) and l0 == l1
     # shards: contiguous, cover everything once
     assert s0[0] == 0 and s0[1] == s1[0] and s1[1] == 1003
+
+
+def test_feature_ownership_covers_every_feature_once():
+    """The division of the features among the ranks (what decides which bins a rank sums and
+    searches): contiguous, in rank order, complete, also with more ranks than features; a pure host
+    function of the C ABI, equal on every rank by construction."""
+    import legateboost_b200 as lb
+
+    for F in (0, 1, 7, 64, 100, 4096):
+        for R in (1, 2, 3, 8, 64):
+            got = [lb.library.owned_features(r, R, F) for r in range(R)]
+            assert got[0][0] == 0 and got[-1][1] == F
+            for (b0, e0), (b1, e1) in zip(got, got[1:]):
+                assert e0 == b1 and b0 <= e0
+            sizes = [e - b for b, e in got]
+            assert max(sizes) - min(sizes) <= 1
+    lib = lb.library.load()
+    import ctypes as C
+
+    b, e = C.c_int(), C.c_int()
+    assert lib.lbk_owned_features(2, 2, 10, C.byref(b), C.byref(e)) == -1   # rank out of range

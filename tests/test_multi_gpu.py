@@ -1,7 +1,8 @@
-"""Multi-GPU parity: every rank holds a contiguous block of rows, the library's NCCL all-reduces
-combine proposals, scale, root sums and per-level histograms, and every rank must end with the
-tree the oracle grows for the same number of simulated ranks (bit-exact).  Skipped with fewer than
-two GPUs."""
+"""Multi-GPU parity: every rank holds a contiguous block of rows, the library's collectives combine
+proposals, scale and root sums, the histograms of a level are summed by feature ownership through
+buffers the GPUs read from each other, the ranks exchange their best split candidates, and every
+rank must end with the tree the oracle grows for the same number of simulated ranks (bit-exact).
+Skipped with fewer than two GPUs."""
 import os
 import socket
 import sys
@@ -20,6 +21,40 @@ def _free_port():
     p = s.getsockname()[1]
     s.close()
     return p
+
+
+def _run(procs, q, world):
+    """Starts the rank processes, collects one result per rank and never leaves a rank behind: a rank
+    that is still alive after the others failed (it waits in a collective) is killed, so that it
+    cannot sit on a GPU under the tests that follow."""
+    import time
+
+    for p in procs:
+        p.start()
+    deadline = time.monotonic() + 240
+    try:
+        res = []
+        for _ in range(world):
+            while True:
+                try:
+                    res.append(q.get(timeout=5))
+                    break
+                except Exception:
+                    if time.monotonic() > deadline:
+                        raise AssertionError("the rank processes did not finish in time")
+                    if any(p.exitcode not in (None, 0) for p in procs):
+                        raise AssertionError("a rank process failed: %s" % [p.exitcode for p in procs])
+                    if all(p.exitcode is not None for p in procs):
+                        raise AssertionError("the rank processes ended without a result")
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+        return res
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
 
 
 def _worker(rank, world, port, case, q):
@@ -84,12 +119,7 @@ def test_two_gpus_match_oracle_with_two_ranks(case):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, world, port, case, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = [q.get(timeout=300) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    res = _run(procs, q, world)
     assert all(ok for _, ok, _ in res), res
     assert res[0][2] > 3
 
@@ -110,24 +140,45 @@ def _hist_worker(rank, world, port, q):
     ctx = lb.library.init_distributed(rank)
     gen = torch.Generator(device=dev)
     gen.manual_seed(100 + rank)
-    N, F, nb, n_nodes = 150000 + 1000 * rank, 128, 256, 128
-    bins = torch.randint(0, nb, (N, F), dtype=torch.uint8, device=dev, generator=gen)
-    row_ptr = torch.arange(F + 1, dtype=torch.int32, device=dev) * nb
-    q_pairs = torch.randint(-5000, 5000, (N, 1, 2), dtype=torch.int32, device=dev, generator=gen)
-    node = torch.randint(0, n_nodes, (N,), dtype=torch.int32, device=dev, generator=gen) + (n_nodes - 1)
-    row_index, seg = stages.group_rows(node, n_nodes - 1, n_nodes)
-    local = stages.histogram(bins, row_ptr, q_pairs, row_index, seg, F, mode=0, ctx=ctx)
-    want = local.clone()
-    dist.all_reduce(want)
-    # large enough (67 MB, 256 tickets) for the all-reduce to travel in parts beside the next part's kernel
-    got = stages.histogram(bins, row_ptr, q_pairs, row_index, seg, F, mode=0, ctx=ctx, all_reduce=True)
-    ok = bool(torch.equal(got, want)) and bool((want != local).any())
+    ok = True
+    # second scenario: the last rank has no rows at all (it must still take part in every collective)
+    for empty_last in (False, True):
+        for mode in (0, 1):
+            empty = empty_last and rank == world - 1
+            N = 1 if empty else 150000 + 1000 * rank
+            F, nb, n_nodes = 128, 256, 128
+            bins = torch.randint(0, nb, (N, F), dtype=torch.uint8, device=dev, generator=gen)
+            row_ptr = torch.arange(F + 1, dtype=torch.int32, device=dev) * nb
+            if mode == 0:
+                pairs = torch.randint(-5000, 5000, (N, 1, 2), dtype=torch.int32, device=dev, generator=gen)
+            else:
+                pairs = torch.randn((N, 1, 2), dtype=torch.float32, device=dev, generator=gen)
+            node = torch.randint(0, n_nodes, (N,), dtype=torch.int32, device=dev, generator=gen) + (n_nodes - 1)
+            if empty:
+                node[:] = 5 * n_nodes  # its one row belongs to no node of the level: nothing to build
+            row_index, seg = stages.group_rows(node, n_nodes - 1, n_nodes)
+            local = stages.histogram(bins, row_ptr, pairs, row_index, seg, F, mode=mode, ctx=ctx)
+            want = local.clone()
+            dist.all_reduce(want)
+            # every bin everywhere
+            got = stages.histogram(bins, row_ptr, pairs, row_index, seg, F, mode=mode, ctx=ctx, all_reduce=1)
+            # only the bins of the features this rank owns
+            own = stages.histogram(bins, row_ptr, pairs, row_index, seg, F, mode=mode, ctx=ctx, all_reduce=2)
+            f0, f1 = lb.library.owned_features(rank, world, F)
+            lo, hi = f0 * nb, f1 * nb
+            if mode == 0:
+                ok = ok and bool(torch.equal(got, want)) and bool(torch.equal(own[:, :, lo:hi], want[:, :, lo:hi]))
+            else:
+                tol = 1e-5 * float(want.abs().max())
+                ok = ok and float((got - want).abs().max()) <= tol
+                ok = ok and float((own[:, :, lo:hi] - want[:, :, lo:hi]).abs().max()) <= tol
+            ok = ok and (empty_last or bool((want != local).any()))  # the other rank really contributed
     q.put((rank, ok))
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_histogram_all_reduce_in_parts_matches_a_plain_all_reduce():
+def test_histogram_sums_over_ranks_match_a_plain_all_reduce():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -137,10 +188,5 @@ def test_histogram_all_reduce_in_parts_matches_a_plain_all_reduce():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_hist_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = [q.get(timeout=300) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    res = _run(procs, q, world)
     assert all(ok for _, ok in res), res
