@@ -116,6 +116,19 @@ def hist_inputs(torch, n_rows, seed, device):
     return bins, row_ptr, gpair, gpair_f, row_index, seg, node, max_abs
 
 
+# DRAM bytes of one k_hist_smem launch as ncu measured them (profiles/k_hist_smem_config2_ncu.md):
+# bytes read per row, and bytes that do not grow with the rows (the output leaving L2 and what the
+# flush buffer left dirty there).  None = no capture of the kernel as it is now: traffic is null.
+HIST_DRAM_BYTES_PER_ROW = None
+HIST_DRAM_BYTES_FIXED = None
+
+
+def hist_traffic(n_rows):
+    if HIST_DRAM_BYTES_PER_ROW is None:
+        return None
+    return n_rows * HIST_DRAM_BYTES_PER_ROW + HIST_DRAM_BYTES_FIXED
+
+
 def algorithmic_bytes(n_rows):
     # per processed row: F bin bytes + 8 (int32 pair) + 4 (row index); per built node: B*16
     return n_rows * (HIST_FEATURES + 8 + 4) + HIST_NODES * HIST_FEATURES * HIST_BINS * 16
@@ -196,6 +209,209 @@ def cpu_hist_sample(n_rows_sample, seed, threads, data=None):
     return n_rows_sample * HIST_FEATURES / dt, dt, kind
 
 
+ROUNDS_TOTAL_ROWS, ROUNDS_FEATURES, ROUNDS_DEPTH = 100_000_000, 64, 8
+PREDICT_TOTAL_ROWS, PREDICT_FEATURES, PREDICT_TREES, PREDICT_DEPTH = 50_000_000, 100, 500, 8
+
+
+def _max_over_ranks(torch, dist, world, device, value):
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def rounds_section(torch, dist, lb, rank, world, device, total_rows, rounds, warmup):
+    """Boosting rounds per second (squared error, depth 8, 256 bins) on the scale-out workload:
+    X uniform[0,1) float32 (total_rows, 64), y = X w + 0.1 N(0,1); the rows are split evenly over
+    the ranks (strong scaling).  Also the histogram kernel's share: its algorithmic bytes over the
+    timed rounds (from the grown trees' node sizes: with unit hessians a node's hessian is its row
+    count; the smaller child of every split is what gets built) against its summed duration."""
+    import ctypes as C
+
+    b, e = shard_rows(total_rows, rank, world)
+    n, F = e - b, ROUNDS_FEATURES
+    gen = torch.Generator(device=device)
+    gen.manual_seed(3 + rank)
+    X = torch.rand((n, F), dtype=torch.float32, device=device, generator=gen)
+    w = torch.randn(F, dtype=torch.float32, device=device, generator=torch.Generator(device=device).manual_seed(3))
+    y = X @ w + 0.1 * torch.randn(n, dtype=torch.float32, device=device, generator=gen)
+    ctx = lb.library.init_distributed(device.index)
+    lib = ctx.lib
+    mk = lambda k: lb.LBRegressor(n_estimators=k, base_models=(lb.Tree(max_depth=ROUNDS_DEPTH),), random_state=0)  # noqa: E731
+    mk(max(warmup, 1)).fit(X, y)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    lib.lbk_profile_enable(ctx.handle, 1)
+    m = mk(rounds)
+    a, bb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    m.fit(X, y)
+    bb.record()
+    torch.cuda.synchronize()
+    ms = _max_over_ranks(torch, dist, world, device, a.elapsed_time(bb))
+    hist_ms, launches = C.c_float(0), C.c_int(0)
+    ctx.check(lib.lbk_profile_histogram_total(ctx.handle, C.byref(hist_ms), C.byref(launches)))
+    hist_ms_max = _max_over_ranks(torch, dist, world, device, hist_ms.value)
+    # algorithmic bytes of the histogram builds of this rank: rows * (F + 8 + 4) + built nodes * B * 16
+    rows_built, nodes_built = 0.0, 0
+    for t in m.models_:
+        feat = t.feature.cpu().numpy()
+        hess = t.hessian.cpu().numpy()[:, 0]
+        rows_built += hess[0]
+        nodes_built += 1
+        split = np.nonzero(feat >= 0)[0]
+        # the children of the splits of levels 0 .. depth-2 are built (the last level is not evaluated)
+        last_eval_begin = 2 ** (ROUNDS_DEPTH - 1) - 1
+        inner = split[split < last_eval_begin]
+        rows_built += np.minimum(hess[2 * inner + 1], hess[2 * inner + 2]).sum()
+        nodes_built += len(inner)
+    bins_total = F * 256
+    alg = rows_built / world * (F + 8 + 4) + nodes_built * bins_total * 16
+    peak, which = measured_peaks()
+    gbs = alg / (hist_ms_max * 1e-3) / 1e9 if hist_ms_max > 0 else 0.0
+    lib.lbk_profile_enable(ctx.handle, 0)
+    del X, y, m
+    torch.cuda.empty_cache()
+    return {"value": rounds / (ms * 1e-3), "unit": "rounds/s", "depth": ROUNDS_DEPTH, "rows": total_rows,
+            "features": F, "rounds": rounds, "ms_per_round": ms / rounds, "scaling": "strong",
+            "hist": {"kernel_ms_per_round": hist_ms_max / rounds, "launches": launches.value, "achieved": gbs,
+                     "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": which}}
+
+
+def predict_section(torch, dist, lb, rank, world, device, total_rows, steps):
+    """Ensemble predict rows per second: 500 random trees of depth 8 (feature uniform, threshold
+    uniform[0,1), leaves N(0,1)) on X uniform[0,1) float32 (total_rows, 100), one output; the rows are
+    split over the ranks, no collective."""
+    from legateboost_b200.tree import predict_arrays
+
+    b, e = shard_rows(total_rows, rank, world)
+    n, F, T, D = e - b, PREDICT_FEATURES, PREDICT_TREES, PREDICT_DEPTH
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4)
+    M = 2 ** (D + 1) - 1
+    trees = []
+    for _ in range(T):
+        feat = torch.randint(0, F, (M,), dtype=torch.int32, device=device, generator=gen)
+        feat[2 ** D - 1:] = -1
+        trees.append((torch.randn((M, 1), dtype=torch.float64, device=device, generator=gen), feat,
+                      torch.rand((M,), dtype=torch.float64, device=device, generator=gen)))
+    gen.manual_seed(40 + rank)
+    X = torch.rand((n, F), dtype=torch.float32, device=device, generator=gen)
+    predict_arrays(X, trees)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, bb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        predict_arrays(X, trees)
+    bb.record()
+    torch.cuda.synchronize()
+    ms = _max_over_ranks(torch, dist, world, device, a.elapsed_time(bb)) / steps
+    peak, which = measured_peaks()
+    gbs = total_rows * (F * 4 + 8) / (ms * 1e-3) / 1e9
+    del X
+    torch.cuda.empty_cache()
+    return {"value": total_rows / (ms * 1e-3), "unit": "rows/s", "rows": total_rows, "features": F, "trees": T,
+            "depth": D, "ms_per_pass": ms, "node_visits_per_s": total_rows * T * D / (ms * 1e-3),
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak * world, "unit": "GB/s",
+                         "frac": gbs / (peak * world), "peak_source": which}}
+
+
+def _ref_cpu_lib():
+    import ctypes as C
+
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_cpu.so")
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
+def cpu_rounds_sample(sample_rows, threads):
+    """The reference's CPU BUILD_TREE + PREDICT (its unmodified build_tree.cc / predict.cc, stub-compiled)
+    for one round of the scale-out workload on a row sample: one rank per host thread, every rank
+    grows a depth-8 tree on its own row shard and predicts it (no collective between them: a lower
+    bound of the distributed round's time).  Returns rounds/s on the sample, or None."""
+    import ctypes as C
+
+    ref = _ref_cpu_lib()
+    if ref is None:
+        return None
+    F, D = ROUNDS_FEATURES, ROUNDS_DEPTH
+    rs = np.random.default_rng(3)
+    X = rs.random((sample_rows, F), dtype=np.float32)
+    w = rs.normal(size=F).astype(np.float32)
+    g = (0.0 - (X @ w + 0.1 * rs.normal(size=sample_rows).astype(np.float32))).astype(np.float64)[:, None]
+    h = np.ones((sample_rows, 1))
+    M = 2 ** (D + 1) - 1
+    times = [0.0] * threads
+    ref.ref_build_tree_cpu.restype = C.c_int
+    ref.ref_predict_cpu.restype = C.c_int
+
+    def work(t):
+        b, e = shard_rows(sample_rows, t, threads)
+        Xs, gs, hs = (np.ascontiguousarray(a[b:e]) for a in (X, g, h))
+        leaf, feat, split, gain, hess = np.zeros((M, 1)), np.zeros(M, dtype=np.int32), np.zeros(M), np.zeros(M), np.zeros((M, 1))
+        pred = np.zeros((e - b, 1))
+        t0 = time.perf_counter()
+        p = lambda a: a.ctypes.data_as(C.c_void_p)  # noqa: E731
+        ref.ref_build_tree_cpu(C.c_int(0), p(Xs), p(gs), p(hs), None, C.c_int64(e - b), C.c_int(F), C.c_int(1), C.c_int(D),
+                               C.c_int(256), C.c_int(7), C.c_double(0.0), C.c_double(1.0), C.c_double(0.0), p(leaf),
+                               p(feat), p(split), p(gain), p(hess))
+        PP = C.c_void_p * 1
+        ref.ref_predict_cpu(C.c_int(0), p(Xs), C.c_int64(e - b), C.c_int(F), C.c_int(1), C.c_int(1), (C.c_int32 * 1)(M),
+                            PP(leaf.ctypes.data), PP(feat.ctypes.data), PP(split.ctypes.data), p(pred))
+        times[t] = time.perf_counter() - t0
+
+    ths = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    return 1.0 / max(times)
+
+
+def cpu_predict_sample(sample_rows, threads):
+    """The reference's CPU PREDICT (predict.cc, stub-compiled) of the 500-tree ensemble on a row sample,
+    one rank per host thread on a row shard.  Returns rows/s, or None."""
+    import ctypes as C
+
+    ref = _ref_cpu_lib()
+    if ref is None:
+        return None
+    F, T, D = PREDICT_FEATURES, PREDICT_TREES, PREDICT_DEPTH
+    rs = np.random.default_rng(4)
+    M = 2 ** (D + 1) - 1
+    leaf = [rs.normal(size=(M, 1)) for _ in range(T)]
+    feat = []
+    for _ in range(T):
+        f = rs.integers(0, F, size=M).astype(np.int32)
+        f[2 ** D - 1:] = -1
+        feat.append(f)
+    split = [rs.random(M) for _ in range(T)]
+    X = rs.random((sample_rows, F), dtype=np.float32)
+    PP = C.c_void_p * T
+    lp, fp, sp = PP(*[a.ctypes.data for a in leaf]), PP(*[a.ctypes.data for a in feat]), PP(*[a.ctypes.data for a in split])
+    mn = (C.c_int32 * T)(*([M] * T))
+    times = [0.0] * threads
+    ref.ref_predict_cpu.restype = C.c_int
+
+    def work(t):
+        b, e = shard_rows(sample_rows, t, threads)
+        Xs = np.ascontiguousarray(X[b:e])
+        pred = np.zeros((e - b, 1))
+        t0 = time.perf_counter()
+        ref.ref_predict_cpu(C.c_int(0), Xs.ctypes.data_as(C.c_void_p), C.c_int64(e - b), C.c_int(F), C.c_int(1), C.c_int(T),
+                            mn, lp, fp, sp, pred.ctypes.data_as(C.c_void_p))
+        times[t] = time.perf_counter() - t0
+
+    ths = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    return sample_rows / max(times)
+
+
 def run_reference(args):
     """Reference arm: the reference's CPU histogram path on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -220,10 +436,27 @@ def run_reference(args):
                                "float64 accumulation on the host" % (sample, HIST_FEATURES, HIST_BINS)},
         "cpu_baseline": {"value": value, "unit": "row-features/s", "cores": threads, "kind": kind,
                          "sample": "%d-row sample of the 10M-row batch per step, %d ranks (threads) on row shards, "
-                                   "time = slowest rank inside ComputeHistogram + in-process sum" % (sample, threads)},
+                                   "time = slowest rank inside ComputeHistogram (which ends with its prefix scan; "
+                                   "the GPU figure is the build alone) + in-process sum; reference sources compiled "
+                                   "with g++ -O2 against the runtime stand-in" % (sample, threads)},
         "e2e": {"value": value, "unit": "row-features/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if not args.no_extra:
+        rows_r, rows_p = 2_000_000, 400_000
+        r = cpu_rounds_sample(rows_r, threads)
+        if r is not None:
+            line["rounds"] = {"value": r, "unit": "rounds/s", "depth": ROUNDS_DEPTH, "rows": rows_r,
+                              "features": ROUNDS_FEATURES,
+                              "sample": "one round (BUILD_TREE + PREDICT of the reference's CPU code) on a %d-row sample of "
+                                        "the 100M x 64 workload, %d ranks (threads) on row shards without a collective; "
+                                        "the work is linear in the rows" % (rows_r, threads)}
+        r = cpu_predict_sample(rows_p, threads)
+        if r is not None:
+            line["predict"] = {"value": r, "unit": "rows/s", "rows": rows_p, "features": PREDICT_FEATURES,
+                               "trees": PREDICT_TREES, "depth": PREDICT_DEPTH,
+                               "sample": "%d-row sample of the 50M x 100 matrix, %d ranks (threads) on row shards"
+                                         % (rows_p, threads)}
     print(json.dumps(line), flush=True)
 
 
@@ -355,10 +588,9 @@ def run_hist(args):
         peak, which = measured_peaks()
         kms = ksum / args.steps
         achieved = algorithmic_bytes(n_rows) / (kms * 1e-3) / 1e9
-        # DRAM traffic of one launch, from the ncu capture of the 2 M-row case summarised in
-        # profiles/k_hist_config2_ncu_full.md (149.9 B read per row; 45.7 MB written, which does not
-        # grow with the rows: the output and what the flush buffer left dirty in L2), scaled by rows
-        traffic = n_rows * 149.9 + 45.7e6 if mode == 0 else None
+        # DRAM traffic of one launch: taken from the ncu capture summarised beside the kernel's profile
+        # (bytes per row and bytes per launch of the case captured there), scaled by the rows
+        traffic = hist_traffic(n_rows) if mode == 0 and world == 1 else None
         line = {
             "metric": "histogram rows*features/s", "value": value, "unit": "row-features/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
@@ -382,7 +614,18 @@ def run_hist(args):
             v, dt, kind = cpu_hist_sample(5_000_000, 7, threads)
             line["cpu_baseline"] = {"value": v, "unit": "row-features/s", "cores": threads, "kind": kind,
                                     "sample": "one 5M-row sample of the batch, %d ranks (threads) on row shards "
-                                              "(%.2f s, %.0f core-seconds)" % (threads, dt, dt * threads)}
+                                              "(%.2f s, %.0f core-seconds); the reference's ComputeHistogram ends with "
+                                              "its prefix scan (the GPU figure is the build alone); sources compiled "
+                                              "with g++ -O2 against the runtime stand-in" % (threads, dt, dt * threads)}
+    # the other two metrics of the path, on their own workloads (every rank takes part)
+    extra = {}
+    if not args.no_extra:
+        del bins, gpair, gpair_f, gp, gp_by_row, row_index, seg, node, hist, flush
+        torch.cuda.empty_cache()
+        extra["rounds"] = rounds_section(torch, dist, lb, rank, world, device, args.rounds_rows, args.rounds, 1)
+        extra["predict"] = predict_section(torch, dist, lb, rank, world, device, args.predict_rows, 2)
+    if rank == 0:
+        line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -535,6 +778,11 @@ def main():
     ap.add_argument("--pairs-by-row", action="store_true",
                     help="hist workload: gradient pairs indexed by row id (gathered) instead of stored in "
                          "row_index order")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="hist workload: leave the rounds/s and predict rows/s sections out of the line")
+    ap.add_argument("--rounds-rows", type=int, default=ROUNDS_TOTAL_ROWS)
+    ap.add_argument("--rounds", type=int, default=3)
+    ap.add_argument("--predict-rows", type=int, default=PREDICT_TOTAL_ROWS)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -53,6 +53,26 @@ const char* lbk_last_error(const lbk_context* ctx);
 /* Release cached scratch memory back to the driver. */
 int lbk_context_trim(lbk_context* ctx);
 
+/* Scratch from the caller's allocator instead of the context's own pool (reference: every scratch
+ * buffer of the task bodies is a legate::create_buffer, e.g. build_tree.cu:785-809, which is why the
+ * variants are registered with_has_allocations(true), build_tree.h:308-317): a runtime that has
+ * reserved the GPU's memory wants the binned matrix, the quantised pairs and the row lists of a tree
+ * (13 GB at 100M x 64) inside that reservation.
+ *   alloc(user, bytes, stream) returns device memory (256-byte aligned) that work queued on `stream`
+ *     after the call may use, or NULL (the library then fails with LBK_ERR_ALLOC);
+ *   release(user, ptr, stream) is called once per allocation after the library has queued its last
+ *     use of it on `stream`: the memory may be handed out again for work that is ordered after what
+ *     `stream` holds at that moment (what cudaFreeAsync, torch's caching allocator and a buffer that
+ *     lives until the end of the task all provide).
+ * Both are called on the thread that calls into the library.  NULL for both restores the pool.  The
+ * buffers that other ranks' GPUs map (multi-rank calls, see lbk_histogram_args.all_reduce) are not
+ * scratch of one call and stay with the library. */
+typedef void* (*lbk_alloc_fn)(void* user, size_t bytes, void* stream);
+typedef void (*lbk_release_fn)(void* user, void* ptr, void* stream);
+int lbk_context_set_allocator(lbk_context* ctx, lbk_alloc_fn alloc, lbk_release_fn release, void* user);
+/* Bytes the context's own pool holds at the moment (reserved from the driver, in use or cached). */
+int lbk_context_pool_bytes(lbk_context* ctx, size_t* reserved);
+
 /* Communicator (reference: the ncclComm_t* the runtime hands to the task, cpp_utils.cuh:100-134).
  * Either create one from an id that rank 0 made and every rank received out of band ... */
 #define LBK_UNIQUE_ID_BYTES 128
@@ -76,6 +96,9 @@ int lbk_owned_features(int rank, int n_ranks, int n_features, int* begin, int* e
  * caller's stream; lbk_profile_histogram_ms returns the duration of the most recent one. */
 int lbk_profile_enable(lbk_context* ctx, int on);
 int lbk_profile_histogram_ms(lbk_context* ctx, float* ms);
+/* The sum over all histogram launches since the last call of this function (or since the timing was
+ * enabled) and their number; starts a new sum.  Waits for the launches to finish. */
+int lbk_profile_histogram_total(lbk_context* ctx, float* ms, int* launches);
 
 /* ------------------------------------------------------------------------------------------
  * BUILD_TREE.  Field order follows the task's argument order (legateboost/models/tree.py:117-183,

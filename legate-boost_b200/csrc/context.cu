@@ -86,19 +86,33 @@ int nccl_op(lbk_redop o) { return o == LBK_SUM ? 0 : 2; }  // ncclSum, ncclMax
 
 namespace lbk {
 
+// An allocation goes back the way it came: the allocator is fixed for the lifetime of a Scratch
+// (lbk_context_set_allocator is not to be called while a call is in progress on the context).
+static void ReleaseScratch(lbk_context* ctx, void* p, cudaStream_t stream)
+{
+  if (ctx->release_cb != nullptr) ctx->release_cb(ctx->alloc_user, p, stream);
+  else cudaFreeAsync(p, stream);
+}
+
 Scratch::~Scratch()
 {
   for (void* p : ptrs_)
-    if (p) cudaFreeAsync(p, stream_);
+    if (p) ReleaseScratch(ctx_, p, stream_);
 }
 
 void* Scratch::alloc_bytes(size_t bytes)
 {
-  void* p       = nullptr;
-  cudaError_t e = cudaMallocFromPoolAsync(&p, bytes > 0 ? bytes : 16, ctx_->pool, stream_);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    throw Error(LBK_ERR_ALLOC, "scratch allocation of " + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e));
+  void* p = nullptr;
+  if (ctx_->alloc_cb != nullptr) {
+    p = ctx_->alloc_cb(ctx_->alloc_user, bytes > 0 ? bytes : 16, stream_);
+    if (p == nullptr)
+      throw Error(LBK_ERR_ALLOC, "the caller's allocator returned no memory for " + std::to_string(bytes) + " bytes of scratch");
+  } else {
+    cudaError_t e = cudaMallocFromPoolAsync(&p, bytes > 0 ? bytes : 16, ctx_->pool, stream_);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      throw Error(LBK_ERR_ALLOC, "scratch allocation of " + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e));
+    }
   }
   ptrs_.push_back(p);
   return p;
@@ -108,7 +122,7 @@ void Scratch::free_one(void* p)
 {
   for (auto& q : ptrs_)
     if (q == p) {
-      cudaFreeAsync(q, stream_);
+      ReleaseScratch(ctx_, q, stream_);
       q = nullptr;
     }
 }
@@ -133,6 +147,19 @@ bool AllGatherBytes(lbk_context* ctx, const void* send, void* recv, size_t bytes
   if (nccl().AllGather == nullptr) return false;
   nccl_check(nccl().AllGather(send, recv, bytes, 0 /* ncclInt8 */, ctx->nccl_comm, stream), "ncclAllGather");
   return true;
+}
+
+std::pair<cudaEvent_t, cudaEvent_t> NextProfileEvents(lbk_context* ctx)
+{
+  constexpr size_t kMaxProfiledLaunches = 4096;
+  if (ctx->prof_used < ctx->prof_events.size()) return ctx->prof_events[ctx->prof_used++];
+  if (ctx->prof_events.size() >= kMaxProfiledLaunches) return ctx->prof_events.back();
+  std::pair<cudaEvent_t, cudaEvent_t> ev{nullptr, nullptr};
+  LBK_CUDA(cudaEventCreate(&ev.first));
+  LBK_CUDA(cudaEventCreate(&ev.second));
+  ctx->prof_events.push_back(ev);
+  ctx->prof_used = ctx->prof_events.size();
+  return ev;
 }
 
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream)
@@ -208,8 +235,10 @@ void lbk_context_destroy(lbk_context* ctx)
   if (ctx->owns_nccl && ctx->nccl_comm && nccl().CommDestroy) nccl().CommDestroy(ctx->nccl_comm);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->pool) cudaMemPoolDestroy(ctx->pool);
-  if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
-  if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
+  for (auto& ev : ctx->prof_events) {
+    cudaEventDestroy(ev.first);
+    cudaEventDestroy(ev.second);
+  }
   delete ctx;
 }
 
@@ -222,6 +251,28 @@ int lbk_context_trim(lbk_context* ctx)
     LBK_CUDA(cudaSetDevice(ctx->device));
     LBK_CUDA(cudaDeviceSynchronize());
     LBK_CUDA(cudaMemPoolTrimTo(ctx->pool, 0));
+  });
+}
+
+int lbk_context_set_allocator(lbk_context* ctx, lbk_alloc_fn alloc, lbk_release_fn release, void* user)
+{
+  return lbk::Guard(ctx, [&] {
+    LBK_EXPECT(ctx != nullptr, "context is null");
+    LBK_EXPECT((alloc == nullptr) == (release == nullptr), "give both callbacks or neither");
+    ctx->alloc_cb   = alloc;
+    ctx->release_cb = release;
+    ctx->alloc_user = user;
+  });
+}
+
+int lbk_context_pool_bytes(lbk_context* ctx, size_t* reserved)
+{
+  return lbk::Guard(ctx, [&] {
+    LBK_EXPECT(ctx && reserved, "null argument");
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    uint64_t v = 0;
+    LBK_CUDA(cudaMemPoolGetAttribute(ctx->pool, cudaMemPoolAttrReservedMemCurrent, &v));
+    *reserved = static_cast<size_t>(v);
   });
 }
 
@@ -300,13 +351,8 @@ int lbk_profile_enable(lbk_context* ctx, int on)
 {
   return lbk::Guard(ctx, [&] {
     LBK_EXPECT(ctx != nullptr, "context is null");
-    LBK_CUDA(cudaSetDevice(ctx->device));
-    if (on && !ctx->ev_start) {
-      LBK_CUDA(cudaEventCreate(&ctx->ev_start));
-      LBK_CUDA(cudaEventCreate(&ctx->ev_stop));
-    }
-    ctx->profile          = on != 0;
-    ctx->profile_recorded = false;
+    ctx->profile   = on != 0;
+    ctx->prof_used = 0;
   });
 }
 
@@ -314,9 +360,30 @@ int lbk_profile_histogram_ms(lbk_context* ctx, float* ms)
 {
   return lbk::Guard(ctx, [&] {
     LBK_EXPECT(ctx && ms, "null argument");
-    LBK_EXPECT(ctx->profile && ctx->profile_recorded, "no histogram launch has been timed");
-    LBK_CUDA(cudaEventSynchronize(ctx->ev_stop));
-    LBK_CUDA(cudaEventElapsedTime(ms, ctx->ev_start, ctx->ev_stop));
+    LBK_EXPECT(ctx->profile && ctx->prof_used > 0, "no histogram launch has been timed");
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    const auto& ev = ctx->prof_events[ctx->prof_used - 1];
+    LBK_CUDA(cudaEventSynchronize(ev.second));
+    LBK_CUDA(cudaEventElapsedTime(ms, ev.first, ev.second));
+  });
+}
+
+int lbk_profile_histogram_total(lbk_context* ctx, float* ms, int* launches)
+{
+  return lbk::Guard(ctx, [&] {
+    LBK_EXPECT(ctx && ms && launches, "null argument");
+    LBK_EXPECT(ctx->profile, "the histogram timing is not enabled");
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    float total = 0.f;
+    for (size_t i = 0; i < ctx->prof_used; ++i) {
+      float t = 0.f;
+      LBK_CUDA(cudaEventSynchronize(ctx->prof_events[i].second));
+      LBK_CUDA(cudaEventElapsedTime(&t, ctx->prof_events[i].first, ctx->prof_events[i].second));
+      total += t;
+    }
+    *ms            = total;
+    *launches      = static_cast<int>(ctx->prof_used);
+    ctx->prof_used = 0;
   });
 }
 

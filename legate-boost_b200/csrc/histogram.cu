@@ -997,13 +997,14 @@ void BuildHistogram(lbk_context* ctx, Scratch& s, const HistLevel& lv, cudaStrea
                                       lv.float_mode ? nullptr : max_abs, slot_capacity, chunk_off, wpre, p.arrive,
                                       n_arrive, plan, p.ticket);
   LBK_LAUNCH_CHECK();
-  if (ctx->profile) LBK_CUDA(cudaEventRecord(ctx->ev_start, stream));
+  std::pair<cudaEvent_t, cudaEvent_t> ev{nullptr, nullptr};
+  if (ctx->profile) {
+    ev = NextProfileEvents(ctx);
+    LBK_CUDA(cudaEventRecord(ev.first, stream));
+  }
   hl.fn<<<hl.grid, hl.threads, hl.smem, stream>>>(p);
   LBK_LAUNCH_CHECK();
-  if (ctx->profile) {
-    LBK_CUDA(cudaEventRecord(ctx->ev_stop, stream));
-    ctx->profile_recorded = true;
-  }
+  if (ctx->profile) LBK_CUDA(cudaEventRecord(ev.second, stream));
   // stream ordered: the slots go back to the pool once the kernel has run
   if (p.partial) s.free_one(p.partial);
 }

@@ -6,6 +6,7 @@
 #include <functional>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "lbk.h"
@@ -66,6 +67,10 @@ struct lbk_context {
   int sm_count      = 0;
   int max_smem_optin = 0;
   cudaMemPool_t pool = nullptr;
+  // the caller's allocator for scratch (both set or both null)
+  lbk_alloc_fn alloc_cb     = nullptr;
+  lbk_release_fn release_cb = nullptr;
+  void* alloc_user          = nullptr;
   std::string err;
   // device status word: 0 = ok, otherwise a kernel wrote a fault code
   int* d_status = nullptr;
@@ -79,8 +84,8 @@ struct lbk_context {
   lbk::PeerExchange* xchg = nullptr;
   // optional timing of the histogram kernel alone (events on the caller's stream)
   bool profile            = false;
-  cudaEvent_t ev_start    = nullptr, ev_stop = nullptr;
-  bool profile_recorded   = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;  // one pair per timed launch since the last total
+  size_t prof_used        = 0;
 };
 
 namespace lbk {
@@ -145,6 +150,9 @@ void ExchangeReducePushed(lbk_context* ctx, void* dst, int n_seg, int push_len, 
 // Includes a barrier.
 void ExchangeGatherAll(lbk_context* ctx, void* buf, void* dst, int n_seg, int B, int F, const int32_t* row_ptr,
                        cudaStream_t stream);
+// The event pair that brackets the next timed histogram launch (profile mode): the first that is
+// free, made on demand; when kMaxProfiledLaunches are in use the last one is used again.
+std::pair<cudaEvent_t, cudaEvent_t> NextProfileEvents(lbk_context* ctx);
 // Reads the device status word (synchronises the stream) and throws LBK_ERR_DEVICE if set.
 void CheckDeviceStatus(lbk_context* ctx, cudaStream_t stream);
 

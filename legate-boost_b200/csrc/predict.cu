@@ -197,7 +197,7 @@ __global__ void k_pack_complete(const TreePtrs* __restrict__ trees, int K, int F
 
 // Tiled kernel.  Shared memory: X tile [F][RB] | accumulators [K][RB] (K > 1) |
 // NBUF x TG x slot, slot = NI nodes (+ NL leaf values when K == 1).
-template <typename T, int RB, int TG>
+template <typename T, int RB, int TG, bool kLeafShared>
 __global__ void __launch_bounds__(RB)
   k_predict_tiled(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
                   const typename NodeOf<T>::type* __restrict__ nodes_c, const double* __restrict__ leaves_c,
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(RB)
   off += K > 1 ? sizeof(double) * static_cast<size_t>(K) * RB : 0;
   // a group buffer: the nodes of its TG trees, then (K == 1) their bottom-level values
   const unsigned node_bytes = static_cast<unsigned>(NI * sizeof(NodeT));
-  const unsigned leaf_bytes = K == 1 ? static_cast<unsigned>(NL * sizeof(double)) : 0u;
+  const unsigned leaf_bytes = kLeafShared ? static_cast<unsigned>(NL * sizeof(double)) : 0u;
   const unsigned buf_bytes  = TG * (node_bytes + leaf_bytes);
   unsigned char* tree_s     = smem_raw + off;
 
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(RB)
     const unsigned dst = tree0 + static_cast<unsigned>(buf) * buf_bytes;
     MbarExpectTx(bar, nt * (node_bytes + leaf_bytes));
     BulkCopy(dst, nodes_c + static_cast<int64_t>(t0) * NI, nt * node_bytes, bar);
-    if (K == 1) BulkCopy(dst + TG * node_bytes, leaves_c + static_cast<int64_t>(t0) * NL, nt * leaf_bytes, bar);
+    if (kLeafShared) BulkCopy(dst + TG * node_bytes, leaves_c + static_cast<int64_t>(t0) * NL, nt * leaf_bytes, bar);
   };
   stage_group(0, 0);
 
@@ -287,31 +287,42 @@ __global__ void __launch_bounds__(RB)
 #pragma unroll
       for (int j = 0; j < TG; ++j) p8[j] = 0;
       if (nt == TG) {
+        // a step of all TG walks: first every node load, then every x load, then the compares, so
+        // that the loads of the independent walks are in flight together (the loads are volatile
+        // and keep their order: interleaved per walk they would run one after the other)
         for (int step = 0; step < S; ++step) {
+          T split[TG];
+          int foff[TG];
+          T x[TG];
 #pragma unroll
-          for (int j = 0; j < TG; ++j) {
-            T split;
-            int foff;
-            LdsNode(gbase + j * node_bytes + (p8[j] << kNodeShift), split, foff);
-            const T x = LdsX(xcol_s + foff, T());
-            p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
-          }
+          for (int j = 0; j < TG; ++j) LdsNode(gbase + j * node_bytes + (p8[j] << kNodeShift), split[j], foff[j]);
+#pragma unroll
+          for (int j = 0; j < TG; ++j) x[j] = LdsX(xcol_s + foff[j], T());
+#pragma unroll
+          for (int j = 0; j < TG; ++j) p8[j] = 2 * p8[j] + (x[j] <= split[j] ? 8u : 16u);
         }
       } else {
+        // (the last, partial group: the same unrolled steps under a predicate, so that p8 stays in
+        // registers)
         for (int step = 0; step < S; ++step) {
-          for (int j = 0; j < nt; ++j) {
-            T split;
-            int foff;
-            LdsNode(gbase + j * node_bytes + (p8[j] << kNodeShift), split, foff);
-            const T x = LdsX(xcol_s + foff, T());
-            p8[j]     = 2 * p8[j] + (x <= split ? 8u : 16u);
-          }
+          T split[TG];
+          int foff[TG];
+          T x[TG];
+#pragma unroll
+          for (int j = 0; j < TG; ++j)
+            if (j < nt) LdsNode(gbase + j * node_bytes + (p8[j] << kNodeShift), split[j], foff[j]);
+#pragma unroll
+          for (int j = 0; j < TG; ++j)
+            if (j < nt) x[j] = LdsX(xcol_s + foff[j], T());
+#pragma unroll
+          for (int j = 0; j < TG; ++j)
+            if (j < nt) p8[j] = 2 * p8[j] + (x[j] <= split[j] ? 8u : 16u);
         }
       }
 #pragma unroll
       for (int j = 0; j < TG; ++j) {
         if (j < nt) {
-          if (K == 1) {
+          if (kLeafShared) {
             acc0 += LdsF64(gbase + j * leaf_bytes + leaf_adj + p8[j]);
           } else {
             const int64_t lj = static_cast<int64_t>(g * TG + j) * NL + ((p8[j] >> 3) - ((1u << S) - 1u));
@@ -360,25 +371,25 @@ __global__ void __launch_bounds__(128)
 }
 
 template <typename T>
-size_t TiledSmem(int rb, int tg, int nbuf, int F, int K, int NI, int NL)
+size_t TiledSmem(int rb, int tg, int nbuf, int F, int K, int NI, int NL, bool leaf_shared)
 {
   using NodeT = typename NodeOf<T>::type;
   const size_t x_bytes    = (sizeof(T) * static_cast<size_t>(F) * rb + 15) / 16 * 16;
   const size_t a_bytes    = K > 1 ? sizeof(double) * static_cast<size_t>(K) * rb : 0;
-  const size_t slot_bytes = static_cast<size_t>(NI) * sizeof(NodeT) + (K == 1 ? static_cast<size_t>(NL) * sizeof(double) : 0);
+  const size_t slot_bytes = static_cast<size_t>(NI) * sizeof(NodeT) + (leaf_shared ? static_cast<size_t>(NL) * sizeof(double) : 0);
   return x_bytes + a_bytes + static_cast<size_t>(nbuf) * tg * slot_bytes;
 }
 
-template <typename T, int RB, int TG>
+template <typename T, int RB, int TG, bool kLeafShared>
 void LaunchTiled(const T* X, int64_t ldx, int64_t n_rows, int F, int K, int n_trees,
                  const typename NodeOf<T>::type* nodes_c, const double* leaves_c, double* pred, int64_t ldp, int S,
                  int NI, int NL, size_t smem, int* status, cudaStream_t stream)
 {
   if (smem > 48 * 1024)
-    LBK_CUDA(cudaFuncSetAttribute(k_predict_tiled<T, RB, TG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    LBK_CUDA(cudaFuncSetAttribute(k_predict_tiled<T, RB, TG, kLeafShared>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem)));
   const unsigned grid = static_cast<unsigned>((n_rows + RB - 1) / RB);
-  k_predict_tiled<T, RB, TG><<<grid, RB, smem, stream>>>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S,
+  k_predict_tiled<T, RB, TG, kLeafShared><<<grid, RB, smem, stream>>>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S,
                                                           NI, NL, status);
   LBK_LAUNCH_CHECK();
 }
@@ -416,24 +427,26 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
   const int NI = (1 << S) > 2 ? (1 << S) : 2;  // internal nodes 2^S - 1, padded to a 16-byte multiple
   const int NL = NI;                           // bottom level 2^S values, same padding
 
-  // tile shape: rows per block RB, trees per group TG, one or two group buffers
+  // tile shape: rows per block RB, trees per group TG, one or two group buffers.  (Measured at 5 M x
+  // 100, 500 trees of depth 8: groups of 8 trees 14.8 ms; groups of 16 with the bottom-level values
+  // left in global memory 29.8 ms; groups of 4 27.3 ms.)
   const size_t budget = static_cast<size_t>(ctx->max_smem_optin) - 1024;
   int rb = 0, tg = 0;
+  const bool leaf_shared = K == 1;
   size_t smem = 0;
   if (S <= 14) {
     const int rbs[4] = {256, 128, 64, 32};
     const int tgs[4] = {8, 4, 2, 1};
     for (int ri = 0; ri < 4 && rb == 0; ++ri) {
       if (static_cast<int64_t>(F) * rbs[ri] * static_cast<int64_t>(sizeof(T)) >= (int64_t{1} << 30)) continue;
-      for (int ti = 0; ti < 4; ++ti) {
+      for (int ti = 0; ti < 4 && rb == 0; ++ti) {
         if (tgs[ti] > n_trees && tgs[ti] > 1) continue;  // no wider than the ensemble
         const int nbuf = n_trees > tgs[ti] ? 2 : 1;
-        const size_t need = TiledSmem<T>(rbs[ri], tgs[ti], nbuf, F, K, NI, NL);
+        const size_t need = TiledSmem<T>(rbs[ri], tgs[ti], nbuf, F, K, NI, NL, leaf_shared);
         if (need <= budget) {
           rb   = rbs[ri];
           tg   = tgs[ti];
           smem = need;
-          break;
         }
       }
     }
@@ -458,13 +471,15 @@ void PredictLaunch(lbk_context* ctx, Scratch& s, const T* X, int64_t ldx, int64_
   k_pack_complete<NodeT><<<n_trees, 256, 0, stream>>>(d_trees, K, F, rb * static_cast<int>(sizeof(T)), S, NI, NL,
                                                       nodes_c, leaves_c);
   LBK_LAUNCH_CHECK();
-#define LBK_PREDICT_CASE(RB_, TG_)                                                                                  \
-  if (rb == RB_ && tg == TG_) {                                                                                     \
-    LaunchTiled<T, RB_, TG_>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S, NI, NL, smem,          \
-                             ctx->d_status, stream);                                                                \
+#define LBK_PREDICT_CASE(RB_, TG_, LS_)                                                                             \
+  if (rb == RB_ && tg == TG_ && leaf_shared == LS_) {                                                               \
+    LaunchTiled<T, RB_, TG_, LS_>(X, ldx, n_rows, F, K, n_trees, nodes_c, leaves_c, pred, ldp, S, NI, NL, smem,     \
+                                  ctx->d_status, stream);                                                           \
     return;                                                                                                         \
   }
-#define LBK_PREDICT_ROW(RB_) LBK_PREDICT_CASE(RB_, 8) LBK_PREDICT_CASE(RB_, 4) LBK_PREDICT_CASE(RB_, 2) LBK_PREDICT_CASE(RB_, 1)
+#define LBK_PREDICT_ROW(RB_)                                                                                        \
+  LBK_PREDICT_CASE(RB_, 8, true) LBK_PREDICT_CASE(RB_, 4, true) LBK_PREDICT_CASE(RB_, 2, true) LBK_PREDICT_CASE(RB_, 1, true) \
+  LBK_PREDICT_CASE(RB_, 8, false) LBK_PREDICT_CASE(RB_, 4, false) LBK_PREDICT_CASE(RB_, 2, false) LBK_PREDICT_CASE(RB_, 1, false)
   LBK_PREDICT_ROW(256)
   LBK_PREDICT_ROW(128)
   LBK_PREDICT_ROW(64)

@@ -18,10 +18,15 @@ UNIQUE_ID_BYTES = 128
 #: every symbol include/lbk.h declares
 EXPORTS = [
     "lbk_version", "lbk_context_create", "lbk_context_destroy", "lbk_last_error", "lbk_context_trim",
+    "lbk_context_set_allocator", "lbk_context_pool_bytes",
     "lbk_comm_unique_id", "lbk_comm_init", "lbk_comm_attach_nccl", "lbk_comm_set_callback",
-    "lbk_comm_size", "lbk_owned_features", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_build_tree", "lbk_sketch_bytes", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
+    "lbk_comm_size", "lbk_owned_features", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_profile_histogram_total", "lbk_build_tree", "lbk_sketch_bytes", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
     "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_histogram_noalloc", "lbk_group_rows",
 ]
+
+
+ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p)
+RELEASE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_void_p)
 
 
 class LbkError(RuntimeError):
@@ -108,6 +113,8 @@ def load():
             lib.lbk_last_error.argtypes = [C.c_void_p]
             lib.lbk_last_error.restype = C.c_char_p
             lib.lbk_context_trim.argtypes = [C.c_void_p]
+            lib.lbk_context_set_allocator.argtypes = [C.c_void_p, ALLOC_FN, RELEASE_FN, C.c_void_p]
+            lib.lbk_context_pool_bytes.argtypes = [C.c_void_p, C.POINTER(C.c_size_t)]
             lib.lbk_comm_unique_id.argtypes = [C.c_void_p]
             lib.lbk_comm_init.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
             lib.lbk_comm_attach_nccl.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
@@ -115,6 +122,7 @@ def load():
             lib.lbk_owned_features.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
             lib.lbk_profile_enable.argtypes = [C.c_void_p, C.c_int]
             lib.lbk_profile_histogram_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
+            lib.lbk_profile_histogram_total.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]
             lib.lbk_build_tree.argtypes = [C.c_void_p, C.POINTER(BuildTreeArgs)]
             lib.lbk_predict.argtypes = [C.c_void_p, C.POINTER(PredictArgs)]
             lib.lbk_histogram.argtypes = [C.c_void_p, C.POINTER(HistogramArgs)]
@@ -165,6 +173,39 @@ class Context:
         buf = C.create_string_buffer(id_bytes, UNIQUE_ID_BYTES)
         self.check(self.lib.lbk_comm_init(self.handle, buf, rank, n_ranks))
         self.rank, self.n_ranks = rank, n_ranks
+
+    def use_torch_allocator(self, on=True):
+        """Route the library's scratch through torch's caching allocator (``lbk_context_set_allocator``):
+        every allocation is a uint8 tensor made on the current stream and kept until the library gives
+        it back.  ``on=False`` restores the context's own pool."""
+        import torch
+
+        if not on:
+            self.check(self.lib.lbk_context_set_allocator(self.handle, ALLOC_FN(0), RELEASE_FN(0), None))
+            self._held, self._cbs = {}, None
+            return
+        held = {}
+        device = torch.device("cuda", self.device)
+
+        def alloc(user, nbytes, stream):
+            try:
+                t = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+            except RuntimeError:
+                return None
+            held[t.data_ptr()] = t
+            return t.data_ptr()
+
+        def release(user, ptr, stream):
+            held.pop(ptr, None)
+
+        self._held = held
+        self._cbs = (ALLOC_FN(alloc), RELEASE_FN(release))  # keep the trampolines alive
+        self.check(self.lib.lbk_context_set_allocator(self.handle, self._cbs[0], self._cbs[1], None))
+
+    def pool_bytes(self) -> int:
+        v = C.c_size_t(0)
+        self.check(self.lib.lbk_context_pool_bytes(self.handle, C.byref(v)))
+        return v.value
 
     def close(self):
         if self.handle:

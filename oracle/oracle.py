@@ -16,11 +16,16 @@ _LIB = None
 _REF = None
 
 
-def build(ref: bool = False) -> None:
-    """Compile the oracle (and, if asked and the reference tree exists, the reference CPU build)."""
+def build(ref: bool = False, reference_dir: str = None) -> None:
+    """Compile the oracle (and, if asked and the reference tree exists, the reference's CPU and GPU
+    builds against the runtime stand-in; ``reference_dir`` = where the reference's sources lie,
+    default: the REFERENCE_DIR variable or a folder named "reference" beside the repository)."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
     if ref:
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+        if reference_dir is None:
+            reference_dir = os.environ.get("REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)),
+                                                                            "reference")
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "ref_gpu", "REFERENCE_DIR=" + reference_dir])
 
 
 class _TreeArgs(C.Structure):

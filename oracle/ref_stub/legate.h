@@ -187,6 +187,14 @@ struct AccessorBase {
     for (int d = 0; d < N; ++d) off += (p[d] - origin[d]) * stride[d];
     return base[off];
   }
+  // address of one element, and of the first element of a rectangle together with the strides (in
+  // elements) of its dimensions: what an adapter needs to hand a store to a C library
+  T* ptr(const Point<N>& p) const { return &at(p); }
+  T* ptr(const Rect<N>& r, std::size_t* strides) const
+  {
+    for (int d = 0; d < N; ++d) strides[d] = static_cast<std::size_t>(stride[d]);
+    return &at(r.lo);
+  }
 };
 template <typename T, int N>
 struct AccessorRO : AccessorBase<const T, N> {
@@ -277,6 +285,9 @@ class Scalar {
 struct Domain {
   std::size_t get_volume() const { return 1; }
 };
+struct DomainPoint {
+  long long operator[](int) const { return 0; }
+};
 struct Communicator {
   template <typename T>
   T get() const
@@ -299,6 +310,7 @@ class TaskContext {
   const std::vector<Scalar>& scalars() const { return st->scalars; }
   const Scalar& scalar(std::size_t i) const { return st->scalars.at(i); }
   Domain get_launch_domain() const { return {}; }
+  DomainPoint get_task_index() const { return {}; }
   std::size_t num_communicators() const { return 0; }
   Communicator communicator(int) const { return {}; }
 #if defined(__CUDACC__)

@@ -76,3 +76,23 @@ def test_seed_and_feature_draw_order():
     choice = rs.choice(10, 5, False)
     rs2 = np.random.RandomState(5)
     assert rs2.randint(0, 2 ** 31) == seed and np.array_equal(rs2.choice(10, 5, False), choice)
+
+
+def test_legate_adapter_compiles_against_the_runtime_stand_in(tmp_path):
+    """adapter/legate_adapter.cu - the bodies a maintainer puts behind BuildTreeTask::gpu_variant and
+    PredictTask::gpu_variant - is real source: it compiles (nvcc, host and device pass) against
+    include/lbk.h and the stand-in of the legate headers that the reference's own task bodies are
+    compiled against here.  No legate runtime exists in this image, so it cannot be run."""
+    import shutil
+    import subprocess
+
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc")
+    out = tmp_path / "legate_adapter.o"
+    cmd = [nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-c",
+           os.path.join(ROOT, "adapter", "legate_adapter.cu"), "-I", os.path.join(ROOT, "include"),
+           "-I", os.path.join(ROOT, "oracle", "ref_stub"), "-o", str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert out.stat().st_size > 0

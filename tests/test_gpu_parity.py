@@ -266,6 +266,35 @@ def test_build_tree_histograms_bit_exact(lb, oracle):
         assert np.array_equal(got["feature"].cpu().numpy(), want.feature)
 
 
+def test_scratch_through_the_callers_allocator(lb):
+    """lbk_context_set_allocator: with torch's caching allocator behind the callbacks a whole tree is
+    built without the library's own pool reserving a byte, and it is the same tree."""
+    from legateboost_b200.tree import build_tree_arrays
+
+    N, F, K, D = 50000, 40, 2, 6
+    rs = np.random.RandomState(3)
+    X, g, h = dev(rs.random((N, F)).astype(np.float32)), dev(rs.normal(size=(N, K))), dev(rs.random((N, K)) + 0.1)
+    kw = dict(max_depth=D, split_samples=256, seed=9, row_offset=0, dataset_rows=N, want_leaf=True)
+    want = build_tree_arrays(X, g, h, **kw)
+    ctx = lb.library.context(X.device.index)
+    torch.cuda.synchronize()
+    ctx.check(ctx.lib.lbk_context_trim(ctx.handle))
+    assert ctx.pool_bytes() == 0
+    ctx.use_torch_allocator(True)
+    try:
+        got = build_tree_arrays(X, g, h, **kw)
+        torch.cuda.synchronize()
+        assert ctx.pool_bytes() == 0
+        assert len(ctx._held) == 0  # everything was given back
+    finally:
+        ctx.use_torch_allocator(False)
+    for name in ("feature", "split_value", "gain", "leaf_value", "hessian", "leaf"):
+        assert torch.equal(got[name], want[name]), name
+    # the pool is in use again afterwards
+    build_tree_arrays(X, g, h, **kw)
+    assert ctx.pool_bytes() > 0
+
+
 def test_fixed_sketch_save_and_reuse(lb, oracle):
     """The optional sketch buffer: a saving call gives the oracle's tree, a reusing call with the same
     seed gives it again without reading X, a reusing call with another seed splits on the saved
