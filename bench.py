@@ -607,6 +607,19 @@ def run_hist(args):
                          "traffic": traffic, "peak_source": which, "kernel": "k_hist_smem", "kernel_ms": kms},
             "clocks": clocks, "e2e": e2e, "gpu_launches": (3 if world == 1 else 5) * args.steps,
         }
+        # The kernel's other bound is the SM's load/store pipe: one shared-memory reduction instruction
+        # (32 lanes, 32 different banks by construction of the layout) per 32 updates of a gradient
+        # or hessian word, and the pipe retires at most one such pass per clock.  Rate = passes per
+        # SM clock per SM over the kernel time, at the SM clock sampled under load.
+        sm_mhz = clocks.get("sm_mhz") if isinstance(clocks, dict) else None
+        if sm_mhz:
+            passes = n_rows * HIST_FEATURES * 2 / 32
+            sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+            rate = passes / (kms * 1e-3 * sm_mhz * 1e6 * sm_count)
+            line["shared_atomics"] = {"updates_per_s": n_rows * HIST_FEATURES * 2 / (kms * 1e-3),
+                                      "passes_per_clk_per_sm": rate, "peak": 1.0, "frac": rate,
+                                      "note": "red.shared.add.s32 passes of 32 lanes; peak = one pass per clock per "
+                                              "SM on the load/store pipe, which the row gathers share"}
         if allreduce_check is not None:
             line["allreduce_check"] = allreduce_check
         if not args.no_cpu and world == 1:

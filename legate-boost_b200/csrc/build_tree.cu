@@ -20,7 +20,66 @@ namespace {
 // The node each row ends in, read off the binned matrix: "x <= split value" is "bin <= split bin"
 // because a split value is one of the feature's proposals (the repartition relies on the same
 // fact), so this is the walk the predict kernel does on X, on a quarter of the bytes (float32 X).
-// One thread per row; the row's bin bytes (one or two lines) stay in L1 between the levels.
+//
+// Tiled form (rows of at most kLeafMaxPitch bytes, at most kLeafMaxNodes nodes): the load/store
+// pipe spends one pass per distinct 128-byte line of a load, so a thread per row reading its own
+// line costs 32 passes per level.  Instead a warp copies its 32 consecutive rows - one contiguous
+// piece of the matrix - into shared memory with 16-byte loads (the shared rows are one word longer,
+// which spreads equal features of the 32 rows over the banks), and the tree's nodes sit in shared
+// memory too, feature + 1 and split bin packed into one word.
+constexpr int kLeafMaxPitch = 256;
+constexpr int kLeafMaxNodes = 8192;
+constexpr int kLeafWarps    = 8;
+
+template <typename BinT>
+__global__ void __launch_bounds__(kLeafWarps * 32)
+  k_leaf_of_row_tiled(const BinT* __restrict__ bins, int pitch_bytes, int64_t n_rows, const int32_t* __restrict__ feature,
+                      const int32_t* __restrict__ split_bin, int max_depth, int n_nodes, int32_t* __restrict__ leaf)
+{
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned* s_node = reinterpret_cast<unsigned*>(smem_raw);
+  for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) {
+    const int f = feature[i];
+    s_node[i]   = f < 0 ? 0u : (static_cast<unsigned>(f + 1) << 16) | static_cast<unsigned>(split_bin[i] & 0xffff);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int spitch = pitch_bytes + 4;  // bytes of a row in shared memory
+  unsigned char* tile = smem_raw + (static_cast<size_t>(n_nodes) * 4 + 15) / 16 * 16 + static_cast<size_t>(warp) * 32 * spitch;
+  const int vec_per_row  = pitch_bytes / 16;
+  const int64_t n_chunks = (n_rows + 31) / 32;
+  for (int64_t chunk = blockIdx.x * static_cast<int64_t>(kLeafWarps) + warp; chunk < n_chunks;
+       chunk += static_cast<int64_t>(gridDim.x) * kLeafWarps) {
+    const int64_t row0 = chunk * 32;
+    const int rows     = static_cast<int>(n_rows - row0 < 32 ? n_rows - row0 : 32);
+    const uint4* src   = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(bins) + row0 * pitch_bytes);
+    const int n_vec    = rows * vec_per_row;
+    __syncwarp();  // the previous chunk's walks are done with the tile
+    for (int v = lane; v < n_vec; v += 32) {
+      const uint4 w = __ldcs(src + v);
+      const int r = v / vec_per_row, c = v - r * vec_per_row;
+      unsigned* dst = reinterpret_cast<unsigned*>(tile + r * spitch + c * 16);
+      dst[0] = w.x;
+      dst[1] = w.y;
+      dst[2] = w.z;
+      dst[3] = w.w;
+    }
+    __syncwarp();
+    if (lane < rows) {
+      const BinT* b = reinterpret_cast<const BinT*>(tile + lane * spitch);
+      int node      = 0;
+      for (int d = 0; d < max_depth; ++d) {
+        // a node without children in the arrays is a leaf (its feature is -1 by construction)
+        const unsigned nd = node < n_nodes ? s_node[node] : 0u;
+        if (nd == 0u) break;
+        node = 2 * node + 1 + (static_cast<unsigned>(b[(nd >> 16) - 1]) > (nd & 0xffffu) ? 1 : 0);
+      }
+      leaf[row0 + lane] = node;
+    }
+  }
+}
+
+// One thread per row, everything from global memory: wide rows and very deep trees.
 template <typename BinT>
 __global__ void __launch_bounds__(256)
   k_leaf_of_row(const BinT* __restrict__ bins, int64_t pitch, int64_t n_rows, const int32_t* __restrict__ feature,
@@ -36,6 +95,31 @@ __global__ void __launch_bounds__(256)
     node = 2 * node + 1 + (static_cast<int>(b[f]) > __ldg(split_bin + node) ? 1 : 0);
   }
   leaf[row] = node;
+}
+
+template <typename BinT>
+void LeafOfRow(lbk_context* ctx, const void* bins, int64_t pitch, int64_t N, int F, const int32_t* feature,
+               const int32_t* split_bin, int D, int M, int32_t* leaf, cudaStream_t stream)
+{
+  const int64_t pitch_bytes = pitch * static_cast<int64_t>(sizeof(BinT));
+  const bool aligned        = (reinterpret_cast<uintptr_t>(bins) & 15) == 0;
+  if (pitch_bytes <= kLeafMaxPitch && M <= kLeafMaxNodes && F < 65535 && aligned) {
+    const size_t smem = (static_cast<size_t>(M) * 4 + 15) / 16 * 16 + static_cast<size_t>(kLeafWarps) * 32 * (pitch_bytes + 4);
+    auto fn           = k_leaf_of_row_tiled<BinT>;
+    if (smem > 48 * 1024)
+      LBK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    int per_sm = 0;
+    LBK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kLeafWarps * 32, smem));
+    const int64_t chunks = (N + 31) / 32;
+    int64_t blocks       = static_cast<int64_t>(ctx->sm_count) * (per_sm > 0 ? per_sm : 1);
+    blocks               = std::min<int64_t>(blocks, (chunks + kLeafWarps - 1) / kLeafWarps);
+    fn<<<static_cast<unsigned>(std::max<int64_t>(blocks, 1)), kLeafWarps * 32, smem, stream>>>(
+      static_cast<const BinT*>(bins), static_cast<int>(pitch_bytes), N, feature, split_bin, D, M, leaf);
+  } else {
+    const unsigned blocks = static_cast<unsigned>((N + 255) / 256);
+    k_leaf_of_row<BinT><<<blocks, 256, 0, stream>>>(static_cast<const BinT*>(bins), pitch, N, feature, split_bin, D, leaf);
+  }
+  LBK_LAUNCH_CHECK();
 }
 
 // out[i, :] = table[index[i], :]: the leaf values of the nodes a set of rows ended in.
@@ -368,14 +452,8 @@ void BuildTreeImpl(lbk_context* ctx, const lbk_build_tree_args& a, cudaStream_t 
   if (a.out_leaf != nullptr && N > 0) {
     int32_t* d_leaf = a.host_buffers ? s.alloc<int32_t>(static_cast<size_t>(N)) : a.out_leaf;
     const int64_t pitch = static_cast<int64_t>((F + kGroup - 1) / kGroup) * kGroup;
-    const unsigned blocks = static_cast<unsigned>((N + 255) / 256);
-    if (bin_bytes == 1)
-      k_leaf_of_row<uint8_t><<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(bins), pitch, N, tree.feature,
-                                                         tree.split_bin, D, d_leaf);
-    else
-      k_leaf_of_row<uint16_t><<<blocks, 256, 0, stream>>>(static_cast<const uint16_t*>(bins), pitch, N, tree.feature,
-                                                          tree.split_bin, D, d_leaf);
-    LBK_LAUNCH_CHECK();
+    if (bin_bytes == 1) LeafOfRow<uint8_t>(ctx, bins, pitch, N, F, tree.feature, tree.split_bin, D, M, d_leaf, stream);
+    else LeafOfRow<uint16_t>(ctx, bins, pitch, N, F, tree.feature, tree.split_bin, D, M, d_leaf, stream);
     if (a.host_buffers)
       LBK_CUDA(cudaMemcpyAsync(a.out_leaf, d_leaf, sizeof(int32_t) * N, cudaMemcpyDeviceToHost, stream));
   }

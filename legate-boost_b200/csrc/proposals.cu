@@ -14,6 +14,8 @@
 #include <limits>
 
 #include "device_utils.cuh"
+#include <type_traits>
+
 #include "internal.h"
 
 namespace lbk {
@@ -212,17 +214,29 @@ struct SearchLevels<T, U, -1, kPitch> {
 // One warp per row, one lane per feature of the group.
 //
 // Shared-memory variant: the proposals of the group are kept transposed and padded, sp[j][lane] =
-// proposal j of the lane's feature (+inf beyond the feature's last one, P = 2^kLog2P rows), so
-// that every probe of lane l goes to bank l: the probes of a lower_bound are conflict-free
-// wavefronts whatever the values.  The search is the branchless form "pos += step while
-// sp[pos+step-1] < x" on the shared-memory address of the lane's column, fully unrolled; it
-// returns the number of proposals below x, i.e. the index of the first proposal >= x.
+// proposal j of the lane's feature (+inf beyond the feature's last one and for the lanes beyond
+// the last feature, P = 2^kLog2P rows), so that every probe of lane l goes to bank l: the probes
+// of a lower_bound are conflict-free passes whatever the values.  The search is the branchless
+// form "pos += step while sp[pos+step-1] < x" on the shared-memory address of the lane's column,
+// fully unrolled; it returns the number of proposals below x, i.e. the index of the first
+// proposal >= x.  The pivots of the first two levels are kept in registers.
+//
+// A warp takes kTileRows consecutive rows per turn, eight at a time.  What bounds the kernel is
+// the load/store pipe (one pass per distinct 128-byte line of an instruction) and the issue slots,
+// so: the turns that lie wholly inside the matrix run without row checks; and the feature-major
+// copy of one-byte ids goes through a per-warp tile in shared memory, [32 features][kTileRows
+// bytes], from which the warp writes kTileRows contiguous bytes per feature (two features per
+// store instruction) instead of one 16-byte piece per lane and line.
+constexpr int kBinTileRows  = 64;
+constexpr int kBinTilePitch = kBinTileRows + 8;  // bytes; 18 words: 8-byte stores of 16 lanes fall on distinct banks
+
 template <typename T, typename BinT, int kLog2P, bool kCopyT>
 __global__ void __launch_bounds__(256, sizeof(T) == 4 ? 4 : 2)
   k_bin_smem(const T* __restrict__ X, int64_t ldx, int64_t n_rows, int F, const T* __restrict__ proposals,
              const int32_t* __restrict__ row_ptr, BinT* __restrict__ bins, BinT* __restrict__ bins_t, int64_t pitch_t)
 {
   constexpr int P = 1 << kLog2P;
+  constexpr bool kTile = kCopyT && sizeof(BinT) == 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* sp          = reinterpret_cast<T*>(smem_raw);
   const int g    = blockIdx.y;
@@ -238,62 +252,87 @@ __global__ void __launch_bounds__(256, sizeof(T) == 4 ? 4 : 2)
     sp[idx] = v;
   }
   __syncthreads();
-  // Lanes beyond the last feature read the last feature's values (in bounds) and store zeros.
-  const bool active    = f0 + lane < F;
-  const unsigned amask = active ? 0xffffffffu : 0u;
+  // Lanes beyond the last feature read the last feature's values (in bounds); their column of the
+  // table is all +inf, so their ids are 0.
+  const bool active = f0 + lane < F;
   constexpr unsigned kPitch = kGroup * sizeof(T);  // bytes from one proposal of a feature to the next
   const unsigned col_s      = static_cast<unsigned>(__cvta_generic_to_shared(sp + lane));
+  unsigned char* tile = smem_raw + sizeof(T) * P * kGroup + (threadIdx.x >> 5) * (kGroup * kBinTilePitch);
+  const unsigned tile_s = static_cast<unsigned>(__cvta_generic_to_shared(tile));
   // rows are counted in 32 bits (row indices are 32-bit everywhere in this library)
   const int pitch   = static_cast<int>(gridDim.y) * kGroup;  // bins are row-major, rows padded to groups
   constexpr int U   = 8;  // rows per warp in flight
   const int n       = static_cast<int>(n_rows);
   const int ld      = static_cast<int>(ldx);
-  // A warp takes 32 consecutive rows per turn, eight at a time.  With one-byte ids a lane keeps
-  // the 32 ids of its feature in registers and writes them to the feature-major copy as one whole
-  // 32-byte sector per turn.
-  constexpr int kSubs = 4;
-  constexpr int kTurn = kSubs * U;
+  constexpr int kSubs = kBinTileRows / U;
+  constexpr int kTurn = kBinTileRows;
   const int hop     = static_cast<int>(gridDim.x) * (blockDim.x >> 5) * kTurn;  // rows from one turn of a warp to the next
   int turn          = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kTurn;
   const T* xcol     = X + (active ? f0 + lane : F - 1);
   BinT* ocol        = bins + f0 + lane;
   BinT* tcol        = kCopyT ? bins_t + static_cast<int64_t>(active ? f0 + lane : F - 1) * pitch_t : nullptr;
+  // pivots of the first two levels
+  T piv_h = T(), piv_q1 = T(), piv_q3 = T();
+  if (kLog2P >= 2) {
+    piv_h  = sp[(P / 2 - 1) * kGroup + lane];
+    piv_q1 = sp[(P / 4 - 1) * kGroup + lane];
+    piv_q3 = sp[(3 * P / 4 - 1) * kGroup + lane];
+  }
   // the values of the warp's next eight rows are loaded while the current eight are searched
   auto load_rows = [&](int first, T (&x)[U]) {
+    const T* src = xcol + static_cast<int64_t>(first) * ld;
+#pragma unroll
+    for (int u = 0; u < U; ++u) x[u] = LdgStream(src + u * ld);
+  };
+  auto load_rows_checked = [&](int first, T (&x)[U]) {
     const T* src = xcol + static_cast<int64_t>(first) * ld;
 #pragma unroll
     for (int u = 0; u < U; ++u) x[u] = first + u < n ? LdgStream(src + u * ld) : static_cast<T>(-INFINITY);
   };
   T xn[U];
-  if (turn < n) load_rows(turn, xn);
-  for (; turn < n; turn += hop) {
-    uint2 sector[kSubs];
-#pragma unroll
+  if (turn < n) load_rows_checked(turn, xn);
+  // one turn; kChecked: the turn may reach beyond the last row
+  auto do_turn = [&](auto checked) {
+    constexpr bool kChecked = decltype(checked)::value;
+#pragma unroll 2
     for (int sub = 0; sub < kSubs; ++sub) {
       const int base = turn + sub * U;
       T x[U];
       unsigned pos[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        x[u]   = xn[u];
-        pos[u] = col_s;
-      }
+      for (int u = 0; u < U; ++u) x[u] = xn[u];
       {
         const int nb = sub + 1 < kSubs ? base + U : turn + hop;
-        if (nb < n) load_rows(nb, xn);
+        if (sub + 1 < kSubs && !kChecked) load_rows(nb, xn);
+        else if (nb < n) load_rows_checked(nb, xn);
       }
-      SearchLevels<T, U, kLog2P - 1, kPitch>::run(pos, x);
+      if (kLog2P >= 2) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const bool c1 = piv_h < x[u];
+          pos[u]        = c1 ? col_s + (P / 2) * kPitch : col_s;
+          const T piv   = c1 ? piv_q3 : piv_q1;
+          if (piv < x[u]) pos[u] += (P / 4) * kPitch;
+        }
+        SearchLevels<T, U, kLog2P - 3, kPitch>::run(pos, x);
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) pos[u] = col_s;
+        SearchLevels<T, U, kLog2P - 1, kPitch>::run(pos, x);
+      }
       unsigned id[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) id[u] = ((pos[u] - col_s) / kPitch) & amask;
+      for (int u = 0; u < U; ++u) id[u] = (pos[u] - col_s) / kPitch;
       BinT* orow = ocol + static_cast<int64_t>(base) * pitch;
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (base + u < n) orow[u * pitch] = static_cast<BinT>(id[u]);
+        if (!kChecked || base + u < n) orow[u * pitch] = static_cast<BinT>(id[u]);
       if (kCopyT) {
-        if (sizeof(BinT) == 1) {
-          sector[sub].x = id[0] | (id[1] << 8) | (id[2] << 16) | (id[3] << 24);
-          sector[sub].y = id[4] | (id[5] << 8) | (id[6] << 16) | (id[7] << 24);
+        if (kTile) {
+          const unsigned lo = id[0] | (id[1] << 8) | (id[2] << 16) | (id[3] << 24);
+          const unsigned hi = id[4] | (id[5] << 8) | (id[6] << 16) | (id[7] << 24);
+          asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(tile_s + lane * kBinTilePitch + sub * U), "r"(lo), "r"(hi)
+                       : "memory");
         } else if (active && base < n) {
           uint4 pk;
           pk.x = id[0] | (id[1] << 16);
@@ -304,12 +343,26 @@ __global__ void __launch_bounds__(256, sizeof(T) == 4 ? 4 : 2)
         }
       }
     }
-    if (kCopyT && sizeof(BinT) == 1 && active) {
-      uint4* dst = reinterpret_cast<uint4*>(tcol + turn);
-      dst[0]     = make_uint4(sector[0].x, sector[0].y, sector[1].x, sector[1].y);
-      dst[1]     = make_uint4(sector[2].x, sector[2].y, sector[3].x, sector[3].y);
+    if (kTile) {
+      // the tile leaves feature by feature: lanes 0-15 write the 64 bytes of one feature, lanes
+      // 16-31 those of the next (rows up to the padded end of a feature's row of the copy; the ids
+      // of rows beyond the last one are 0)
+      __syncwarp();
+      const int w    = lane & 15;
+      const bool in  = turn + 4 * w < pitch_t;
+#pragma unroll 4
+      for (int i = 0; i < kGroup / 2; ++i) {
+        const int fl = 2 * i + (lane >> 4);
+        unsigned v;
+        asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(tile_s + fl * kBinTilePitch + 4 * w));
+        if (in && f0 + fl < F)
+          *reinterpret_cast<unsigned*>(bins_t + static_cast<int64_t>(f0 + fl) * pitch_t + turn + 4 * w) = v;
+      }
+      __syncwarp();
     }
-  }
+  };
+  for (; turn + kTurn <= n; turn += hop) do_turn(std::false_type());
+  if (turn < n) do_turn(std::true_type());
 }
 
 // Global-memory variant for features with more proposals than shared memory holds.
@@ -403,8 +456,10 @@ void BinMatrix(const T* X, int64_t ldx, int64_t n_rows, int F, const T* proposal
   // the shared-memory table is padded to one of a few sizes (each is its own fully unrolled kernel)
   const int need   = NextPow2(max_bins_per_feature);
   const int log2p  = need <= 16 ? 4 : need <= 64 ? 6 : need <= 256 ? 8 : 9;
-  const size_t smem     = sizeof(T) * static_cast<size_t>(kGroup) * (size_t{1} << log2p);
-  const bool use_smem   = need <= 512 && smem <= 96 * 1024;
+  // the table, and one tile per warp for the feature-major copy of one-byte ids
+  const size_t table    = sizeof(T) * static_cast<size_t>(kGroup) * (size_t{1} << log2p);
+  const size_t smem     = table + (bins_t != nullptr && bin_bytes == 1 ? size_t{8} * kGroup * kBinTilePitch : 0);
+  const bool use_smem   = need <= 512 && table <= 96 * 1024;
   // a block fills its table once and then walks the rows with a grid stride: the grid is what is
   // resident at once (from the occupancy calculator), spread over the feature groups
   auto make_grid = [&](int blocks_per_sm) {

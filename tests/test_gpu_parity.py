@@ -295,6 +295,32 @@ def test_scratch_through_the_callers_allocator(lb):
     assert ctx.pool_bytes() > 0
 
 
+@pytest.mark.parametrize("N,F,K,D,S,dtype", [
+    (50001, 40, 1, 8, 256, np.float32),    # rows of 64 bytes, a last chunk of one row
+    (20000, 7, 2, 5, 64, np.float64),      # one group
+    (9000, 130, 1, 6, 256, np.float32),    # rows of 160 bytes
+    (6000, 300, 1, 4, 128, np.float32),    # rows wider than the tiled form takes
+    (7000, 20, 1, 6, 400, np.float32),     # two-byte bins
+    (3000, 5, 1, 13, 256, np.float32),     # more nodes than the tiled form takes
+])
+def test_leaf_record_is_the_walk_of_predict(lb, N, F, K, D, S, dtype):
+    """out_leaf (read off the binned matrix) names, for every row, the node whose value predict adds
+    for that row when it walks X: leaf_value[out_leaf] == predict(X, tree), bit for bit."""
+    from legateboost_b200.tree import build_tree_arrays, predict_arrays
+
+    rs = np.random.RandomState(N % 97)
+    X = dev(rs.normal(size=(N, F)).astype(dtype))
+    g, h = dev(rs.normal(size=(N, K))), dev(rs.random((N, K)) + 0.05)
+    t = build_tree_arrays(X, g, h, max_depth=D, split_samples=S, seed=4, row_offset=0, dataset_rows=N, want_leaf=True)
+    # distinct values per node, so that equal predictions mean equal nodes
+    M = t["feature"].shape[0]
+    values = torch.arange(1, M * K + 1, dtype=torch.float64, device=X.device).reshape(M, K)
+    pred = predict_arrays(X, [(values, t["feature"], t["split_value"])])
+    leaf = t["leaf"].long()
+    assert int(leaf.min()) >= 0 and int(leaf.max()) < M
+    assert torch.equal(values[leaf], pred)
+
+
 def test_fixed_sketch_save_and_reuse(lb, oracle):
     """The optional sketch buffer: a saving call gives the oracle's tree, a reusing call with the same
     seed gives it again without reading X, a reusing call with another seed splits on the saved
