@@ -118,9 +118,10 @@ def hist_inputs(torch, n_rows, seed, device):
 
 # DRAM bytes of one k_hist_smem launch as ncu measured them (profiles/k_hist_smem_config2_ncu.md):
 # bytes read per row, and bytes that do not grow with the rows (the output leaving L2 and what the
-# flush buffer left dirty there).  None = no capture of the kernel as it is now: traffic is null.
-HIST_DRAM_BYTES_PER_ROW = None
-HIST_DRAM_BYTES_FIXED = None
+# flush buffer left dirty there), from the 2 M-row capture of the kernel as it is now.  None = no such
+# capture: traffic is null.
+HIST_DRAM_BYTES_PER_ROW = 145.2
+HIST_DRAM_BYTES_FIXED = 60.1e6
 
 
 def hist_traffic(n_rows):

@@ -90,6 +90,13 @@ int lbk_comm_size(const lbk_context* ctx);
  * feature exactly once; a pure function of its arguments (no device needed).  The reference has no
  * counterpart: all of its ranks reduce and search everything (build_tree.cu:1107-1151). */
 int lbk_owned_features(int rank, int n_ranks, int n_features, int* begin, int* end);
+/* Failure detection check that needs no second GPU and faults nothing: runs the barrier kernel of the
+ * peer exchange for an emulated world of two ranks on this context's device.  With peer_present != 0
+ * the other rank's flag is preset and the call returns LBK_OK; with 0 nobody ever sets it, the
+ * kernel's wait runs out after about a second, it reports through the context's status word and
+ * returns, and the call returns LBK_ERR_DEVICE with the fault code in lbk_last_error.  The context
+ * is usable afterwards.  No counterpart in the reference (NCCL's own timeouts play that role). */
+int lbk_selftest_peer_barrier(lbk_context* ctx, int peer_present, void* stream);
 
 /* Timing of the histogram kernel alone (no counterpart in the reference, which leaves profiling
  * to external tools): when enabled, every histogram launch is bracketed by CUDA events on the

@@ -434,3 +434,28 @@ void ExchangeGatherAll(lbk_context* ctx, void* buf, void* dst, int n_seg, int B,
 }
 
 }  // namespace lbk
+
+// The peer barrier's bounded wait, exercised on one GPU: an emulated world of two ranks whose flag
+// arrays both live on this device; rank 1 either has arrived already (its flag is preset) or never
+// arrives.  In the second case the kernel gives up after its limit (about a second), reports
+// through the status word and returns, and this call returns LBK_ERR_DEVICE; the context stays
+// usable.  Nothing faults, traps or spins without limit.
+extern "C" int lbk_selftest_peer_barrier(lbk_context* ctx, int peer_present, void* stream_)
+{
+  return lbk::Guard(ctx, [&] {
+    LBK_EXPECT(ctx != nullptr, "null argument");
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    lbk::Scratch s(ctx, stream);
+    unsigned* flags = s.alloc<unsigned>(4);  // [rank 0's array: slots 0, 1][rank 1's array: slots 0, 1]
+    void** table    = s.alloc<void*>(2);
+    const unsigned h_flags[4] = {0u, peer_present ? 1u : 0u, 0u, 0u};
+    void* h_table[2]          = {flags, flags + 2};
+    LBK_CUDA(cudaMemcpyAsync(flags, h_flags, sizeof(h_flags), cudaMemcpyHostToDevice, stream));
+    LBK_CUDA(cudaMemcpyAsync(table, h_table, sizeof(h_table), cudaMemcpyHostToDevice, stream));
+    lbk::k_peer_barrier<<<1, 64, 0, stream>>>(table, 2, 0, 1u, ctx->d_status);
+    LBK_LAUNCH_CHECK();
+    lbk::CheckDeviceStatus(ctx, stream);
+  });
+}
+

@@ -20,7 +20,7 @@ EXPORTS = [
     "lbk_version", "lbk_context_create", "lbk_context_destroy", "lbk_last_error", "lbk_context_trim",
     "lbk_context_set_allocator", "lbk_context_pool_bytes",
     "lbk_comm_unique_id", "lbk_comm_init", "lbk_comm_attach_nccl", "lbk_comm_set_callback",
-    "lbk_comm_size", "lbk_owned_features", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_profile_histogram_total", "lbk_build_tree", "lbk_sketch_bytes", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
+    "lbk_comm_size", "lbk_owned_features", "lbk_selftest_peer_barrier", "lbk_profile_enable", "lbk_profile_histogram_ms", "lbk_profile_histogram_total", "lbk_build_tree", "lbk_sketch_bytes", "lbk_leaf_values", "lbk_update_tree", "lbk_gradient", "lbk_predict", "lbk_split_proposals", "lbk_bin_matrix",
     "lbk_bin_matrix_bytes", "lbk_quantise", "lbk_histogram", "lbk_histogram_noalloc", "lbk_group_rows",
 ]
 
@@ -120,6 +120,7 @@ def load():
             lib.lbk_comm_attach_nccl.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
             lib.lbk_comm_size.argtypes = [C.c_void_p]
             lib.lbk_owned_features.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+            lib.lbk_selftest_peer_barrier.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
             lib.lbk_profile_enable.argtypes = [C.c_void_p, C.c_int]
             lib.lbk_profile_histogram_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
             lib.lbk_profile_histogram_total.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]

@@ -321,6 +321,29 @@ def test_leaf_record_is_the_walk_of_predict(lb, N, F, K, D, S, dtype):
     assert torch.equal(values[leaf], pred)
 
 
+def test_peer_barrier_gives_up_and_reports(lb):
+    """A peer that never reaches the barrier of the histogram exchange: the barrier kernel's wait is
+    bounded (about a second), then it reports through the status word and returns, the call returns
+    an error, and the context keeps working.  Emulated on one GPU with a flag that nothing sets."""
+    import time
+    from legateboost_b200.tree import build_tree_arrays
+
+    ctx = lb.library.context(torch.cuda.current_device())
+    stream = torch.cuda.current_stream().cuda_stream
+    assert ctx.lib.lbk_selftest_peer_barrier(ctx.handle, 1, stream) == 0
+    t0 = time.perf_counter()
+    rc = ctx.lib.lbk_selftest_peer_barrier(ctx.handle, 0, stream)
+    dt = time.perf_counter() - t0
+    assert rc != 0 and b"fault code 41" in ctx.lib.lbk_last_error(ctx.handle)
+    assert dt < 20.0
+    # the status word was cleared and the device still answers: a present peer passes, a tree builds
+    assert ctx.lib.lbk_selftest_peer_barrier(ctx.handle, 1, stream) == 0
+    rs = np.random.RandomState(0)
+    X, g, h = dev(rs.random((500, 4)).astype(np.float32)), dev(rs.normal(size=(500, 1))), dev(rs.random((500, 1)) + 0.1)
+    t = build_tree_arrays(X, g, h, max_depth=2, split_samples=16, seed=1, row_offset=0, dataset_rows=500)
+    assert int((t["feature"] >= 0).sum()) >= 1
+
+
 def test_fixed_sketch_save_and_reuse(lb, oracle):
     """The optional sketch buffer: a saving call gives the oracle's tree, a reusing call with the same
     seed gives it again without reading X, a reusing call with another seed splits on the saved
