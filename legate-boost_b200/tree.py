@@ -174,6 +174,46 @@ def predict_arrays(X, trees, n_outputs=None, ctx=None):
     return pred
 
 
+def onnx_tree_ensemble_attributes(feature, split_value, leaf_value):
+    """The attributes of ONNX ``ai.onnx.ml.TreeEnsemble`` (opset 5) nodes for one tree in the
+    heap layout of this library, one dict per output column (the operator has scalar leaves, so a
+    vector-leaf tree becomes ``n_outputs`` ensembles that share the structure; the reference does
+    the same, legateboost/models/tree.py:319-438).  Node slot i of the heap is both interior node
+    i and leaf i of the operator: a child id is a node index or a leaf index depending on the
+    ``*leafs`` flag of its parent.  numpy in, numpy out; no onnx package needed."""
+    feature = np.asarray(feature, dtype=np.int64)
+    split_value = np.asarray(split_value, dtype=np.float64)
+    leaf_value = np.asarray(leaf_value, dtype=np.float64)
+    M = feature.shape[0]
+    ids = np.arange(M, dtype=np.int64)
+    left, right = 2 * ids + 1, 2 * ids + 2
+    is_leaf = feature < 0
+
+    def child_is_leaf(child):
+        # children of leaf slots can point past the arrays; such slots are never visited
+        return is_leaf[np.minimum(child, M - 1)].astype(np.int64)
+
+    true_leaf, false_leaf = child_is_leaf(left), child_is_leaf(right)
+    true_id, false_id = left.copy(), right.copy()
+    if is_leaf[0]:
+        # a tree that is one leaf: the root sends every row to leaf 0
+        true_id[0] = false_id[0] = 0
+        true_leaf[0] = false_leaf[0] = 1
+    out = []
+    for k in range(leaf_value.shape[1]):
+        out.append(dict(
+            n_targets=int(leaf_value.shape[1]), aggregate_function=1, post_transform=0, tree_roots=[0],
+            nodes_modes=np.zeros(M, dtype=np.uint8),            # 0 = BRANCH_LEQ: x <= split goes to the true child
+            nodes_featureids=np.where(is_leaf, 0, feature),
+            nodes_splits=split_value.copy(),
+            nodes_truenodeids=true_id, nodes_trueleafs=true_leaf,
+            nodes_falsenodeids=false_id, nodes_falseleafs=false_leaf,
+            leaf_targetids=np.full(M, k, dtype=np.int64),
+            leaf_weights=leaf_value[:, k].copy(),
+        ))
+    return out
+
+
 class BaseModel:
     """Interface of a base learner (reference: legateboost/models/base_model.py:11-138)."""
 
@@ -366,6 +406,36 @@ class Tree(BaseModel):
         state.pop("_fit_rows", None)
         state.pop("sketch", None)
         return state
+
+    def to_onnx(self) -> Any:
+        """The tree as an ONNX model: X (float64, [rows, features]) -> predictions ([rows, outputs]),
+        one ``TreeEnsemble`` node per output column summed with ``Add`` nodes, as the reference
+        exports it (legateboost/models/tree.py:319-438).  Needs the ``onnx`` package."""
+        try:
+            import onnx
+            from onnx import helper, numpy_helper
+        except ImportError as e:  # the reference fails the same way without the package
+            raise ImportError("Tree.to_onnx needs the onnx package") from e
+        attrs = onnx_tree_ensemble_attributes(self.feature.cpu().numpy(), self.split_value.cpu().numpy(),
+                                              self.leaf_value.cpu().numpy())
+        nodes = []
+        last = None
+        for k, a in enumerate(attrs):
+            tensors = {n: numpy_helper.from_array(a[n], name=n) for n in ("nodes_modes", "nodes_splits", "leaf_weights")}
+            plain = {n: (v.tolist() if isinstance(v, np.ndarray) else v) for n, v in a.items() if n not in tensors}
+            nodes.append(helper.make_node("TreeEnsemble", ["X"], ["pred%d" % k], domain="ai.onnx.ml", **plain, **tensors))
+            acc = "accumulated_pred%d" % k
+            if last is None:
+                nodes.append(helper.make_node("Identity", ["pred%d" % k], [acc]))
+            else:
+                nodes.append(helper.make_node("Add", [last, "pred%d" % k], [acc]))
+            last = acc
+        X = helper.make_tensor_value_info("X", onnx.TensorProto.DOUBLE, [None, None])
+        Y = helper.make_tensor_value_info(last, onnx.TensorProto.DOUBLE, [None, None])
+        graph = helper.make_graph(nodes, "legateboost.models.Tree", [X], [Y])
+        model = helper.make_model(graph, opset_imports=[helper.make_opsetid("ai.onnx.ml", 5), helper.make_opsetid("", 14)])
+        onnx.checker.check_model(model)
+        return model
 
     def __mul__(self, scalar: Any) -> "Tree":
         self._fit_rows = None  # the record of the training rows is not worth copying
