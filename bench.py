@@ -69,20 +69,33 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def wait_for_first_sample(self, limit=3.0):
+        """nvidia-smi takes a moment to start printing: the timed region should begin after that."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.rows and time.perf_counter() - t0 < limit:
+            time.sleep(0.01)
+
+    def stop(self, t_begin=None, t_end=None, t_load=None):
+        """Median SM clock and the throttle reasons seen between t_begin and t_load (host clock,
+        seconds: the timed region and the identical untimed steps after it); all samples if none
+        arrived in that window."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.03)  # the sample taken at the end of the window is still on its way
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        rows = list(self.rows)
+        timed = [r for t, r in rows if t_begin is not None and t_begin <= t <= t_end + 0.03]
+        loaded = [r for t, r in rows if t_begin is not None and t_begin <= t <= (t_load or t_end) + 0.03]
+        use = loaded if loaded else [r for _, r in rows]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in use:
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
@@ -92,7 +105,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "samples_in_timed_region": len(timed), "reasons": sorted(reasons)}
 
 
 def hist_inputs(torch, n_rows, seed, device):
@@ -530,14 +543,16 @@ def run_hist(args):
         allreduce_check = "ok" if int(flag[0]) == 1 else "mismatch"
         del want, own, full
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        sampler.wait_for_first_sample()
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    t_begin = time.perf_counter()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     kernel_ms = []
     for i in range(args.steps):
@@ -551,12 +566,24 @@ def run_hist(args):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    t_end = time.perf_counter()
     total_ms = sum(a.elapsed_time(b) for a, b in ev)
     t = torch.tensor([total_ms, sum(kernel_ms)], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, ksum = float(t[0]), float(t[1])
+    # A short timed region sees few clock samples: the same steps go on, untimed, until about a
+    # quarter of a second of this load has passed, so that nvidia-smi reports a handful of samples
+    # under it.  The count comes from the reduced time, so every rank runs the same number (a
+    # multi-rank step is collective).
+    t_load = t_end
+    if not args.no_clock_tail:
+        n_tail = int(250.0 / max(total_ms / args.steps, 1e-3)) - args.steps
+        for _ in range(max(0, min(n_tail, 1000))):
+            step()
+        torch.cuda.synchronize()
+        t_load = time.perf_counter()
+    clocks = sampler.stop(t_begin, t_end, t_load) if rank == 0 else None
     value = n_rows * HIST_FEATURES * world * args.steps / (total_ms * 1e-3)
 
     # end to end through the C ABI with host buffers (pinned), copies inside the timed region
@@ -797,6 +824,7 @@ def main():
                          "row_index order")
     ap.add_argument("--no-extra", action="store_true",
                     help="hist workload: leave the rounds/s and predict rows/s sections out of the line")
+    ap.add_argument("--no-clock-tail", action="store_true", help="do not run untimed steps after the timed region for clock samples")
     ap.add_argument("--rounds-rows", type=int, default=ROUNDS_TOTAL_ROWS)
     ap.add_argument("--rounds", type=int, default=3)
     ap.add_argument("--predict-rows", type=int, default=PREDICT_TOTAL_ROWS)
