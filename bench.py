@@ -697,16 +697,27 @@ def run_train(args):
     n, F = args.rows, args.features
     X = torch.rand((n, F), dtype=torch.float32, device=device, generator=gen)
     w = torch.randn(F, dtype=torch.float32, device=device, generator=torch.Generator(device=device).manual_seed(3))
-    y = X @ w + 0.1 * torch.randn(n, dtype=torch.float32, device=device, generator=gen)
+    if args.classes > 1:
+        # multi-output classification: labels = argmax of a noisy linear map of the first features
+        # (all classes occur on every rank; the softmax objective has one output per class)
+        c = args.classes
+        X = torch.randn((n, F), dtype=torch.float32, device=device, generator=gen)
+        W = torch.randn((min(F, c), c), dtype=torch.float32, device=device,
+                        generator=torch.Generator(device=device).manual_seed(3))
+        y = (X[:, : min(F, c)] @ W + 0.5 * torch.randn((n, c), dtype=torch.float32, device=device, generator=gen)).argmax(dim=1)
+        make = lambda r: lb.LBClassifier(n_estimators=r, base_models=(lb.Tree(max_depth=args.depth),), random_state=0,  # noqa: E731
+                                         fixed_sketch=args.fixed_sketch)
+    else:
+        y = X @ w + 0.1 * torch.randn(n, dtype=torch.float32, device=device, generator=gen)
+        make = lambda r: lb.LBRegressor(n_estimators=r, base_models=(lb.Tree(max_depth=args.depth),), random_state=0,  # noqa: E731
+                                        fixed_sketch=args.fixed_sketch)
     rounds = args.steps
-    m = lb.LBRegressor(n_estimators=max(args.warmup, 1), base_models=(lb.Tree(max_depth=args.depth),), random_state=0,
-                       fixed_sketch=args.fixed_sketch)
+    m = make(max(args.warmup, 1))
     m.fit(X, y)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    m = lb.LBRegressor(n_estimators=rounds, base_models=(lb.Tree(max_depth=args.depth),), random_state=0,
-                       fixed_sketch=args.fixed_sketch)
+    m = make(rounds)
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     m.fit(X, y)
@@ -721,8 +732,9 @@ def run_train(args):
                           "n_gpus": world, "steps": rounds, "warmup": max(args.warmup, 1), "ms_per_step": ms / rounds,
                           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
                           "data": "synthetic",
-                          "config": {"workload": "squared-error boosting, depth %d, 256 bins, %d rows x %d features per GPU%s"
-                                                 % (args.depth, n, F, ", proposals and bins of the first tree reused "
+                          "config": {"workload": "%s boosting, depth %d, 256 bins, %d rows x %d features per GPU%s"
+                                                 % ("%d-class log-loss" % args.classes if args.classes > 1 else "squared-error",
+                                                    args.depth, n, F, ", proposals and bins of the first tree reused "
                                                     "(not the reference's per-tree sketch)" if args.fixed_sketch else "")}}),
               flush=True)
     if world > 1:
@@ -815,6 +827,7 @@ def main():
     ap.add_argument("--features", type=int, default=64)
     ap.add_argument("--depth", type=int, default=8)
     ap.add_argument("--trees", type=int, default=500)
+    ap.add_argument("--classes", type=int, default=1, help="train workload: > 1 = classification with that many classes")
     ap.add_argument("--float-path", action="store_true")
     ap.add_argument("--fixed-sketch", action="store_true",
                     help="train workload: reuse the first tree's proposals and bins (an extension; results differ "
