@@ -641,7 +641,9 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
     const int g0     = gp * W;
     const int groups = min(W, p.G - g0);
     const int seg    = pc.slot * p.K + k;
-    const bool tree  = pc.pieces > 1 && pc.tree_base >= 0 && p.partial != nullptr && pc.node_rows <= cap_rows &&
+    // the merge tree adds 32-bit images: a piece (at most range_rows rows) has to stay below the safe
+    // count, and the tree is climbed only as far as the merged images do (see below)
+    const bool tree  = pc.pieces > 1 && pc.tree_base >= 0 && p.partial != nullptr && range_rows <= cap_rows &&
                       rows_safe >= kTileRows;
     if (rows_safe < kTileRows || (pc.re - pc.rb <= kDirectRows && !tree)) {
       DirectRows<uint8_t, A>(p, pc.rb, pc.re, g0 * kGroup, groups, k, seg, warp, kWarps, lane);
@@ -720,10 +722,18 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
     smem_t* slots         = static_cast<smem_t*>(p.partial);
     const int n4          = hist_words >> 2;
     int idx = pc.index, members = pc.pieces, soff = 0, coff = 0;
+    long long image_rows = range_rows;  // rows an image of this tree level holds at most
     while (true) {
       const int n_groups = (members + kTreeFanIn - 1) / kTreeFanIn;
       const int grp      = idx / kTreeFanIn;
       const int gsize    = min(kTreeFanIn, members - grp * kTreeFanIn);
+      // A node with more rows than 32-bit sums are safe for: its images are merged as far as they
+      // stay below that count, and what is left (a handful instead of one per piece) is added into
+      // the output with 64-bit atomics.  Every holder of an image of this level decides alike.
+      if (min(static_cast<long long>(pc.node_rows), image_rows * kTreeFanIn) > cap_rows) {
+        flush(true);
+        return;
+      }
       if (gsize > 1) {
         // leave my sums where the last one of the group finds them, then count myself in
         smem_t* mine = slots + (static_cast<size_t>(pc.tree_base + soff + idx) * GK + gk) * stride;
@@ -755,6 +765,7 @@ __global__ void __launch_bounds__(kHistThreads * W, W == 1 ? 2 : 1)
       coff += n_groups;
       idx     = grp;
       members = n_groups;
+      image_rows *= kTreeFanIn;
     }
     flush(false);
   };

@@ -682,7 +682,10 @@ def test_full_size_histogram_exact(lb):
 
 @pytest.mark.parametrize("N,F,K,weights,mode,qmax", [
     (1_500_000, 64, 1, [0.80, 0.0, 0.15, 0.05], 0, 300),    # one node in about 120 pieces: a deep merge tree
-    (1_500_000, 64, 1, [0.80, 0.0, 0.15, 0.05], 0, 5000),   # ... too many rows for 32-bit sums: atomics instead
+    (1_500_000, 64, 1, [0.80, 0.0, 0.15, 0.05], 0, 5000),   # ... too many rows for 32-bit sums: the tree is climbed
+                                                            # two levels, the rest are 64-bit atomics
+    (1_500_000, 64, 1, [0.80, 0.0, 0.15, 0.05], 0, 40000),  # ... one level only
+    (1_500_000, 64, 1, [0.80, 0.0, 0.15, 0.05], 0, 400000), # ... a single piece is already too long: no tree
     (1_500_000, 96, 3, [0.3, 0.3, 0.2, 0.1, 0.1], 0, 300),  # three groups: the second group set is half empty
     (2_000_000, 32, 2, [1.0] * 37, 0, 300),                 # one group per unit (two blocks per SM)
     (1_500_000, 128, 1, [0.55, 0.45], 1, 0),                # float pairs through the same ranges
