@@ -108,7 +108,8 @@ def _worker(rank, world, port, case, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("case", [(20000, 40, 1, 6, 256), (5001, 13, 3, 5, 64)])
+@pytest.mark.parametrize("case", [(20000, 40, 1, 6, 256), (5001, 13, 3, 5, 64),
+                                  (3000, 1, 1, 3, 16)])  # one feature: rank 0 owns none and searches nothing
 def test_two_gpus_match_oracle_with_two_ranks(case):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -121,7 +122,7 @@ def test_two_gpus_match_oracle_with_two_ranks(case):
     procs = [ctx.Process(target=_worker, args=(r, world, port, case, q)) for r in range(world)]
     res = _run(procs, q, world)
     assert all(ok for _, ok, _ in res), res
-    assert res[0][2] > 3
+    assert res[0][2] >= 3
 
 
 def _hist_worker(rank, world, port, q):
