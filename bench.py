@@ -839,7 +839,7 @@ def main():
                     help="hist workload: leave the rounds/s and predict rows/s sections out of the line")
     ap.add_argument("--no-clock-tail", action="store_true", help="do not run untimed steps after the timed region for clock samples")
     ap.add_argument("--rounds-rows", type=int, default=ROUNDS_TOTAL_ROWS)
-    ap.add_argument("--rounds", type=int, default=3)
+    ap.add_argument("--rounds", type=int, default=5)
     ap.add_argument("--predict-rows", type=int, default=PREDICT_TOTAL_ROWS)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
